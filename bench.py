@@ -1,0 +1,254 @@
+"""Decode throughput of the B200 decoder token loop.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl b200|reference] [--workload c2]
+
+A step is one greedy single-token decode step of the whole batch (embedding ... logits, argmax, token feedback).
+Default workload: BASELINE configuration 2 (vocab 32000, d 768, 12 layers, 12/4 heads, SwiGLU 2048, bf16 weights,
+batch 16 per GPU, prompt 512 random ids).  Weights and prompts are seeded synthetic data.  With N > 1 (one process
+per GPU under torch.distributed.run) every rank decodes its own batch of independent sequences with replicated
+weights and no collective on the data path: weak scaling.
+
+The printed JSON line carries the device-resident throughput (`value`), the host-in-the-loop throughput through
+the C ABI (`e2e`), the roofline of the dominant kernel (`roofline`) and the reference's CPU decoder timed on the
+host cores (`cpu_baseline`).  `--impl reference` times only that CPU decoder.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+from ctorch_b200 import workloads as W  # noqa: E402
+
+METRIC, UNIT = "decode_tokens_per_s", "tokens/s"
+
+
+def measured_peaks() -> tuple[float, str]:
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as handle:
+            return float(json.load(handle)["hbm_gbs"]), "measured"
+    except Exception:  # noqa: BLE001
+        return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.rows, self.process = index, [], None
+
+    def start(self):
+        try:
+            self.process = subprocess.Popen(["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.QUERY}",
+                                             "--format=csv,noheader,nounits", "-lms", "100"], stdout=subprocess.PIPE,
+                                            stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.process = None
+
+    def _read(self):
+        for line in self.process.stdout:
+            self.rows.append([cell.strip() for cell in line.split(",")])
+
+    def stop(self) -> dict:
+        if self.process:
+            self.process.terminate()
+            try:
+                self.process.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.process.kill()
+        clocks, maxima, reasons = [], [], set()
+        for row in self.rows:
+            try:
+                clocks.append(float(row[0]))
+                maxima.append(float(row[1]))
+            except (ValueError, IndexError):
+                continue
+            for name, cell in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), row[2:6]):
+                if cell.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": float(np.median(clocks)) if clocks else None, "sm_max_mhz": max(maxima) if maxima else None,
+                "reasons": sorted(reasons), "samples": len(clocks)}
+
+
+def cpu_reference(spec: dict, weights, steps: int, warmup: int, threads: int | None = None) -> dict:
+    """The reference's CPU decoder on this machine's cores: one or more sequences per worker thread, a short prompt
+    (CPU prefill of the full prompt would take minutes), `steps` timed greedy steps of the whole batch."""
+    import oracle
+    kind = "ref" if oracle.have_ref() else "port"
+    cores = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+    threads = max(1, min(threads or cores, spec["batch"]))
+    prompt_length = 8
+    cpu_spec = dict(spec, context=prompt_length + warmup + steps + 1)
+    model = oracle.CpuDecoder(cpu_spec, weights, kind=kind)
+    seconds = oracle.timed_decode(model, W.make_prompts(cpu_spec, length=prompt_length), warmup, steps, threads)
+    model.close()
+    return {"value": spec["batch"] * steps / seconds, "unit": UNIT, "cores": threads,
+            "kind": "reference" if kind == "ref" else "port", "seconds": seconds,
+            "sample": f"{steps} greedy steps of batch {spec['batch']} after an {prompt_length}-token prompt and {warmup} "
+                      f"warm-up steps, {threads} threads (own sequences and caches each)"}
+
+
+def distributed():
+    """(rank, world, local_rank, dist module or None).  torch.distributed is only plumbing: barrier and max-reduce."""
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if world == 1:
+        return 0, 1, 0, None
+    import torch
+    import torch.distributed as dist
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    return dist.get_rank(), world, local, dist
+
+
+def max_over_ranks(value: float, dist, local: int) -> float:
+    if dist is None:
+        return value
+    import torch
+    t = torch.tensor([value], dtype=torch.float64, device=torch.device("cuda", local))
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+def barrier(dist, local: int):
+    if dist is not None:
+        import torch
+        dist.barrier(device_ids=[local])
+        torch.cuda.synchronize(local)
+
+
+def run_reference(args, spec, weights) -> dict:
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return {}
+    result = cpu_reference(spec, weights, args.steps, args.warmup)
+    ms = result["seconds"] * 1000.0 / args.steps
+    return {"impl": "reference", "metric": METRIC, "value": result["value"], "unit": UNIT, "n_gpus": args.gpus,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": args.workload, "batch": spec["batch"], "note": "CPU decoder of the reference, f32 math on " + spec["dtype"] + " weights"},
+            "cpu_baseline": {k: result[k] for k in ("value", "unit", "cores", "kind", "sample")},
+            "e2e": {"value": result["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0}
+
+
+def run_b200(args, spec, weights) -> dict:
+    import ctorch_b200 as B
+    rank, world, local, dist = distributed()
+    batch, prompt_len = spec["batch"], spec["prompt"]
+    total_steps = 2 * (args.warmup + args.steps) + 4
+    spec = dict(spec, context=max(spec["context"], prompt_len + total_steps + 1))
+    model = B.DecoderModel(spec, weights, device=local)
+    gen = B.Generation(model, batch, total_steps + 1)
+    prompt = W.make_prompts(spec, seed=99 + rank)
+    sampler = ClockSampler(local)
+    sampler.start()  # nvidia-smi needs about a second to start: it runs from the prefill to the end of the timed loops
+    gen.prefill(prompt)
+    B.synchronize(local)
+
+    # ---- device-resident loop: K graph replays, timed with CUDA events on the library's stream ----
+    gen.step(args.warmup)
+    B.synchronize(local)
+    start_length = model.cache_length()
+    barrier(dist, local)
+    B.timer_start(local)
+    gen.step(args.steps)
+    device_ms = B.timer_stop(local)
+    barrier(dist, local)
+    device_ms = max_over_ranks(device_ms, dist, local)
+
+    # ---- host in the loop: ids H2D, one step, chosen ids D2H, every step (the reference example's loop) ----
+    out = np.empty(batch, dtype=np.int64)
+    feed = np.ascontiguousarray(gen.tokens()[:, -1])
+    for _ in range(args.warmup):
+        gen.step_host(feed, out)
+        feed, out = out, feed
+    barrier(dist, local)
+    B.timer_start(local)
+    for _ in range(args.steps):
+        gen.step_host(feed, out)
+        feed, out = out, feed
+    e2e_ms = max_over_ranks(B.timer_stop(local), dist, local)
+    clocks = sampler.stop()
+
+    # ---- per-kernel-class device time of one eager step (events after every launch) ----
+    profile = gen.profile_step()
+    for _ in range(2):
+        more = gen.profile_step()
+        profile = {k: min(profile[k], more[k]) for k in profile}
+    launches = gen.launches_per_step()
+
+    tokens = world * batch * args.steps
+    value = tokens / (device_ms / 1000.0)
+    mean_context = start_length + args.steps / 2.0
+    kv_dtype = "bf16" if spec["dtype"] == "bf16" else "f32"
+    linear_bytes = W.weight_bytes(spec)
+    kv_bytes = W.kv_bytes_per_token(spec, kv_dtype) * mean_context * batch
+    peak, peak_kind = measured_peaks()
+    achieved = linear_bytes / (profile["linear_ms"] / 1000.0) / 1e9 if profile["linear_ms"] > 0 else None
+    line = {
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": device_ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16 weights and KV, f32 accumulate and activations" if spec["dtype"] == "bf16" else "f32",
+        "data": "synthetic",
+        "config": {"workload": args.workload, "batch_per_gpu": batch, "prompt": prompt_len, "mean_context": mean_context,
+                   "layers": spec["layers"], "d_model": spec["d_model"], "vocab": spec["vocab"], "parallelism": f"replicas x{world}",
+                   "l2": "inputs larger than L2: %.0f MB of weights and KV are streamed per step" % ((linear_bytes + kv_bytes) / 1e6),
+                   "step_bytes": linear_bytes + kv_bytes,
+                   "step_gbs": (linear_bytes + kv_bytes) / (device_ms / args.steps / 1000.0) / 1e9,
+                   "step_frac_of_peak": (linear_bytes + kv_bytes) / (device_ms / args.steps / 1000.0) / 1e9 / peak,
+                   "kernel_ms_per_step": profile},
+        "clocks": clocks,
+        "e2e": {"value": tokens / (e2e_ms / 1000.0), "unit": UNIT, "h2d_bytes_per_step": 8 * batch, "d2h_bytes_per_step": 8 * batch,
+                "ms_per_step": e2e_ms / args.steps},
+        "gpu_launches": launches * args.steps,
+        "roofline": {"bound": "hbm", "kernel": "linear_small_kernel (all skinny-linear launches of one step)",
+                     "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak if achieved else None,
+                     "peak_kind": peak_kind, "traffic": None,
+                     "algorithmic_bytes": linear_bytes, "launch_ms": profile["linear_ms"]},
+    }
+    if rank == 0 and world == 1 and not args.no_cpu:
+        cpu = cpu_reference(spec, weights, args.cpu_steps, 1)
+        line["cpu_baseline"] = {k: cpu[k] for k in ("value", "unit", "cores", "kind", "sample")}
+    if dist is not None:
+        dist.destroy_process_group()
+    return line if rank == 0 else {}
+
+
+def main():
+    parser = argparse.ArgumentParser()
+    parser.add_argument("--gpus", type=int, default=1)
+    parser.add_argument("--steps", type=int, default=64)
+    parser.add_argument("--warmup", type=int, default=8)
+    parser.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    parser.add_argument("--workload", default="c2", choices=["c1", "c2", "c4"])
+    parser.add_argument("--cpu-steps", type=int, default=24, help="timed CPU-baseline steps of the default run")
+    parser.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    args = parser.parse_args()
+    if args.warmup < 3:
+        args.warmup = 3
+    spec = dict(W.CONFIGS[args.workload])
+    weights = W.make_weights(spec)
+    line = run_reference(args, spec, weights) if args.impl == "reference" else run_b200(args, spec, weights)
+    if line:
+        print(json.dumps(line))
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,509 @@
+// Fixed execution plan and device-resident greedy generation (see plan.h).
+#include "dl/plan.h"
+#include "dl/internal.h"
+
+#include <algorithm>
+#include <stdexcept>
+
+namespace dl::nn {
+
+namespace {
+
+// Optional per-launch event trail (Generation::profile_step); kinds: 0 linear, 1 attention, 2 other.
+struct StepProbe {
+    cudaStream_t stream;
+    std::vector<cudaEvent_t> events;
+    std::vector<int> kinds;
+    void mark(int kind) {
+        cudaEvent_t event;
+        runtime::check_cuda(cudaEventCreate(&event), "cudaEventCreate");
+        runtime::check_cuda(cudaEventRecord(event, stream), "cudaEventRecord");
+        events.push_back(event);
+        kinds.push_back(kind);
+    }
+};
+thread_local StepProbe* step_probe = nullptr;
+void probe(int kind) { if (step_probe) step_probe->mark(kind); }
+
+int code_of(DType dtype) { return dtype == DType::bf16 ? B200_BF16 : B200_F32; }
+
+cudaStream_t cuda_stream(int device) { return static_cast<cudaStream_t>(runtime::stream(device)); }
+
+void require_cuda(const Tensor& t, const char* what) {
+    if (t.device().type != DeviceType::cuda)
+        throw std::invalid_argument(std::string(what) + ": tensors must live on a CUDA device (this library has no CPU compute path)");
+}
+
+// Device-side row copy: dst rows [first, first+n) of a [*, width] matrix with `pitch` bytes per destination row.
+void copy_rows(void* dst, std::size_t dst_pitch, const Tensor& src, int device) {
+    const std::size_t row = static_cast<std::size_t>(src.size(1)) * element_size(src.dtype());
+    runtime::check_cuda(cudaMemcpy2DAsync(dst, dst_pitch, src.raw_data(), row, row, static_cast<std::size_t>(src.size(0)),
+                                          cudaMemcpyDeviceToDevice, cuda_stream(device)), "cudaMemcpy2DAsync");
+}
+
+}  // namespace
+
+Tensor interleave_rows(const Tensor& even_rows, const Tensor& odd_rows) {
+    require_cuda(even_rows, "interleave_rows");
+    if (even_rows.shape() != odd_rows.shape() || even_rows.dtype() != odd_rows.dtype() || even_rows.ndim() != 2)
+        throw std::invalid_argument("interleave_rows: matrices must match");
+    const int device = even_rows.device().index;
+    runtime::set_device(device);
+    Tensor result = empty({2 * even_rows.size(0), even_rows.size(1)}, {even_rows.dtype(), even_rows.device()});
+    const std::size_t row = static_cast<std::size_t>(even_rows.size(1)) * element_size(even_rows.dtype());
+    copy_rows(result.mutable_data(), 2 * row, even_rows, device);
+    copy_rows(static_cast<char*>(result.mutable_data()) + row, 2 * row, odd_rows, device);
+    return result;
+}
+
+Tensor concat_rows(std::span<const Tensor> parts) {
+    Index rows = 0;
+    for (const auto& part : parts) {
+        require_cuda(part, "concat_rows");
+        if (part.ndim() != 2 || part.size(1) != parts.front().size(1) || part.dtype() != parts.front().dtype())
+            throw std::invalid_argument("concat_rows: matrices must share width and dtype");
+        rows += part.size(0);
+    }
+    const int device = parts.front().device().index;
+    runtime::set_device(device);
+    Tensor result = empty({rows, parts.front().size(1)}, {parts.front().dtype(), parts.front().device()});
+    std::size_t offset = 0;
+    for (const auto& part : parts) {
+        runtime::check_cuda(cudaMemcpyAsync(static_cast<char*>(result.mutable_data()) + offset, part.raw_data(), part.nbytes(),
+                                            cudaMemcpyDeviceToDevice, cuda_stream(device)), "cudaMemcpyAsync");
+        offset += part.nbytes();
+    }
+    return result;
+}
+
+Tensor add(const Tensor& a, const Tensor& b) {
+    require_cuda(a, "add");
+    if (a.shape() != b.shape() || a.device() != b.device()) throw std::invalid_argument("add: shapes and devices must match");
+    Tensor result = (a.dtype() == DType::f32 ? a : a.astype(DType::f32)).clone();
+    const Tensor other = b.dtype() == DType::f32 ? b : b.astype(DType::f32);
+    runtime::check(b200_scaled_add(static_cast<float*>(result.mutable_data()), other.data<float>(), 1.0f, result.numel(),
+                                   runtime::stream(a.device().index)), "add");
+    return result;
+}
+
+namespace {
+
+struct AttentionWeights {
+    Tensor wqkv, lora_down;
+    const void *q_up = nullptr, *v_up = nullptr;
+    int rank = 0;
+    float scale = 0.0f;
+};
+
+AttentionWeights pack_attention(const GroupedQueryAttention& a) {
+    AttentionWeights w;
+    const auto* qa = a.query_adapter();
+    const auto* va = a.value_adapter();
+    const Tensor parts[3] = {qa ? qa->weight() : a.query().weight(), a.key().weight(), va ? va->weight() : a.value().weight()};
+    w.wqkv = concat_rows(parts);
+    if (qa) {
+        const Tensor downs[2] = {qa->down().weight(), va->down().weight()};
+        w.lora_down = concat_rows(downs);
+        w.q_up = qa->up().weight().raw_data();
+        w.v_up = va->up().weight().raw_data();
+        w.rank = static_cast<int>(qa->rank());
+        w.scale = static_cast<float>(qa->scale());
+        if (static_cast<float>(va->scale()) != w.scale) throw std::invalid_argument("query and value adapters must share alpha/rank");
+    }
+    return w;
+}
+
+// RMSNorm? + QKV + RoPE + append, attention, output projection.  `norm` may be null.  y = residual + o-proj when
+// residual != nullptr, else y = o-proj.
+void enqueue_attention(const GroupedQueryAttention& a, const AttentionWeights& w, const float* x, const Tensor* norm, double eps,
+                       Index batch, Index length, KVCache& cache, Index max_length, float* q, float* attended, float* low,
+                       void* scratch, std::size_t scratch_bytes, const float* residual, float* y, int device, void* stream) {
+    const Index D = a.dimensions(), H = a.heads(), HK = a.kv_heads(), hd = D / H, rows = batch * length;
+    const int wcode = code_of(a.key().weight().dtype());
+    b200_kv_cache* kv = cache.ensure(device, batch, HK, hd);
+    b200_qkv_args args{};
+    args.heads = static_cast<int32_t>(H); args.kv_heads = static_cast<int32_t>(HK); args.head_dim = static_cast<int32_t>(hd);
+    args.tokens_per_sequence = static_cast<int32_t>(length);
+    args.cosine = a.rotary().cosine().data<float>(); args.sine = a.rotary().sine().data<float>();
+    args.context = static_cast<int32_t>(a.rotary().cosine().size(0));
+    args.cache = kv; args.q_out = q;
+    const void* norm_w = norm ? norm->raw_data() : nullptr;
+    const int norm_code = norm ? code_of(norm->dtype()) : B200_F32;
+    if (w.rank > 0) {
+        runtime::check(b200_linear(x, rows, D, w.lora_down.raw_data(), wcode, 2 * w.rank, norm_w, norm_code, eps, B200_EPI_STORE,
+                                   nullptr, nullptr, low, stream), "adapter down-projection");
+        probe(0);
+        args.lora_rank = w.rank; args.lora_scale = w.scale; args.low = low; args.q_up = w.q_up; args.v_up = w.v_up;
+    }
+    runtime::check(b200_linear(x, rows, D, w.wqkv.raw_data(), wcode, D + 2 * HK * hd, norm_w, norm_code, eps, B200_EPI_QKV, nullptr,
+                               &args, q, stream), "q/k/v projection");
+    probe(0);
+    runtime::check(b200_attention_decode(q, rows, static_cast<int32_t>(length), static_cast<int32_t>(H), kv,
+                                         static_cast<int32_t>(max_length), 1, scratch, scratch_bytes, attended, stream), "attention");
+    probe(1);
+    runtime::check(b200_linear(attended, rows, D, a.output().weight().raw_data(), code_of(a.output().weight().dtype()), D, nullptr, 0,
+                               0.0, residual ? B200_EPI_RESIDUAL : B200_EPI_STORE, residual, nullptr, y, stream), "output projection");
+    probe(0);
+}
+
+}  // namespace
+
+Tensor attention_block(GroupedQueryAttention& a, const Tensor& input, KVCache& cache) {
+    require_cuda(input, "GroupedQueryAttention");
+    if (input.ndim() != 3 || input.size(2) != a.dimensions()) throw std::invalid_argument("attention expects [batch,length,dimensions]");
+    const Index batch = input.size(0), length = input.size(1), D = a.dimensions(), rows = batch * length;
+    if (length > cache.capacity() - cache.length())
+        throw std::invalid_argument("KV cache append exceeds capacity or has unequal key/value lengths");
+    if (length > a.rotary().cosine().size(0) - cache.length()) throw std::out_of_range("RoPE positions exceed the table capacity");
+    const int device = input.device().index;
+    runtime::set_device(device);
+    void* stream = runtime::stream(device);
+    const Tensor x = input.dtype() == DType::f32 ? input : input.astype(DType::f32);
+    const AttentionWeights w = pack_attention(a);
+    const TensorOptions f32{DType::f32, input.device()};
+    Tensor q = empty({rows, D}, f32), attended = empty({rows, D}, f32), y = empty({batch, length, D}, f32);
+    Tensor low = empty({rows, std::max<Index>(1, 2 * w.rank)}, f32);
+    const Index max_length = cache.length() + length;
+    const std::size_t scratch_bytes = b200_attention_scratch_bytes(rows, static_cast<int32_t>(a.heads()), static_cast<int32_t>(a.kv_heads()),
+                                                                   static_cast<int32_t>(D / a.heads()), static_cast<int32_t>(max_length), 64);
+    Tensor scratch = empty({static_cast<Index>(scratch_bytes / 4 + 1)}, f32);
+    enqueue_attention(a, w, x.data<float>(), nullptr, 0.0, batch, length, cache, max_length, static_cast<float*>(q.mutable_data()),
+                      static_cast<float*>(attended.mutable_data()), static_cast<float*>(low.mutable_data()), scratch.mutable_data(),
+                      scratch_bytes, nullptr, static_cast<float*>(y.mutable_data()), device, stream);
+    b200_kv_cache* handle = cache.handle();
+    runtime::check(b200_kv_cache_advance(&handle, 1, static_cast<int32_t>(length), stream), "KV advance");
+    cache.commit(length);
+    synchronize(input.device());  // temporaries above are released on return
+    return y;
+}
+
+// ---- DecodePlan -----------------------------------------------------------------------------------------
+DecodePlan::DecodePlan(TransformerDecoder& owner) : owner_(owner) {}
+DecodePlan::~DecodePlan() = default;
+
+void DecodePlan::refresh() {
+    const auto version = owner_.version();
+    if (version == packed_version_ && !layers_.empty()) return;
+    const Tensor& probe = owner_.normalization().weight() ? *owner_.normalization().weight() : owner_.layer(0).attention().key().weight();
+    require_cuda(probe, "TransformerDecoder");
+    runtime::set_device(probe.device().index);
+    layers_.clear();
+    for (Index i = 0; i < owner_.layer_count(); ++i) {
+        auto& layer = owner_.layer(i);
+        const AttentionWeights a = pack_attention(layer.attention());
+        Layer packed{};
+        packed.wqkv = a.wqkv; packed.lora_down = a.lora_down; packed.q_up = a.q_up; packed.v_up = a.v_up;
+        packed.rank = a.rank; packed.scale = a.scale;
+        packed.wgu = interleave_rows(layer.feedforward().gate().weight(), layer.feedforward().up().weight());
+        packed.wo = layer.attention().output().weight().raw_data();
+        packed.wd = layer.feedforward().down().weight().raw_data();
+        packed.norm1 = layer.attention_norm().weight()->raw_data();
+        packed.norm2 = layer.feedforward_norm().weight()->raw_data();
+        layers_.push_back(std::move(packed));
+    }
+    synchronize(probe.device());
+    packed_version_ = version;
+}
+
+void DecodePlan::reserve(Index rows, Index max_length, int device) {
+    const Index D = owner_.dimensions(), F = owner_.hidden();
+    const std::size_t need = b200_attention_scratch_bytes(rows, static_cast<int32_t>(owner_.heads()), static_cast<int32_t>(owner_.kv_heads()),
+                                                          static_cast<int32_t>(D / owner_.heads()), static_cast<int32_t>(max_length), 64);
+    const TensorOptions f32{DType::f32, Device::cuda(device)};
+    if (rows > reserved_rows_ || !h_.defined() || h_.device().index != device) {
+        synchronize(Device::cuda(device));
+        int max_rank = 0;
+        for (const auto& layer : layers_) max_rank = std::max(max_rank, layer.rank);
+        h_ = empty({rows, D}, f32); q_ = empty({rows, D}, f32); attended_ = empty({rows, D}, f32);
+        activated_ = empty({rows, F}, f32); low_ = empty({rows, std::max(1, 2 * max_rank)}, f32);
+        reserved_rows_ = rows;
+        ++buffer_epoch_;
+    }
+    if (need > scratch_bytes_ || !scratch_.defined() || scratch_.device().index != device) {
+        synchronize(Device::cuda(device));
+        scratch_ = empty({static_cast<Index>(need / 4 + 1)}, f32);
+        scratch_bytes_ = need;
+        ++buffer_epoch_;
+    }
+}
+
+void DecodePlan::validate(Index batch, Index length, std::span<KVCache> cache, int device) {
+    if (static_cast<Index>(cache.size()) != owner_.layer_count()) throw std::invalid_argument("decoder requires one cache per layer");
+    const Index prefix = cache.front().length();
+    for (const auto& layer : cache)
+        if (layer.length() != prefix) throw std::invalid_argument("decoder cache positions differ");
+    // Everything that can fail is checked before the first kernel is enqueued, so a rejected chunk leaves every
+    // layer at the prefix it had (the reference reaches the same state by truncating after the throw,
+    // src/nn/decoder.cpp:137-141).
+    for (const auto& layer : cache)
+        if (length > layer.capacity() - layer.length())
+            throw std::invalid_argument("KV cache append exceeds capacity or has unequal key/value lengths");
+    if (length > owner_.context() - prefix) throw std::out_of_range("RoPE positions exceed the table capacity");
+    const Index hd = owner_.dimensions() / owner_.heads();
+    for (auto& layer : cache) layer.ensure(device, batch, owner_.kv_heads(), hd);
+}
+
+void DecodePlan::run_layers(const float* x, Index batch, Index length, std::span<KVCache> cache, Index max_length, void* stream) {
+    const Index D = owner_.dimensions(), F = owner_.hidden(), rows = batch * length;
+    const int device = h_.device().index;
+    const double eps = TransformerDecoderLayer::norm_epsilon;
+    float* h = hidden();
+    auto* act = static_cast<float*>(activated_.mutable_data());
+    for (Index i = 0; i < owner_.layer_count(); ++i) {
+        auto& layer = owner_.layer(i);
+        const Layer& packed = layers_[static_cast<std::size_t>(i)];
+        const float* in = i == 0 ? x : h;
+        AttentionWeights w;
+        w.wqkv = packed.wqkv; w.lora_down = packed.lora_down; w.q_up = packed.q_up; w.v_up = packed.v_up; w.rank = packed.rank; w.scale = packed.scale;
+        enqueue_attention(layer.attention(), w, in, layer.attention_norm().weight(), eps, batch, length, cache[static_cast<std::size_t>(i)],
+                          max_length, static_cast<float*>(q_.mutable_data()), static_cast<float*>(attended_.mutable_data()),
+                          static_cast<float*>(low_.mutable_data()), scratch_.mutable_data(), scratch_bytes_, in, h, device, stream);
+        const int wcode = code_of(layer.feedforward().gate().weight().dtype());
+        runtime::check(b200_linear(h, rows, D, packed.wgu.raw_data(), wcode, 2 * F, packed.norm2, code_of(layer.feedforward_norm().weight()->dtype()),
+                                   eps, B200_EPI_SWIGLU, nullptr, nullptr, act, stream), "gate/up projection");
+        probe(0);
+        runtime::check(b200_linear(act, rows, F, packed.wd, wcode, D, nullptr, 0, 0.0, B200_EPI_RESIDUAL, h, nullptr, h, stream),
+                       "down projection");
+        probe(0);
+    }
+}
+
+Tensor DecodePlan::decode(const Tensor& input, std::span<KVCache> cache) {
+    require_cuda(input, "TransformerDecoder::decode");
+    if (input.ndim() != 3 || input.size(2) != owner_.dimensions())
+        throw std::invalid_argument("decoder expects [batch,length,dimensions]");
+    const Index batch = input.size(0), length = input.size(1), rows = batch * length;
+    const int device = input.device().index;
+    runtime::set_device(device);
+    refresh();
+    validate(batch, length, cache, device);
+    Tensor result = empty(input.shape(), {DType::f32, input.device()});
+    if (rows == 0) return result;
+    const Tensor x = input.dtype() == DType::f32 ? input : input.astype(DType::f32);
+    const Index max_length = cache.front().length() + length;
+    reserve(rows, max_length, device);
+    void* stream = runtime::stream(device);
+    run_layers(x.data<float>(), batch, length, cache, max_length, stream);
+    const Tensor* norm = owner_.normalization().weight();
+    runtime::check(b200_rms_norm(hidden(), norm->raw_data(), code_of(norm->dtype()), rows, owner_.dimensions(),
+                                 owner_.normalization().epsilon(), static_cast<float*>(result.mutable_data()), stream), "final norm");
+    std::vector<b200_kv_cache*> handles;
+    for (auto& layer : cache) handles.push_back(layer.handle());
+    runtime::check(b200_kv_cache_advance(handles.data(), static_cast<int32_t>(handles.size()), static_cast<int32_t>(length), stream), "KV advance");
+    for (auto& layer : cache) layer.commit(length);
+    synchronize(input.device());  // `x` may be a temporary; results are complete when the call returns
+    return result;
+}
+
+// ---- Generation -----------------------------------------------------------------------------------------
+Generation::Generation(std::shared_ptr<TransformerDecoder> decoder, std::shared_ptr<Embedding> tokens, std::shared_ptr<Linear> output,
+                       std::vector<KVCache>* cache, Index batch, Index max_steps)
+    : decoder_(std::move(decoder)), tokens_(std::move(tokens)), output_(std::move(output)), cache_(cache), batch_(batch),
+      max_steps_(max_steps) {
+    if (!decoder_ || !tokens_ || !output_ || !cache_) throw std::invalid_argument("generation needs a decoder, an embedding, an output layer and a cache");
+    if (batch <= 0 || max_steps <= 0) throw std::invalid_argument("generation needs a positive batch and step budget");
+    require_cuda(tokens_->weight(), "generation");
+    if (tokens_->weight().size(1) != decoder_->dimensions() || output_->weight().size(1) != decoder_->dimensions())
+        throw std::invalid_argument("embedding and output widths must equal the decoder's dimensions");
+    device_ = tokens_->weight().device().index;
+    runtime::set_device(device_);
+    const Device where = Device::cuda(device_);
+    ids_ = zeros({batch}, {DType::i64, where});
+    next_ = zeros({batch}, {DType::i64, where});
+    logits_ = empty({batch, output_->weight().size(0)}, {DType::f32, where});
+    history_ = zeros({max_steps, batch}, {DType::i64, where});
+    counter_ = zeros({1}, {DType::i64, where});  // the kernel uses the first 32 bits
+    x_ = empty({batch, decoder_->dimensions()}, {DType::f32, where});
+    pinned_ = std::make_shared<runtime::Storage>(sizeof(Index) * static_cast<std::size_t>(batch) * 2, Device::cpu(), true);
+}
+Generation::~Generation() {
+    try { synchronize(Device::cuda(device_)); } catch (...) {}
+    if (graph_) cudaGraphExecDestroy(graph_);
+}
+
+// logits of `rows` hidden rows (final RMSNorm fused into the projection), argmax, token feedback
+static void enqueue_head(TransformerDecoder& decoder, const Linear& output, const float* hidden, Index batch, float* logits,
+                         Index* next, Index* ids, Index* history, Index history_rows, int32_t* counter, void* stream) {
+    const Tensor* norm = decoder.normalization().weight();
+    const Index V = output.weight().size(0), D = decoder.dimensions();
+    runtime::check(b200_linear(hidden, batch, D, output.weight().raw_data(), code_of(output.weight().dtype()), V, norm->raw_data(),
+                               code_of(norm->dtype()), decoder.normalization().epsilon(), B200_EPI_STORE, nullptr, nullptr, logits, stream),
+                   "logits");
+    probe(0);
+    runtime::check(b200_argmax(logits, batch, V, next, stream), "argmax");
+    runtime::check(b200_token_feedback(next, batch, ids, history, history_rows, counter, stream), "token feedback");
+    probe(2);
+}
+
+void Generation::prefill(const Tensor& prompt) {
+    if (prompt.ndim() != 2 || prompt.size(0) != batch_ || prompt.dtype() != DType::i64 || prompt.size(1) <= 0)
+        throw std::invalid_argument("prompt must be int64 [batch, length] with a positive length");
+    const Index P = prompt.size(1), D = decoder_->dimensions();
+    runtime::set_device(device_);
+    void* stream = runtime::stream(device_);
+    if (prompt.device().type == DeviceType::cpu) {
+        const Index V = tokens_->weight().size(0);
+        for (Index i = 0; i < prompt.numel(); ++i)
+            if (prompt.data<Index>()[i] < 0 || prompt.data<Index>()[i] >= V) throw std::out_of_range("embedding index out of range");
+    }
+    const Tensor device_prompt = prompt.to(Device::cuda(device_));
+    auto& plan = decoder_->plan();
+    plan.refresh();
+    plan.validate(batch_, P, *cache_, device_);
+    if (generated_ >= max_steps_) throw std::out_of_range("generation step budget exhausted");
+    // Chunked prefill: at most ~8192 rows per pass; chunked decode equals one pass (tests/state.cpp:54-63 of the reference).
+    const Index chunk = std::max<Index>(1, std::min<Index>(P, 8192 / batch_ > 0 ? 8192 / batch_ : 1));
+    Tensor features = empty({batch_ * chunk, D}, {DType::f32, Device::cuda(device_)});
+    Index done = 0;
+    while (done < P) {
+        const Index count = std::min(chunk, P - done);
+        const Tensor part = count == P ? device_prompt : device_prompt.narrow(1, done, count);
+        runtime::check(b200_embedding(tokens_->weight().raw_data(), code_of(tokens_->weight().dtype()), part.data<Index>(), batch_ * count,
+                                      tokens_->weight().size(0), D, static_cast<float*>(features.mutable_data()), stream), "embedding");
+        const Index max_length = cache_->front().length() + count;
+        plan.reserve(batch_ * count, max_length, device_);
+        plan.run_layers(features.data<float>(), batch_, count, *cache_, max_length, stream);
+        std::vector<b200_kv_cache*> handles;
+        for (auto& layer : *cache_) handles.push_back(layer.handle());
+        runtime::check(b200_kv_cache_advance(handles.data(), static_cast<int32_t>(handles.size()), static_cast<int32_t>(count), stream), "KV advance");
+        for (auto& layer : *cache_) layer.commit(count);
+        done += count;
+        if (done == P) {
+            // last position of every sequence -> first generated token
+            runtime::check(b200_select_rows(plan.hidden(), count - 1, count, batch_, D, static_cast<float*>(x_.mutable_data()), stream), "select");
+            enqueue_head(*decoder_, *output_, x_.data<float>(), batch_, static_cast<float*>(logits_.mutable_data()),
+                         static_cast<Index*>(next_.mutable_data()), static_cast<Index*>(ids_.mutable_data()),
+                         static_cast<Index*>(history_.mutable_data()), max_steps_, static_cast<int32_t*>(counter_.mutable_data()), stream);
+        }
+        synchronize(Device::cuda(device_));  // `part` and the chunk buffers are reused
+    }
+    ++generated_;
+}
+
+void Generation::enqueue_step(void* stream, Index max_length) {
+    auto& plan = decoder_->plan();
+    const Index D = decoder_->dimensions();
+    runtime::check(b200_embedding(tokens_->weight().raw_data(), code_of(tokens_->weight().dtype()), ids_.data<Index>(), batch_,
+                                  tokens_->weight().size(0), D, static_cast<float*>(x_.mutable_data()), stream), "embedding");
+    plan.run_layers(x_.data<float>(), batch_, 1, *cache_, max_length, stream);
+    std::vector<b200_kv_cache*> handles;
+    for (auto& layer : *cache_) handles.push_back(layer.handle());
+    runtime::check(b200_kv_cache_advance(handles.data(), static_cast<int32_t>(handles.size()), 1, stream), "KV advance");
+    probe(2);
+    enqueue_head(*decoder_, *output_, plan.hidden(), batch_, static_cast<float*>(logits_.mutable_data()),
+                 static_cast<Index*>(next_.mutable_data()), static_cast<Index*>(ids_.mutable_data()),
+                 static_cast<Index*>(history_.mutable_data()), max_steps_, static_cast<int32_t*>(counter_.mutable_data()), stream);
+}
+
+void Generation::capture() {
+    auto& plan = decoder_->plan();
+    plan.refresh();
+    const std::uint64_t version = decoder_->version() + tokens_->version() + output_->version();
+    runtime::set_device(device_);
+    const Index capacity = cache_->front().capacity();
+    plan.reserve(batch_, capacity, device_);
+    if (graph_ && graph_version_ == version && graph_epoch_ == plan.buffer_epoch()) return;
+    if (graph_) { cudaGraphExecDestroy(graph_); graph_ = nullptr; }
+    cudaStream_t stream = cuda_stream(device_);
+    runtime::check_cuda(cudaStreamSynchronize(stream), "cudaStreamSynchronize");
+    runtime::check_cuda(cudaStreamBeginCapture(stream, cudaStreamCaptureModeThreadLocal), "cudaStreamBeginCapture");
+    cudaGraph_t graph = nullptr;
+    try {
+        enqueue_step(stream, capacity);
+    } catch (...) {
+        cudaStreamEndCapture(stream, &graph);
+        if (graph) cudaGraphDestroy(graph);
+        throw;
+    }
+    runtime::check_cuda(cudaStreamEndCapture(stream, &graph), "cudaStreamEndCapture");
+    std::size_t nodes = 0;
+    cudaGraphGetNodes(graph, nullptr, &nodes);
+    launches_per_step_ = static_cast<Index>(nodes);
+    const auto status = cudaGraphInstantiate(&graph_, graph, 0);
+    cudaGraphDestroy(graph);
+    runtime::check_cuda(status, "cudaGraphInstantiate");
+    graph_version_ = version;
+    graph_epoch_ = plan.buffer_epoch();
+}
+
+void Generation::step(Index steps) {
+    if (steps < 0) throw std::invalid_argument("negative step count");
+    if (generated_ == 0) throw std::logic_error("prefill a prompt before stepping");
+    if (generated_ + steps > max_steps_) throw std::out_of_range("generation step budget exhausted");
+    runtime::set_device(device_);
+    decoder_->plan().refresh();
+    decoder_->plan().validate(batch_, steps, *cache_, device_);  // capacity for all `steps` single-token appends
+    capture();
+    cudaStream_t stream = cuda_stream(device_);
+    for (Index i = 0; i < steps; ++i) runtime::check_cuda(cudaGraphLaunch(graph_, stream), "cudaGraphLaunch");
+    for (auto& layer : *cache_) layer.commit(steps);
+    generated_ += steps;
+}
+
+void Generation::step_host(const Index* ids_in, Index* ids_out) {
+    runtime::set_device(device_);
+    cudaStream_t stream = cuda_stream(device_);
+    auto* staging = static_cast<Index*>(pinned_->data);
+    if (ids_in) {
+        const Index V = tokens_->weight().size(0);
+        for (Index b = 0; b < batch_; ++b) {
+            if (ids_in[b] < 0 || ids_in[b] >= V) throw std::out_of_range("embedding index out of range");
+            staging[b] = ids_in[b];
+        }
+        runtime::check_cuda(cudaMemcpyAsync(ids_.mutable_data(), staging, sizeof(Index) * static_cast<std::size_t>(batch_),
+                                            cudaMemcpyHostToDevice, stream), "cudaMemcpyAsync");
+        if (generated_ == 0) generated_ = 1;  // the caller supplied the first token itself
+    }
+    step(1);
+    runtime::check_cuda(cudaMemcpyAsync(staging + batch_, next_.raw_data(), sizeof(Index) * static_cast<std::size_t>(batch_),
+                                        cudaMemcpyDeviceToHost, stream), "cudaMemcpyAsync");
+    runtime::check_cuda(cudaStreamSynchronize(stream), "cudaStreamSynchronize");
+    if (ids_out) std::copy(staging + batch_, staging + 2 * batch_, ids_out);
+}
+
+Generation::StepProfile Generation::profile_step() {
+    if (generated_ == 0) throw std::logic_error("prefill a prompt before stepping");
+    if (generated_ + 1 > max_steps_) throw std::out_of_range("generation step budget exhausted");
+    runtime::set_device(device_);
+    auto& plan = decoder_->plan();
+    plan.refresh();
+    plan.validate(batch_, 1, *cache_, device_);
+    plan.reserve(batch_, cache_->front().capacity(), device_);
+    cudaStream_t stream = cuda_stream(device_);
+    runtime::check_cuda(cudaStreamSynchronize(stream), "cudaStreamSynchronize");
+    StepProbe trail{stream, {}, {}};
+    trail.mark(2);
+    step_probe = &trail;
+    try {
+        enqueue_step(stream, cache_->front().capacity());
+    } catch (...) {
+        step_probe = nullptr;
+        throw;
+    }
+    step_probe = nullptr;
+    runtime::check_cuda(cudaStreamSynchronize(stream), "cudaStreamSynchronize");
+    for (auto& layer : *cache_) layer.commit(1);
+    ++generated_;
+    StepProfile result{0.0, 0.0, 0.0, static_cast<Index>(trail.events.size()) - 1};
+    for (std::size_t i = 1; i < trail.events.size(); ++i) {
+        float ms = 0.0f;
+        cudaEventElapsedTime(&ms, trail.events[i - 1], trail.events[i]);
+        (trail.kinds[i] == 0 ? result.linear_ms : trail.kinds[i] == 1 ? result.attention_ms : result.other_ms) += ms;
+    }
+    for (auto event : trail.events) cudaEventDestroy(event);
+    return result;
+}
+
+Tensor Generation::tokens() const {
+    synchronize(Device::cuda(device_));
+    // history is [step, batch]; the caller-facing layout is [batch, step]
+    const Tensor host = history_.narrow(0, 0, generated_).to(Device::cpu());
+    Tensor result = empty({batch_, generated_}, {DType::i64, Device::cpu()});
+    for (Index s = 0; s < generated_; ++s)
+        for (Index b = 0; b < batch_; ++b)
+            static_cast<Index*>(result.mutable_data())[b * generated_ + s] = host.data<Index>()[s * batch_ + b];
+    return result;
+}
+Tensor Generation::last_logits() const { return logits_; }
+
+}  // namespace dl::nn

@@ -1,0 +1,92 @@
+// Fixed execution plan of the decoder token loop and the device-resident greedy generation built on it.
+//
+// The reference walks Module::forward op by op (src/nn/decoder.cpp:77-142: ~35 launches per layer and token, every
+// intermediate freshly allocated).  The plan instead owns packed weights (q|k|v rows concatenated, gate/up rows
+// interleaved), persistent workspaces and a fixed kernel sequence per layer:
+//     [adapter down-projection]  ->  RMSNorm + QKV + RoPE + KV append  ->  split-K attention (+ combine)
+//     ->  o-projection + residual  ->  RMSNorm + gate/up + SiLU*up  ->  down-projection + residual
+// For single-token steps the whole token loop body (embedding ... argmax, token feedback, cache length advance)
+// is captured once into a CUDA graph and replayed.
+#pragma once
+
+#include "dl/dl.h"
+
+#include <cuda_runtime.h>
+
+namespace dl::nn {
+
+Tensor interleave_rows(const Tensor& even_rows, const Tensor& odd_rows);  // [n,k],[n,k] -> [2n,k]
+Tensor concat_rows(std::span<const Tensor> parts);                          // [n_i,k] -> [sum n_i,k]
+Tensor add(const Tensor& a, const Tensor& b);                               // f32 CUDA tensors of one shape
+Tensor attention_block(GroupedQueryAttention& attention, const Tensor& input, KVCache& cache);
+
+class DecodePlan {
+public:
+    explicit DecodePlan(TransformerDecoder& owner);
+    ~DecodePlan();
+
+    // TransformerDecoder::decode: features [batch, length, D] -> normalised features, caches advanced by `length`.
+    Tensor decode(const Tensor& input, std::span<KVCache> cache);
+
+    // Pieces used by Generation.  `x` holds rows = batch*length feature rows; the residual stream ends in hidden().
+    void validate(Index batch, Index length, std::span<KVCache> cache, int device);
+    void run_layers(const float* x, Index batch, Index length, std::span<KVCache> cache, Index max_length, void* stream);
+    void reserve(Index rows, Index max_length, int device);
+    float* hidden() const { return static_cast<float*>(h_.mutable_data()); }
+    void refresh();  // re-pack weights when the owner's parameters moved
+    std::uint64_t buffer_epoch() const { return buffer_epoch_; }  // moves when a workspace was reallocated
+
+private:
+    struct Layer {
+        Tensor wqkv, wgu, lora_down;
+        const void *wo, *wd, *norm1, *norm2, *q_up, *v_up;
+        int rank;
+        float scale;
+    };
+    TransformerDecoder& owner_;
+    std::vector<Layer> layers_;
+    std::uint64_t packed_version_ = ~0ull;
+    Index reserved_rows_ = 0;
+    std::size_t scratch_bytes_ = 0;
+    std::uint64_t buffer_epoch_ = 0;
+    Tensor h_, q_, attended_, activated_, low_, scratch_;
+};
+
+// Greedy generation with the token loop resident on the device (the loop of examples/decoder_generate.cpp:20-31).
+class Generation {
+public:
+    Generation(std::shared_ptr<TransformerDecoder> decoder, std::shared_ptr<Embedding> tokens, std::shared_ptr<Linear> output,
+               std::vector<KVCache>* cache, Index batch, Index max_steps);
+    ~Generation();
+    // Prefill the prompt [batch, P] (int64, host or device) in chunks and choose the first token.
+    void prefill(const Tensor& prompt);
+    // Enqueue `steps` single-token steps (graph replays); no host synchronisation.
+    void step(Index steps);
+    // One step driven from the host: ids_in [batch] host -> H2D, step, D2H -> ids_out [batch] host (the reference's
+    // per-token host round trip, examples/decoder_generate.cpp:28-30).  ids_in may be NULL to continue from the device ids.
+    void step_host(const Index* ids_in, Index* ids_out);
+    Index generated() const { return generated_; }
+    Tensor tokens() const;         // [batch, generated] int64 on the host (synchronises)
+    Tensor last_logits() const;    // [batch, vocab] f32 on the device: logits the latest token was chosen from
+    Index launches_per_step() const { return launches_per_step_; }
+    // One real step run eagerly with a CUDA event after every launch: milliseconds spent in the skinny-linear
+    // launches, in the attention launches and in everything else, and the number of launches.
+    struct StepProfile { double linear_ms, attention_ms, other_ms; Index launches; };
+    StepProfile profile_step();
+
+private:
+    void enqueue_step(void* stream, Index max_length);
+    void capture();
+    std::shared_ptr<TransformerDecoder> decoder_;
+    std::shared_ptr<Embedding> tokens_;
+    std::shared_ptr<Linear> output_;
+    std::vector<KVCache>* cache_;
+    Index batch_, max_steps_, generated_ = 0, launches_per_step_ = 0;
+    int device_ = 0;
+    Tensor ids_, next_, logits_, history_, counter_, x_;
+    std::shared_ptr<runtime::Storage> pinned_;
+    cudaGraphExec_t graph_ = nullptr;
+    std::uint64_t graph_version_ = ~0ull, graph_epoch_ = ~0ull;
+};
+
+}  // namespace dl::nn

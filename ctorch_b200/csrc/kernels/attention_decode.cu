@@ -1,0 +1,462 @@
+// Split-K flash-decode grouped-query attention over the paged KV cache.
+//
+// Work item = (query row, KV head): the G = heads / kv_heads query heads that share a KV head are processed
+// together, so every K/V byte is read once per item.  The key range of an item is cut into splits of
+// `pages_per_split` pages (grid.y); each CTA produces a partial (max, sum, accumulator) triple per head in the
+// caller's scratch buffer and a second small kernel merges the splits.  The work is KV streaming (HBM-bound).
+//
+// Fast path (bf16 pools, 64-token pages, head_dim 64 or 128): a producer warp stages K and V pages with
+// non-multicast TMA (cp.async.bulk.tensor, 128-byte swizzle) through a ring of shared-memory stages guarded by
+// mbarriers; four consumer warps take 16 tokens of each page, compute Q.K^T and P.V with bf16 mma.sync
+// (m16n8k16, f32 accumulation, fragments fetched with ldmatrix from the swizzled tiles), keep an online softmax
+// per row, reduce row maxima and sums with quad shuffles and merge through shared memory.
+//
+// Generic path (f32 pools, other head sizes or page sizes): one (row, head) per CTA with plain loads and f32
+// FMAs -- this is the path the f32 parity configuration runs on.
+//
+// Reference semantics: src/ops/attention.cpp:65-95 (scores * f32(1/sqrt(hd)), softmax, P.V) with the causal rule
+// key_pos <= query_pos (src/ops/attention.cpp:52-57) expressed as a per-row key count.
+#include "common.cuh"
+#include "kv_cache.cuh"
+
+#include <cmath>
+
+namespace b200 {
+namespace {
+
+struct AttnParams {
+    const float* q;    // [rows, heads, head_dim]
+    int rows, tokens_per_sequence, heads, causal;
+    KvView kv;
+    int pages_per_split, num_splits;
+    float* part_o;     // [rows*heads, num_splits, head_dim]
+    float* part_ml;    // [rows*heads, num_splits, 2]
+    float* out;        // [rows, heads*head_dim]
+    float scale;
+    int32_t* status;
+};
+
+struct SplitPlan { int pages_total, pages_per_split, num_splits; };
+
+SplitPlan plan_splits(int64_t rows, int kv_heads, int max_length, int page_size) {
+    SplitPlan s{};
+    s.pages_total = (max_length + page_size - 1) / page_size;
+    if (s.pages_total < 1) s.pages_total = 1;
+    const int64_t items = rows * kv_heads;
+    int64_t pps = (items * s.pages_total + 2399) / 2400;
+    if (pps < 1) pps = 1;
+    if (pps > 16) {
+        const int64_t splits16 = (s.pages_total + 15) / 16;
+        pps = items * splits16 <= 32768 ? 16 : s.pages_total;
+    }
+    if (pps > s.pages_total) pps = s.pages_total;
+    s.pages_per_split = static_cast<int>(pps);
+    s.num_splits = (s.pages_total + s.pages_per_split - 1) / s.pages_per_split;
+    return s;
+}
+
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t*>(&v);
+}
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t address) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(address));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], uint32_t address) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(address));
+}
+__device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+constexpr int kConsumerWarps = 4;
+constexpr int kFastThreads = (kConsumerWarps + 1) * 32;
+constexpr int kHalfTileBytes = 64 * 128;  // one TMA box: 64 tokens x 64 bf16
+
+template <int HD> struct FastShape {
+    static constexpr int halves = HD / 64;
+    static constexpr int tile_bytes = halves * kHalfTileBytes;  // K or V page
+    static constexpr int stage_bytes = 2 * tile_bytes;
+    static constexpr int stages = HD == 128 ? 3 : 4;
+    static constexpr int smem_bytes = stages * stage_bytes + 1024 + 2 * stages * 8;
+};
+
+// Byte offset of 16-byte chunk `chunk` (8 features) of token `token` inside a swizzled K or V page.
+__device__ __forceinline__ uint32_t tile_offset(int token, int chunk) {
+    return static_cast<uint32_t>((chunk >> 3) * kHalfTileBytes + token * 128 + (((chunk & 7) ^ (token & 7)) << 4));
+}
+
+template <int HD>
+__global__ void __launch_bounds__(kFastThreads) attention_mma_kernel(const __grid_constant__ CUtensorMap kmap,
+                                                                     const __grid_constant__ CUtensorMap vmap,
+                                                                     const AttnParams p) {
+    using S = FastShape<HD>;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+    uint64_t* full = reinterpret_cast<uint64_t*>(smem + S::stages * S::stage_bytes);
+    uint64_t* empty = full + S::stages;
+
+    const int item = blockIdx.x, split = blockIdx.y;
+    const int row = item / p.kv.kv_heads, kvh = item % p.kv.kv_heads;
+    const int sequence = row / p.tokens_per_sequence;
+    const int kv_len = p.kv.lengths[sequence] + (p.causal ? row % p.tokens_per_sequence + 1 : 0);
+    const int page_begin = split * p.pages_per_split;
+    int page_end = (kv_len + kFastPageSize - 1) / kFastPageSize;
+    if (page_end > page_begin + p.pages_per_split) page_end = page_begin + p.pages_per_split;
+    if (page_begin >= page_end) return;  // uniform for the CTA
+    const int pages = page_end - page_begin;
+    const int group = p.heads / p.kv.kv_heads;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < S::stages; ++s) {
+            mbar_init(&full[s], 1);
+            mbar_init(&empty[s], kConsumerWarps);
+        }
+        mbar_fence_init();
+    }
+    __syncthreads();
+
+    float m_row[2] = {-INFINITY, -INFINITY}, l_row[2] = {0.0f, 0.0f};
+    float o[HD / 8][4];
+#pragma unroll
+    for (int j = 0; j < HD / 8; ++j) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.0f;
+
+    if (warp == kConsumerWarps) {
+        // ---- producer: all lanes walk the loop together, lane 0 waits and issues ----
+        if (lane == 0) { tma_prefetch_descriptor(&kmap); tma_prefetch_descriptor(&vmap); }
+        const int32_t* table = p.kv.page_table + static_cast<int64_t>(sequence) * p.kv.pages_per_seq + page_begin;
+        bool alive = true;
+        for (int i = 0; i < pages && alive; ++i) {
+            if (lane == 0) {
+                const int s = i % S::stages;
+                const uint32_t phase = (i / S::stages) & 1;
+                if (!mbar_wait(&empty[s], phase ^ 1)) {
+                    atomicExch(p.status, B200_DEVICE_TIMEOUT);
+                    alive = false;
+                } else {
+                    const int page = table[i];
+                    const int y = (page * p.kv.kv_heads + kvh) * kFastPageSize;
+                    uint8_t* kdst = smem + s * S::stage_bytes;
+                    uint8_t* vdst = kdst + S::tile_bytes;
+                    mbar_expect_tx(&full[s], S::stage_bytes);
+#pragma unroll
+                    for (int h = 0; h < S::halves; ++h) {
+                        tma_load_2d(kdst + h * kHalfTileBytes, &kmap, h * 64, y, &full[s]);
+                        tma_load_2d(vdst + h * kHalfTileBytes, &vmap, h * 64, y, &full[s]);
+                    }
+                }
+            }
+            alive = __shfl_sync(0xffffffffu, alive, 0);
+        }
+    } else {
+        // ---- consumers ----
+        const int g = lane >> 2, t = lane & 3;
+        uint32_t qa[HD / 16][4];
+        {
+            const float* q0 = p.q + (static_cast<int64_t>(row) * p.heads + kvh * group + g) * HD;
+            const float* q1 = q0 + 8 * HD;
+            const bool v0 = g < group, v1 = g + 8 < group;
+#pragma unroll
+            for (int kk = 0; kk < HD / 16; ++kk) {
+                const int c = kk * 16 + 2 * t;
+                qa[kk][0] = v0 ? pack_bf16(q0[c], q0[c + 1]) : 0u;
+                qa[kk][1] = v1 ? pack_bf16(q1[c], q1[c + 1]) : 0u;
+                qa[kk][2] = v0 ? pack_bf16(q0[c + 8], q0[c + 9]) : 0u;
+                qa[kk][3] = v1 ? pack_bf16(q1[c + 8], q1[c + 9]) : 0u;
+            }
+        }
+        const int tok0 = warp * 16;
+        const int mi = lane >> 3, ri = lane & 7;
+        bool alive = true;
+        for (int i = 0; i < pages && alive; ++i) {
+            const int s = i % S::stages;
+            const uint32_t phase = (i / S::stages) & 1;
+            if (!mbar_wait(&full[s], phase)) {
+                if (lane == 0) atomicExch(p.status, B200_DEVICE_TIMEOUT);
+                alive = false;
+                break;
+            }
+            const uint32_t kbase = smem_u32(smem + s * S::stage_bytes);
+            const uint32_t vbase = kbase + S::tile_bytes;
+
+            float sc[2][4];
+#pragma unroll
+            for (int n = 0; n < 2; ++n) sc[n][0] = sc[n][1] = sc[n][2] = sc[n][3] = 0.0f;
+#pragma unroll
+            for (int kk = 0; kk < HD / 16; ++kk) {
+                uint32_t r[4];
+                ldmatrix_x4(r, kbase + tile_offset(tok0 + (mi >> 1) * 8 + ri, 2 * kk + (mi & 1)));
+                mma_bf16(sc[0], qa[kk], r[0], r[1]);
+                mma_bf16(sc[1], qa[kk], r[2], r[3]);
+            }
+            // scale, mask keys at or beyond the row's key count, online softmax per row (g and g+8)
+            const int token_base = (page_begin + i) * kFastPageSize + tok0 + 2 * t;
+            float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+            for (int n = 0; n < 2; ++n)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int token = token_base + n * 8 + (e & 1);
+                    const float v = token < kv_len ? sc[n][e] * p.scale : -INFINITY;
+                    sc[n][e] = v;
+                    mx[e >> 1] = fmaxf(mx[e >> 1], v);
+                }
+            float corr[2], safe[2];
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 1));
+                mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 2));
+                const float m_new = fmaxf(m_row[h], mx[h]);
+                safe[h] = m_new == -INFINITY ? 0.0f : m_new;
+                corr[h] = expf(m_row[h] - safe[h]);
+                m_row[h] = m_new;
+            }
+            float sum[2] = {0.0f, 0.0f};
+#pragma unroll
+            for (int n = 0; n < 2; ++n)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    sc[n][e] = expf(sc[n][e] - safe[e >> 1]);
+                    sum[e >> 1] += sc[n][e];
+                }
+            l_row[0] = l_row[0] * corr[0] + sum[0];
+            l_row[1] = l_row[1] * corr[1] + sum[1];
+#pragma unroll
+            for (int j = 0; j < HD / 8; ++j) {
+                o[j][0] *= corr[0]; o[j][1] *= corr[0];
+                o[j][2] *= corr[1]; o[j][3] *= corr[1];
+            }
+            uint32_t pa[4];
+            pa[0] = pack_bf16(sc[0][0], sc[0][1]);
+            pa[1] = pack_bf16(sc[0][2], sc[0][3]);
+            pa[2] = pack_bf16(sc[1][0], sc[1][1]);
+            pa[3] = pack_bf16(sc[1][2], sc[1][3]);
+#pragma unroll
+            for (int j = 0; j < HD / 8; j += 2) {
+                uint32_t r[4];
+                ldmatrix_x4_trans(r, vbase + tile_offset(tok0 + (mi & 1) * 8 + ri, j + (mi >> 1)));
+                mma_bf16(o[j], pa, r[0], r[1]);
+                mma_bf16(o[j + 1], pa, r[2], r[3]);
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&empty[s]);
+        }
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            l_row[h] += __shfl_xor_sync(0xffffffffu, l_row[h], 1);
+            l_row[h] += __shfl_xor_sync(0xffffffffu, l_row[h], 2);
+        }
+    }
+    __syncthreads();  // every page has been consumed: the stage memory can be reused for the merge
+
+    float* merge_o = reinterpret_cast<float*>(smem);                       // [warps][group][HD]
+    float* merge_ml = merge_o + kConsumerWarps * 16 * HD;                   // [warps][16][2]
+    if (warp < kConsumerWarps) {
+        const int g = lane >> 2, t = lane & 3;
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const int r = g + 8 * h;
+            if (r < group) {
+                float* dst = merge_o + (warp * 16 + r) * HD + 2 * t;
+#pragma unroll
+                for (int j = 0; j < HD / 8; ++j) {
+                    dst[j * 8] = o[j][2 * h];
+                    dst[j * 8 + 1] = o[j][2 * h + 1];
+                }
+                if (t == 0) {
+                    merge_ml[(warp * 16 + r) * 2] = m_row[h];
+                    merge_ml[(warp * 16 + r) * 2 + 1] = l_row[h];
+                }
+            }
+        }
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < group * HD; i += kFastThreads) {
+        const int r = i / HD, d = i - r * HD;
+        float m = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < kConsumerWarps; ++w) m = fmaxf(m, merge_ml[(w * 16 + r) * 2]);
+        float acc = 0.0f, l = 0.0f;
+#pragma unroll
+        for (int w = 0; w < kConsumerWarps; ++w) {
+            const float mw = merge_ml[(w * 16 + r) * 2];
+            const float weight = mw == -INFINITY ? 0.0f : expf(mw - m);
+            acc += weight * merge_o[(w * 16 + r) * HD + d];
+            l += weight * merge_ml[(w * 16 + r) * 2 + 1];
+        }
+        const int64_t head_item = static_cast<int64_t>(row) * p.heads + kvh * group + r;
+        if (p.num_splits == 1) {
+            p.out[head_item * HD + d] = acc / l;
+        } else {
+            p.part_o[(head_item * p.num_splits + split) * HD + d] = acc;
+            if (d == 0) {
+                p.part_ml[(head_item * p.num_splits + split) * 2] = m;
+                p.part_ml[(head_item * p.num_splits + split) * 2 + 1] = l;
+            }
+        }
+    }
+}
+
+// Generic path: one (row, head) per CTA, four warps stride over the tokens of the split.
+constexpr int kGenericThreads = 128;
+constexpr int kMaxDimsPerLane = 8;  // head_dim <= 256
+
+__global__ void __launch_bounds__(kGenericThreads) attention_generic_kernel(const AttnParams p) {
+    __shared__ float merge_ml[4][2];
+    extern __shared__ float merge_o[];  // [4][head_dim]
+    const int hd = p.kv.head_dim;
+    const int item = blockIdx.x, split = blockIdx.y;
+    const int row = item / p.heads, head = item % p.heads;
+    const int kvh = head / (p.heads / p.kv.kv_heads);
+    const int sequence = row / p.tokens_per_sequence;
+    const int kv_len = p.kv.lengths[sequence] + (p.causal ? row % p.tokens_per_sequence + 1 : 0);
+    const int begin = split * p.pages_per_split * p.kv.page_size;
+    int end = begin + p.pages_per_split * p.kv.page_size;
+    if (end > kv_len) end = kv_len;
+    if (begin >= end) return;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const float* q = p.q + (static_cast<int64_t>(row) * p.heads + head) * hd;
+    float qv[kMaxDimsPerLane], acc[kMaxDimsPerLane];
+#pragma unroll
+    for (int i = 0; i < kMaxDimsPerLane; ++i) {
+        const int d = lane + 32 * i;
+        qv[i] = d < hd ? q[d] : 0.0f;
+        acc[i] = 0.0f;
+    }
+    float m = -INFINITY, l = 0.0f;
+    for (int token = begin + warp; token < end; token += 4) {
+        const int64_t at = kv_offset(p.kv, sequence, token, kvh);
+        float dot = 0.0f;
+#pragma unroll
+        for (int i = 0; i < kMaxDimsPerLane; ++i) {
+            const int d = lane + 32 * i;
+            if (d < hd) dot = fmaf(qv[i], kv_load(p.kv, 0, at + d), dot);
+        }
+        const float score = warp_sum(dot) * p.scale;
+        const float m_new = fmaxf(m, score);
+        const float corr = expf(m - m_new), weight = expf(score - m_new);
+        l = l * corr + weight;
+#pragma unroll
+        for (int i = 0; i < kMaxDimsPerLane; ++i) {
+            const int d = lane + 32 * i;
+            if (d < hd) acc[i] = fmaf(weight, kv_load(p.kv, 1, at + d), acc[i] * corr);
+        }
+        m = m_new;
+    }
+#pragma unroll
+    for (int i = 0; i < kMaxDimsPerLane; ++i) {
+        const int d = lane + 32 * i;
+        if (d < hd) merge_o[warp * hd + d] = acc[i];
+    }
+    if (lane == 0) { merge_ml[warp][0] = m; merge_ml[warp][1] = l; }
+    __syncthreads();
+    const int64_t head_item = static_cast<int64_t>(row) * p.heads + head;
+    for (int d = threadIdx.x; d < hd; d += kGenericThreads) {
+        float mm = -INFINITY;
+        for (int w = 0; w < 4; ++w) mm = fmaxf(mm, merge_ml[w][0]);
+        float a = 0.0f, ll = 0.0f;
+        for (int w = 0; w < 4; ++w) {
+            const float weight = merge_ml[w][0] == -INFINITY ? 0.0f : expf(merge_ml[w][0] - mm);
+            a += weight * merge_o[w * hd + d];
+            ll += weight * merge_ml[w][1];
+        }
+        if (p.num_splits == 1) {
+            p.out[head_item * hd + d] = a / ll;
+        } else {
+            p.part_o[(head_item * p.num_splits + split) * hd + d] = a;
+            if (d == 0) {
+                p.part_ml[(head_item * p.num_splits + split) * 2] = mm;
+                p.part_ml[(head_item * p.num_splits + split) * 2 + 1] = ll;
+            }
+        }
+    }
+}
+
+// Merge of the split partials: one (row, head) per CTA.
+__global__ void attention_combine_kernel(const AttnParams p) {
+    const int hd = p.kv.head_dim;
+    const int64_t head_item = blockIdx.x;
+    const int row = static_cast<int>(head_item / p.heads);
+    const int sequence = row / p.tokens_per_sequence;
+    const int kv_len = p.kv.lengths[sequence] + (p.causal ? row % p.tokens_per_sequence + 1 : 0);
+    const int pages = (kv_len + p.kv.page_size - 1) / p.kv.page_size;
+    int valid = (pages + p.pages_per_split - 1) / p.pages_per_split;
+    if (valid > p.num_splits) valid = p.num_splits;
+    const float* ml = p.part_ml + head_item * p.num_splits * 2;
+    float m = -INFINITY;
+    for (int s = 0; s < valid; ++s) m = fmaxf(m, ml[2 * s]);
+    float l = 0.0f;
+    for (int s = 0; s < valid; ++s) l += expf(ml[2 * s] - m) * ml[2 * s + 1];
+    for (int d = threadIdx.x; d < hd; d += blockDim.x) {
+        float acc = 0.0f;
+        for (int s = 0; s < valid; ++s) acc += expf(ml[2 * s] - m) * p.part_o[(head_item * p.num_splits + s) * hd + d];
+        p.out[head_item * hd + d] = acc / l;
+    }
+}
+
+template <int HD> int launch_fast(const b200_kv_cache* cache, const AttnParams& p, cudaStream_t stream) {
+    using S = FastShape<HD>;
+    auto kernel = attention_mma_kernel<HD>;
+    B200_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, S::smem_bytes));
+    const dim3 grid(static_cast<unsigned>(p.rows) * p.kv.kv_heads, p.num_splits);
+    kernel<<<grid, kFastThreads, S::smem_bytes, stream>>>(*kv_tensor_map(cache, 0), *kv_tensor_map(cache, 1), p);
+    return cuda_status(cudaGetLastError(), "attention_mma_kernel launch");
+}
+
+}  // namespace
+}  // namespace b200
+
+using namespace b200;
+
+extern "C" size_t b200_attention_scratch_bytes(int64_t rows, int32_t heads, int32_t kv_heads, int32_t head_dim,
+                                               int32_t max_length, int32_t page_size) {
+    if (rows <= 0 || heads <= 0 || kv_heads <= 0 || head_dim <= 0 || max_length <= 0 || page_size <= 0) return 0;
+    const SplitPlan s = plan_splits(rows, kv_heads, max_length, page_size);
+    if (s.num_splits == 1) return 256;
+    return static_cast<size_t>(rows) * heads * s.num_splits * (head_dim + 2) * sizeof(float) + 256;
+}
+
+extern "C" int b200_attention_decode(const float* q, int64_t rows, int32_t tokens_per_sequence, int32_t heads,
+                                     const b200_kv_cache* cache, int32_t max_length, int32_t causal, void* scratch,
+                                     size_t scratch_bytes, float* out, void* stream) {
+    if (!q || !cache || !out || rows <= 0 || tokens_per_sequence <= 0 || heads <= 0 || heads % cache->kv_heads
+        || rows != static_cast<int64_t>(cache->sequences) * tokens_per_sequence || max_length <= 0) {
+        set_error("b200_attention_decode: bad pointer, size or head grouping");
+        return B200_BAD_ARGUMENT;
+    }
+    if (cache->head_dim > 32 * kMaxDimsPerLane) { set_error("b200_attention_decode: head_dim above 256 is not supported"); return B200_UNSUPPORTED; }
+    if (max_length > cache->capacity) max_length = cache->capacity;
+    const SplitPlan plan = plan_splits(rows, cache->kv_heads, max_length, cache->page_size);
+    const size_t need = b200_attention_scratch_bytes(rows, heads, cache->kv_heads, cache->head_dim, max_length, cache->page_size);
+    if (plan.num_splits > 1 && (!scratch || scratch_bytes < need)) {
+        set_error("b200_attention_decode: scratch of %zu bytes needed, %zu given", need, scratch_bytes);
+        return B200_BAD_ARGUMENT;
+    }
+    AttnParams p{};
+    p.q = q; p.rows = static_cast<int>(rows); p.tokens_per_sequence = tokens_per_sequence; p.heads = heads; p.causal = causal;
+    p.kv = kv_view(cache);
+    p.pages_per_split = plan.pages_per_split; p.num_splits = plan.num_splits;
+    p.part_o = static_cast<float*>(scratch);
+    p.part_ml = p.part_o ? p.part_o + static_cast<size_t>(rows) * heads * plan.num_splits * cache->head_dim : nullptr;
+    p.out = out;
+    p.scale = static_cast<float>(1.0 / std::sqrt(static_cast<double>(cache->head_dim)));
+    p.status = device_status_word(cache->device);
+    cudaStream_t s = as_stream(stream);
+    const int group = heads / cache->kv_heads;
+    int status;
+    if (kv_tensor_map(cache, 0) && group <= 16 && (cache->head_dim == 64 || cache->head_dim == 128)) {
+        status = cache->head_dim == 128 ? launch_fast<128>(cache, p, s) : launch_fast<64>(cache, p, s);
+    } else {
+        const dim3 grid(static_cast<unsigned>(rows) * heads, plan.num_splits);
+        attention_generic_kernel<<<grid, kGenericThreads, sizeof(float) * 4 * cache->head_dim, s>>>(p);
+        status = cuda_status(cudaGetLastError(), "attention_generic_kernel launch");
+    }
+    if (status != B200_OK || plan.num_splits == 1) return status;
+    attention_combine_kernel<<<static_cast<unsigned>(rows) * heads, 128, 0, s>>>(p);
+    return cuda_status(cudaGetLastError(), "attention_combine_kernel launch");
+}

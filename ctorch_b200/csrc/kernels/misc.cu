@@ -1,0 +1,280 @@
+// Small operators of the token loop (embedding gather, stand-alone RMSNorm, argmax, row select) and the host
+// utilities shared by the kernel files (error text, driver entry point lookup, device status word).
+#include "common.cuh"
+
+#include <cstring>
+#include <mutex>
+
+namespace b200 {
+
+namespace {
+thread_local char error_text[512];
+std::mutex status_mutex;
+int32_t* status_words[64];
+}  // namespace
+
+void set_error(const char* format, ...) {
+    va_list args;
+    va_start(args, format);
+    std::vsnprintf(error_text, sizeof error_text, format, args);
+    va_end(args);
+}
+
+int cuda_status(cudaError_t error, const char* what) {
+    if (error == cudaSuccess) return B200_OK;
+    set_error("CUDA: %s: %s", what, cudaGetErrorString(error));
+    return static_cast<int>(error);
+}
+
+int32_t* device_status_word(int device) {
+    std::lock_guard<std::mutex> lock(status_mutex);
+    if (device < 0 || device >= 64) return nullptr;
+    if (!status_words[device]) {
+        int current = 0;
+        cudaGetDevice(&current);
+        cudaSetDevice(device);
+        if (cudaMalloc(reinterpret_cast<void**>(&status_words[device]), sizeof(int32_t)) == cudaSuccess)
+            cudaMemset(status_words[device], 0, sizeof(int32_t));
+        else
+            status_words[device] = nullptr;
+        cudaSetDevice(current);
+    }
+    return status_words[device];
+}
+
+encode_tiled_fn tensor_map_encoder() {
+    static encode_tiled_fn cached = [] {
+        void* entry = nullptr;
+        cudaDriverEntryPointQueryResult result;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &entry, cudaEnableDefault, &result) != cudaSuccess
+            || result != cudaDriverEntryPointSuccess)
+            entry = nullptr;
+        return reinterpret_cast<encode_tiled_fn>(entry);
+    }();
+    return cached;
+}
+
+namespace {
+
+template <class T>
+__global__ void embedding_kernel(const T* table, const int64_t* ids, int64_t rows, int64_t vocab, int64_t width, float* out,
+                                 int32_t* status) {
+    const int64_t row = blockIdx.x;
+    int64_t id = ids[row];
+    if (id < 0 || id >= vocab) {  // the host API validates ids it can see; device-resident ids are clamped and flagged
+        if (threadIdx.x == 0) atomicExch(status, B200_BAD_ARGUMENT);
+        id = id < 0 ? 0 : vocab - 1;
+    }
+    for (int64_t c = threadIdx.x; c < width; c += blockDim.x) out[row * width + c] = load_as_f32(table, id * width + c);
+}
+
+// One CTA per row; f64 accumulation and f64 scale, one rounding (src/kernels/cpu/normalization.cpp:39-51).
+template <class T>
+__global__ void rms_norm_kernel(const float* x, const T* weight, int64_t width, double eps, float* out) {
+    __shared__ double partial[32];
+    __shared__ double inverse_std;
+    const float* row = x + blockIdx.x * width;
+    double squares = 0.0;
+    for (int64_t c = threadIdx.x; c < width; c += blockDim.x) {
+        const double v = static_cast<double>(row[c]);
+        squares += v * v;
+    }
+    squares = warp_sum(squares);
+    if ((threadIdx.x & 31) == 0) partial[threadIdx.x >> 5] = squares;
+    __syncthreads();
+    if (threadIdx.x < 32) {
+        double v = threadIdx.x < (blockDim.x >> 5) ? partial[threadIdx.x] : 0.0;
+        v = warp_sum(v);
+        if (threadIdx.x == 0) inverse_std = 1.0 / sqrt(v / static_cast<double>(width) + eps);
+    }
+    __syncthreads();
+    for (int64_t c = threadIdx.x; c < width; c += blockDim.x) {
+        double v = static_cast<double>(row[c]) * inverse_std;
+        if (weight) v *= static_cast<double>(load_as_f32(weight, c));
+        out[blockIdx.x * width + c] = static_cast<float>(v);
+    }
+}
+
+// (value, index) ordering of the reference: a NaN beats everything and the first NaN / first maximum wins.
+struct Best { float value; int64_t index; };
+__device__ __forceinline__ bool better(const Best& a, const Best& b) {  // is a preferred over b?
+    const bool an = a.value != a.value, bn = b.value != b.value;
+    if (an || bn) return an && (!bn || a.index < b.index);
+    return a.value > b.value || (a.value == b.value && a.index < b.index);
+}
+__global__ void argmax_kernel(const float* x, int64_t width, int64_t* index) {
+    __shared__ Best partial[32];
+    const float* row = x + blockIdx.x * width;
+    Best best{row[0], 0};
+    for (int64_t c = threadIdx.x; c < width; c += blockDim.x) {
+        const Best candidate{row[c], c};
+        if (better(candidate, best)) best = candidate;
+    }
+    for (int o = 16; o > 0; o >>= 1) {
+        Best other{__shfl_xor_sync(0xffffffffu, best.value, o), __shfl_xor_sync(0xffffffffu, best.index, o)};
+        if (better(other, best)) best = other;
+    }
+    if ((threadIdx.x & 31) == 0) partial[threadIdx.x >> 5] = best;
+    __syncthreads();
+    if (threadIdx.x < 32) {
+        best = threadIdx.x < (blockDim.x >> 5) ? partial[threadIdx.x] : Best{row[0], 0};
+        for (int o = 16; o > 0; o >>= 1) {
+            Best other{__shfl_xor_sync(0xffffffffu, best.value, o), __shfl_xor_sync(0xffffffffu, best.index, o)};
+            if (better(other, best)) best = other;
+        }
+        if (threadIdx.x == 0) index[blockIdx.x] = best.index;
+    }
+}
+
+__global__ void select_rows_kernel(const float* x, int64_t first, int64_t stride, int64_t width, float* out) {
+    const float* row = x + (first + blockIdx.x * stride) * width;
+    for (int64_t c = threadIdx.x; c < width; c += blockDim.x) out[blockIdx.x * width + c] = row[c];
+}
+
+}  // namespace
+}  // namespace b200
+
+using namespace b200;
+
+extern "C" {
+
+const char* b200_last_error(void) { return error_text; }
+
+int b200_embedding(const void* table, int32_t table_dtype, const int64_t* ids, int64_t rows, int64_t vocab, int64_t width,
+                   float* out, void* stream) {
+    if (!table || !ids || !out || rows < 0 || vocab <= 0 || width <= 0) { set_error("b200_embedding: bad pointer or size"); return B200_BAD_ARGUMENT; }
+    if (rows == 0) return B200_OK;
+    int device = 0;
+    B200_CUDA(cudaGetDevice(&device));
+    int32_t* status = device_status_word(device);
+    const int threads = width >= 256 ? 256 : 64;
+    if (table_dtype == B200_BF16)
+        embedding_kernel<<<static_cast<unsigned>(rows), threads, 0, as_stream(stream)>>>(static_cast<const __nv_bfloat16*>(table), ids, rows, vocab, width, out, status);
+    else if (table_dtype == B200_F32)
+        embedding_kernel<<<static_cast<unsigned>(rows), threads, 0, as_stream(stream)>>>(static_cast<const float*>(table), ids, rows, vocab, width, out, status);
+    else { set_error("b200_embedding: table dtype %d is not f32 or bf16", table_dtype); return B200_UNSUPPORTED; }
+    return cuda_status(cudaGetLastError(), "embedding_kernel launch");
+}
+
+int b200_rms_norm(const float* x, const void* weight, int32_t weight_dtype, int64_t rows, int64_t width, double eps,
+                  float* out, void* stream) {
+    if (!x || !out || rows < 0 || width <= 0) { set_error("b200_rms_norm: bad pointer or size"); return B200_BAD_ARGUMENT; }
+    if (rows == 0) return B200_OK;
+    if (weight && weight_dtype == B200_BF16)
+        rms_norm_kernel<<<static_cast<unsigned>(rows), 256, 0, as_stream(stream)>>>(x, static_cast<const __nv_bfloat16*>(weight), width, eps, out);
+    else if (!weight || weight_dtype == B200_F32)
+        rms_norm_kernel<<<static_cast<unsigned>(rows), 256, 0, as_stream(stream)>>>(x, static_cast<const float*>(weight), width, eps, out);
+    else { set_error("b200_rms_norm: weight dtype %d is not f32 or bf16", weight_dtype); return B200_UNSUPPORTED; }
+    return cuda_status(cudaGetLastError(), "rms_norm_kernel launch");
+}
+
+int b200_argmax(const float* x, int64_t rows, int64_t width, int64_t* index, void* stream) {
+    if (!x || !index || rows < 0 || width <= 0) { set_error("b200_argmax: bad pointer or size"); return B200_BAD_ARGUMENT; }
+    if (rows == 0) return B200_OK;
+    argmax_kernel<<<static_cast<unsigned>(rows), width >= 4096 ? 1024 : 256, 0, as_stream(stream)>>>(x, width, index);
+    return cuda_status(cudaGetLastError(), "argmax_kernel launch");
+}
+
+int b200_select_rows(const float* x, int64_t first, int64_t stride, int64_t rows_out, int64_t width, float* out, void* stream) {
+    if (!x || !out || rows_out < 0 || width <= 0 || first < 0 || stride <= 0) { set_error("b200_select_rows: bad pointer or size"); return B200_BAD_ARGUMENT; }
+    if (rows_out == 0) return B200_OK;
+    select_rows_kernel<<<static_cast<unsigned>(rows_out), 256, 0, as_stream(stream)>>>(x, first, stride, width, out);
+    return cuda_status(cudaGetLastError(), "select_rows_kernel launch");
+}
+
+int b200_take_device_status(int32_t device, void* stream, int32_t* status) {
+    if (!status) return B200_BAD_ARGUMENT;
+    int32_t* word = device_status_word(device);
+    if (!word) { set_error("no status word for device %d", device); return B200_NO_DEVICE; }
+    B200_CUDA(cudaMemcpyAsync(status, word, sizeof(int32_t), cudaMemcpyDeviceToHost, as_stream(stream)));
+    B200_CUDA(cudaStreamSynchronize(as_stream(stream)));
+    if (*status) B200_CUDA(cudaMemsetAsync(word, 0, sizeof(int32_t), as_stream(stream)));
+    return B200_OK;
+}
+
+}  // extern "C"
+
+namespace b200 {
+namespace {
+
+__global__ void rotary_kernel(const float* x, int64_t pairs, int64_t length, int64_t half, const float* cosine,
+                              const float* sine, float* out) {
+    for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < pairs;
+         i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+        const int64_t j = i % half, l = (i / half) % length;
+        const float even = x[2 * i], odd = x[2 * i + 1];
+        const float c = cosine[l * half + j], s = sine[l * half + j];
+        out[2 * i] = __fsub_rn(__fmul_rn(even, c), __fmul_rn(odd, s));
+        out[2 * i + 1] = __fadd_rn(__fmul_rn(even, s), __fmul_rn(odd, c));
+    }
+}
+
+__global__ void permute_0213_kernel(const float* in, int64_t a, int64_t b, int64_t c, int64_t d, float* out) {
+    const int64_t total = a * b * c * d;
+    for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < total;
+         i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+        const int64_t id = i % d, ib = (i / d) % b, ic = (i / d / b) % c, ia = i / d / b / c;  // i indexes out [a,c,b,d]
+        out[i] = in[((ia * b + ib) * c + ic) * d + id];
+    }
+}
+
+__global__ void token_feedback_kernel(const int64_t* next, int64_t batch, int64_t* ids, int64_t* history,
+                                      int64_t history_rows, int32_t* counter) {
+    const int32_t step = *counter;
+    for (int64_t s = threadIdx.x; s < batch; s += blockDim.x) {
+        const int64_t token = next[s];
+        if (ids) ids[s] = token;
+        if (history && step < history_rows) history[static_cast<int64_t>(step) * batch + s] = token;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) *counter = step + 1;
+}
+
+unsigned blocks_for(int64_t n) { return static_cast<unsigned>((n + 255) / 256 < 8192 ? (n + 255) / 256 : 8192); }
+
+}  // namespace
+}  // namespace b200
+
+extern "C" {
+
+int b200_rotary(const float* x, int64_t outer, int64_t length, int64_t head_dim, const float* cosine, const float* sine,
+                float* out, void* stream) {
+    if (!x || !cosine || !sine || !out || outer < 0 || length < 0 || head_dim <= 0 || (head_dim & 1)) { set_error("b200_rotary: bad pointer or size"); return B200_BAD_ARGUMENT; }
+    const int64_t pairs = outer * length * (head_dim / 2);
+    if (pairs == 0) return B200_OK;
+    b200::rotary_kernel<<<b200::blocks_for(pairs), 256, 0, as_stream(stream)>>>(x, pairs, length, head_dim / 2, cosine, sine, out);
+    return cuda_status(cudaGetLastError(), "rotary_kernel launch");
+}
+
+int b200_permute_0213(const float* in, int64_t a, int64_t b, int64_t c, int64_t d, float* out, void* stream) {
+    if (!in || !out || a < 0 || b < 0 || c < 0 || d < 0) { set_error("b200_permute_0213: bad pointer or size"); return B200_BAD_ARGUMENT; }
+    if (a * b * c * d == 0) return B200_OK;
+    b200::permute_0213_kernel<<<b200::blocks_for(a * b * c * d), 256, 0, as_stream(stream)>>>(in, a, b, c, d, out);
+    return cuda_status(cudaGetLastError(), "permute_0213_kernel launch");
+}
+
+int b200_token_feedback(const int64_t* next, int64_t batch, int64_t* ids, int64_t* history, int64_t history_rows,
+                        int32_t* counter, void* stream) {
+    if (!next || !counter || batch <= 0) { set_error("b200_token_feedback: bad pointer or size"); return B200_BAD_ARGUMENT; }
+    b200::token_feedback_kernel<<<1, 256, 0, as_stream(stream)>>>(next, batch, ids, history, history_rows, counter);
+    return cuda_status(cudaGetLastError(), "token_feedback_kernel launch");
+}
+
+}  // extern "C"
+
+namespace b200 {
+namespace {
+__global__ void scaled_add_kernel(float* y, const float* x, float scale, int64_t count) {
+    for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < count;
+         i += static_cast<int64_t>(gridDim.x) * blockDim.x)
+        y[i] = __fadd_rn(y[i], __fmul_rn(x[i], scale));
+}
+}  // namespace
+}  // namespace b200
+
+extern "C" int b200_scaled_add(float* y, const float* x, float scale, int64_t count, void* stream) {
+    if (!y || !x || count < 0) { set_error("b200_scaled_add: bad pointer or size"); return B200_BAD_ARGUMENT; }
+    if (count == 0) return B200_OK;
+    b200::scaled_add_kernel<<<b200::blocks_for(count), 256, 0, as_stream(stream)>>>(y, x, scale, count);
+    return cuda_status(cudaGetLastError(), "scaled_add_kernel launch");
+}

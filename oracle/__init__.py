@@ -89,6 +89,7 @@ class CpuLib:
             f("cache_dtype", C.c_int, [C.c_void_p, C.c_int64])
             f("cache_copy", C.c_int, [C.c_void_p, C.c_int64, C.c_int32, fp])
             f("generate_threads", C.c_int, [C.c_void_p, ip] + [C.c_int64] * 4 + [ip])
+            f("timed_decode", C.c_int, [C.c_void_p, ip] + [C.c_int64] * 5 + [C.POINTER(C.c_double)])
             f("linear", C.c_int, [fp, C.c_void_p, C.c_int32, C.c_int64, C.c_int64, C.c_int64, fp])
             f("rotary", C.c_int, [fp] + [C.c_int64] * 4 + [C.c_double, C.c_int64, C.c_int64, fp])
             f("lora_linear", C.c_int, [fp, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32] + [C.c_int64] * 4
@@ -211,6 +212,66 @@ class CpuDecoder:
         self.l.check(self.l.generate_threads(self.handle, _ptr(prompt, C.c_int64), batch, plen, steps, threads,
                                              _ptr(tokens, C.c_int64)))
         return tokens
+
+
+def timed_decode(model: "CpuDecoder", prompt: np.ndarray, warmup: int, steps: int, threads: int) -> float:
+    """Seconds the CPU checker needs for `steps` greedy single-token steps of the whole batch after a prefill and
+    `warmup` untimed steps, with the batch spread over `threads` workers (each with its own cache)."""
+    prompt = np.ascontiguousarray(prompt, dtype=np.int64)
+    batch, plen = prompt.shape
+    threads = max(1, min(threads, batch))
+    if model.l.kind != "port":
+        seconds = C.c_double()
+        model.l.check(model.l.timed_decode(model.handle, _ptr(prompt, C.c_int64), batch, plen, warmup, steps, threads,
+                                           C.byref(seconds)))
+        return seconds.value
+    # port: ctypes releases the GIL during calls, so Python threads run the C code in parallel
+    import threading
+    import time
+    share = (batch + threads - 1) // threads
+    start, finish = threading.Barrier(threads + 1), threading.Barrier(threads + 1)
+    errors = []
+
+    def worker(t):
+        rows = prompt[t * share:(t + 1) * share]
+        count = rows.shape[0]
+        cache = model.l.cache_create(model.handle)
+        vocab = model.spec["vocab"]
+        logits = np.empty((count, plen, vocab), dtype=np.float32)
+        one = np.empty((count, 1, vocab), dtype=np.float32)
+        try:
+            if count:
+                model.l.check(model.l.model_decode(model.handle, cache, _ptr(rows, C.c_int64), count, plen, _ptr(logits)))
+                nxt = argmax(logits[:, -1])
+                for _ in range(warmup):
+                    model.l.check(model.l.model_decode(model.handle, cache, _ptr(nxt, C.c_int64), count, 1, _ptr(one)))
+                    nxt = argmax(one[:, 0])
+            start.wait()
+            for _ in range(steps if count else 0):
+                model.l.check(model.l.model_decode(model.handle, cache, _ptr(nxt, C.c_int64), count, 1, _ptr(one)))
+                nxt = argmax(one[:, 0])
+        except Exception as error:  # noqa: BLE001
+            errors.append(error)
+            start.abort()
+        finally:
+            try:
+                finish.wait()
+            except threading.BrokenBarrierError:
+                pass
+            model.l.cache_release(cache)
+
+    pool = [threading.Thread(target=worker, args=(t,)) for t in range(threads)]
+    for t in pool:
+        t.start()
+    start.wait()
+    begin = time.perf_counter()
+    finish.wait()
+    elapsed = time.perf_counter() - begin
+    for t in pool:
+        t.join()
+    if errors:
+        raise errors[0]
+    return elapsed
 
 
 def gqa_attention(q, k, v, causal_offset: int = -1, kind: str = "port") -> np.ndarray:

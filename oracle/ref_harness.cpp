@@ -15,6 +15,8 @@
 #include <cstring>
 #include <memory>
 #include <string>
+#include <barrier>
+#include <chrono>
 #include <thread>
 #include <vector>
 
@@ -230,6 +232,50 @@ int ref_generate_threads(void* handle, const int64_t* prompt, int64_t batch, int
         });
     }
     for (auto& worker : workers) worker.join();
+    for (int value : status)
+        if (value) return 1;
+    return 0;
+}
+
+// CPU-baseline timing: every worker prefills its slice of the batch and runs `warmup` single-token steps, all
+// workers meet at a barrier, then each runs `steps` timed single-token steps (greedy feedback) and they meet again.
+// seconds = wall time between the two barriers.
+int ref_timed_decode(void* handle, const int64_t* prompt, int64_t batch, int64_t prompt_length, int64_t warmup,
+                     int64_t steps, int64_t threads, double* seconds) {
+    if (threads > batch) threads = batch;
+    std::vector<int> status(static_cast<std::size_t>(threads), 0);
+    std::chrono::steady_clock::time_point begin, end;
+    std::barrier start(static_cast<std::ptrdiff_t>(threads), [&]() noexcept { begin = std::chrono::steady_clock::now(); });
+    std::barrier finish(static_cast<std::ptrdiff_t>(threads), [&]() noexcept { end = std::chrono::steady_clock::now(); });
+    const int64_t share = (batch + threads - 1) / threads;
+    std::vector<std::thread> workers;
+    for (int64_t t = 0; t < threads; ++t) {
+        workers.emplace_back([&, t] {
+            const int64_t first = t * share, count = std::max<int64_t>(0, std::min(share, batch - first));
+            std::vector<int64_t> next;
+            Cache cache;
+            int failed = guarded([&] {
+                if (!count) return;
+                auto& model = *static_cast<Model*>(handle);
+                cache.layers = model.decoder->make_cache();
+                auto last = model_decode(model, cache, prompt + first * prompt_length, count, prompt_length).select(1, prompt_length - 1);
+                next = dl::argmax(last, -1).to_vector<int64_t>();
+                for (int64_t i = 0; i < warmup; ++i)
+                    next = dl::argmax(model_decode(model, cache, next.data(), count, 1).select(1, 0), -1).to_vector<int64_t>();
+            });
+            start.arrive_and_wait();
+            if (!failed)
+                failed = guarded([&] {
+                    auto& model = *static_cast<Model*>(handle);
+                    for (int64_t i = 0; i < steps && count; ++i)
+                        next = dl::argmax(model_decode(model, cache, next.data(), count, 1).select(1, 0), -1).to_vector<int64_t>();
+                });
+            finish.arrive_and_wait();
+            status[static_cast<std::size_t>(t)] = failed;
+        });
+    }
+    for (auto& worker : workers) worker.join();
+    *seconds = std::chrono::duration<double>(end - begin).count();
     for (int value : status)
         if (value) return 1;
     return 0;

@@ -1,0 +1,308 @@
+"""Kernel-level parity: every CUDA kernel is called through the kernel C ABI (b200_*) and compared with the CPU
+oracle on the same seeded inputs.  torch is used only to hold device memory.
+
+Tolerances (relative = max|a-b| / max|b|):
+  f32 paths           1e-5   (the 1e-4 logits budget of the f32 configuration leaves room for depth)
+  bf16 KV / mma path  1e-2   (bf16 storage of K, V, q and the softmax weights; the bf16 logits budget is 2e-2)
+"""
+import ctypes as C
+
+import numpy as np
+import pytest
+
+import ctorch_b200 as B
+import oracle
+from ctorch_b200 import workloads as W
+
+pytestmark = pytest.mark.gpu
+torch = pytest.importorskip("torch")
+
+
+def rel(a, b):
+    return float(np.abs(a.astype(np.float64) - b.astype(np.float64)).max() / max(1e-30, np.abs(b).max()))
+
+
+def dev(array, dtype=None):
+    t = torch.from_numpy(np.ascontiguousarray(array)).cuda()
+    torch.cuda.synchronize()
+    return t
+
+
+def bf16_dev(bits):
+    return dev(bits.view(np.int16))
+
+
+def stream():
+    return B.lib().dl_b200_stream(B.cuda(0))
+
+
+def sync():
+    B.synchronize(0)
+
+
+class Cache:
+    def __init__(self, dtype, sequences, kv_heads, head_dim, capacity, page_size=64):
+        h = C.c_void_p()
+        B.kcheck(B.lib().b200_kv_cache_create(0, dtype, sequences, kv_heads, head_dim, capacity, page_size, C.byref(h)))
+        self.h, self.shape = h, (sequences, kv_heads, head_dim, capacity)
+
+    def __del__(self):
+        B.lib().b200_kv_cache_release(self.h)
+
+    def set_lengths(self, lengths):
+        arr = np.ascontiguousarray(lengths, dtype=np.int32)
+        B.kcheck(B.lib().b200_kv_cache_set_lengths(self.h, arr.ctypes.data_as(C.POINTER(C.c_int32)), stream()))
+
+    def set_page_table(self, table):
+        arr = np.ascontiguousarray(table, dtype=np.int32)
+        B.kcheck(B.lib().b200_kv_cache_set_page_table(self.h, arr.ctypes.data_as(C.POINTER(C.c_int32)), stream()))
+
+    def pages_per_sequence(self):
+        return B.lib().b200_kv_cache_pages_per_sequence(self.h)
+
+    def append(self, k, v):
+        kd, vd = dev(k), dev(v)
+        B.kcheck(B.lib().b200_kv_cache_append(self.h, kd.data_ptr(), vd.data_ptr(), k.shape[2], stream()))
+        sync()
+
+    def gather(self, which, length):
+        s, hk, hd, _ = self.shape
+        out = torch.empty((s, hk, length, hd), dtype=torch.float32, device="cuda")
+        torch.cuda.synchronize()
+        B.kcheck(B.lib().b200_kv_cache_gather(self.h, which, length, out.data_ptr(), stream()))
+        sync()
+        return out.cpu().numpy()
+
+
+def run_linear(x, w, epilogue=0, norm=None, eps=1e-5, residual=None, qkv=None, out_cols=None):
+    rows, inner = x.shape
+    out = w.shape[0]
+    xd = dev(x)
+    wd = bf16_dev(w) if w.dtype == np.uint16 else dev(w)
+    nd = None
+    if norm is not None:
+        nd = bf16_dev(norm) if norm.dtype == np.uint16 else dev(norm)
+    rd = dev(residual) if residual is not None else None
+    y = torch.zeros((rows, out_cols or out), dtype=torch.float32, device="cuda")
+    torch.cuda.synchronize()
+    B.kcheck(B.lib().b200_linear(xd.data_ptr(), rows, inner, wd.data_ptr(), B.BF16 if w.dtype == np.uint16 else B.F32, out,
+                                 nd.data_ptr() if nd is not None else None,
+                                 (B.BF16 if norm.dtype == np.uint16 else B.F32) if norm is not None else 0, eps, epilogue,
+                                 rd.data_ptr() if rd is not None else None, C.byref(qkv) if qkv is not None else None,
+                                 y.data_ptr(), stream()))
+    sync()
+    return y.cpu().numpy()
+
+
+@pytest.mark.parametrize("dtype", ["f32", "bf16"])
+@pytest.mark.parametrize("rows,inner,out", [(1, 256, 256), (2, 768, 1280), (3, 64, 97), (5, 2048, 768), (8, 4096, 130),
+                                            (11, 768, 514), (16, 768, 2048), (4, 12, 8), (1, 6152, 66), (19, 72, 40)])
+def test_linear_store(dtype, rows, inner, out):
+    rng = np.random.default_rng(rows * 1000 + inner + out)
+    x = rng.standard_normal((rows, inner), dtype=np.float32)
+    w = (0.05 * rng.standard_normal((out, inner), dtype=np.float32)).astype(np.float32)
+    if dtype == "bf16":
+        w = W.bf16_bits(w)
+    got = run_linear(x, w)
+    want = oracle.linear(x, w)
+    assert rel(got, want) < 1e-5
+
+
+@pytest.mark.parametrize("dtype", ["f32", "bf16"])
+def test_linear_fused_norm_residual_swiglu(dtype):
+    rng = np.random.default_rng(7)
+    rows, inner, hidden = 6, 768, 1024
+    cast = W.bf16_bits if dtype == "bf16" else (lambda a: a)
+    x = rng.standard_normal((rows, inner), dtype=np.float32) * 3
+    norm = cast((1 + 0.1 * rng.standard_normal(inner)).astype(np.float32))
+    norm_f = W.bf16_to_f32(norm) if dtype == "bf16" else norm
+    gate = cast(0.05 * rng.standard_normal((hidden, inner), dtype=np.float32))
+    up = cast(0.05 * rng.standard_normal((hidden, inner), dtype=np.float32))
+    xn = oracle.rms_norm(x, norm_f, 1e-5)
+    # norm fused into a store
+    assert rel(run_linear(x, gate, norm=norm), oracle.linear(xn, gate)) < 1e-5
+    # SwiGLU epilogue on interleaved rows
+    inter = np.empty((2 * hidden, inner), dtype=gate.dtype)
+    inter[0::2], inter[1::2] = gate, up
+    got = run_linear(x, inter, epilogue=2, norm=norm, out_cols=hidden)
+    want = oracle.silu_mul(oracle.linear(xn, gate), oracle.linear(xn, up))
+    assert rel(got, want) < 1e-5
+    # residual epilogue
+    res = rng.standard_normal((rows, hidden), dtype=np.float32)
+    got = run_linear(x, gate, epilogue=1, residual=res)
+    assert rel(got, res + oracle.linear(x, gate)) < 1e-5
+
+
+def test_rms_norm_matches_reference_rounding():
+    rng = np.random.default_rng(3)
+    x = rng.standard_normal((9, 768), dtype=np.float32) * 5
+    w = (1 + 0.1 * rng.standard_normal(768)).astype(np.float32)
+    xd, wd = dev(x), dev(w)
+    y = torch.empty_like(xd)
+    torch.cuda.synchronize()
+    B.kcheck(B.lib().b200_rms_norm(xd.data_ptr(), wd.data_ptr(), B.F32, 9, 768, 1e-5, y.data_ptr(), stream()))
+    sync()
+    want = oracle.rms_norm(x, w, 1e-5)
+    got = y.cpu().numpy()
+    # f64 accumulation on both sides: at most the last bit differs (summation order of the f64 sum)
+    assert np.abs(got.view(np.int32) - want.view(np.int32)).max() <= 1
+
+
+def test_embedding_and_argmax_rules():
+    rng = np.random.default_rng(5)
+    table = W.bf16_bits(rng.standard_normal((50, 64), dtype=np.float32))
+    ids = rng.integers(0, 50, size=(7,), dtype=np.int64)
+    td, idd = bf16_dev(table), dev(ids)
+    out = torch.empty((7, 64), dtype=torch.float32, device="cuda")
+    torch.cuda.synchronize()
+    B.kcheck(B.lib().b200_embedding(td.data_ptr(), B.BF16, idd.data_ptr(), 7, 50, 64, out.data_ptr(), stream()))
+    sync()
+    assert np.array_equal(out.cpu().numpy(), W.bf16_to_f32(table)[ids])
+
+    x = rng.standard_normal((5, 32000), dtype=np.float32)
+    x[0, 17] = x[0, 31999] = 9.0          # tie: the first wins
+    x[1, 20000] = np.nan                  # NaN wins
+    x[1, 25000] = np.nan
+    x[2, :] = -1.0                        # all equal
+    x[3, 31999] = 50.0                    # last element
+    xd = dev(x)
+    idx = torch.empty((5,), dtype=torch.int64, device="cuda")
+    torch.cuda.synchronize()
+    B.kcheck(B.lib().b200_argmax(xd.data_ptr(), 5, 32000, idx.data_ptr(), stream()))
+    sync()
+    assert idx.cpu().numpy().tolist() == oracle.argmax(x).tolist() == [17, 20000, 0, 31999, int(np.argmax(x[4]))]
+
+
+@pytest.mark.parametrize("cache_dtype", [B.F32, B.BF16])
+def test_qkv_epilogue_rope_and_append(cache_dtype):
+    """Fused q|k|v projection: RoPE on q and k, append of k and v at positions lengths[s] + t (paged)."""
+    rng = np.random.default_rng(11)
+    B_, L, H, HK, hd, cap = 3, 4, 6, 2, 32, 100
+    D, KV = H * hd, HK * hd
+    x = rng.standard_normal((B_ * L, D), dtype=np.float32)
+    w = (0.05 * rng.standard_normal((D + 2 * KV, D), dtype=np.float32)).astype(np.float32)
+    cos, sin = oracle.rope_tables(hd, cap)
+    cache = Cache(cache_dtype, B_, HK, hd, cap)
+    lengths = np.array([0, 61, 70], dtype=np.int32)   # crosses the 64-token page boundary
+    cache.set_lengths(lengths)
+    cd, sd = dev(cos), dev(sin)
+    q = torch.zeros((B_ * L, D), dtype=torch.float32, device="cuda")
+    args = B.QkvArgs(H, HK, hd, L, cd.data_ptr(), sd.data_ptr(), cap, cache.h.value, q.data_ptr(), 0, 0.0, None, None, None)
+    run_linear(x, w, epilogue=3, qkv=args)
+    y = oracle.linear(x, w)
+    for b in range(B_):
+        rows = y[b * L:(b + 1) * L]
+        qb = rows[:, :D].reshape(1, L, H, hd).transpose(0, 2, 1, 3)
+        kb = rows[:, D:D + KV].reshape(1, L, HK, hd).transpose(0, 2, 1, 3)
+        vb = rows[:, D + KV:].reshape(1, L, HK, hd).transpose(0, 2, 1, 3)
+        q_want = oracle.rotary(qb, 10000.0, cap, int(lengths[b])).transpose(0, 2, 1, 3).reshape(L, D)
+        k_want = oracle.rotary(kb, 10000.0, cap, int(lengths[b]))[0]
+        assert rel(q.cpu().numpy()[b * L:(b + 1) * L], q_want) < 1e-5
+        end = int(lengths[b]) + L
+        got_k = cache.gather(0, end)[b][:, lengths[b]:end]
+        got_v = cache.gather(1, end)[b][:, lengths[b]:end]
+        tol = 1e-5 if cache_dtype == B.F32 else 5e-3
+        assert rel(got_k, k_want) < tol and rel(got_v, vb[0]) < tol
+
+
+def attention(q, cache, L, heads, max_length, causal=1):
+    rows = q.shape[0]
+    s, hk, hd, cap = cache.shape
+    qd = dev(q)
+    need = B.lib().b200_attention_scratch_bytes(rows, heads, hk, hd, max_length, 64)
+    scratch = torch.empty((need,), dtype=torch.uint8, device="cuda")
+    out = torch.zeros((rows, heads * hd), dtype=torch.float32, device="cuda")
+    torch.cuda.synchronize()
+    B.kcheck(B.lib().b200_attention_decode(qd.data_ptr(), rows, L, heads, cache.h, max_length, causal, scratch.data_ptr(), need,
+                                           out.data_ptr(), stream()))
+    sync()
+    status = C.c_int32()
+    B.kcheck(B.lib().b200_take_device_status(0, stream(), C.byref(status)))
+    assert status.value == 0
+    return out.cpu().numpy()
+
+
+@pytest.mark.parametrize("cache_dtype,hd,heads,kv_heads,lengths", [
+    (B.F32, 32, 8, 2, [1, 37, 64, 65, 200]),          # generic path, C1 head shape
+    (B.F32, 16, 4, 4, [5, 130]),
+    (B.BF16, 64, 12, 4, [1, 63, 64, 65, 700]),        # tensor-core path, C2 head shape (G = 3)
+    (B.BF16, 128, 32, 8, [17, 128, 1000, 2500]),      # tensor-core path, C3/C5 head shape (G = 4), several splits
+    (B.BF16, 128, 8, 8, [300]),                        # G = 1
+    (B.BF16, 64, 16, 1, [129, 77]),                    # G = 16
+    (B.BF16, 32, 8, 2, [40, 90]),                      # bf16 pool on the generic path
+])
+def test_decode_attention_ragged(cache_dtype, hd, heads, kv_heads, lengths):
+    """One new token per sequence, per-sequence context lengths, shuffled physical pages."""
+    rng = np.random.default_rng(hd + heads + len(lengths))
+    n = len(lengths)
+    cap = max(lengths)
+    cache = Cache(cache_dtype, n, kv_heads, hd, cap)
+    pages = cache.pages_per_sequence() * n
+    cache.set_page_table(rng.permutation(pages).astype(np.int32))
+    k = rng.standard_normal((n, kv_heads, cap, hd), dtype=np.float32)
+    v = rng.standard_normal((n, kv_heads, cap, hd), dtype=np.float32)
+    cache.set_lengths(np.zeros(n, dtype=np.int32))
+    cache.append(k, v)
+    # the kernel's rule for L == 1: row s sees keys 0 .. lengths[s] (the new token included)
+    cache.set_lengths(np.array(lengths, dtype=np.int32) - 1)
+    q = rng.standard_normal((n, heads, hd), dtype=np.float32)
+    got = attention(q, cache, 1, heads, cap)
+    if cache_dtype == B.BF16:
+        k, v = W.bf16_to_f32(W.bf16_bits(k)), W.bf16_to_f32(W.bf16_bits(v))
+    for s, length in enumerate(lengths):
+        want = oracle.gqa_attention(q[s][None, :, None, :], k[s:s + 1, :, :length], v[s:s + 1, :, :length])
+        tol = 1e-5 if cache_dtype == B.F32 else 1e-2
+        assert rel(got[s].reshape(heads, hd), want[0, :, 0, :]) < tol, (s, length)
+
+
+@pytest.mark.parametrize("cache_dtype,hd", [(B.F32, 32), (B.BF16, 64)])
+def test_chunk_attention_is_causal(cache_dtype, hd):
+    """L new tokens per sequence appended to a prefix: row l sees keys 0 .. prefix + l."""
+    rng = np.random.default_rng(23)
+    n, L, heads, kv_heads, prefix = 2, 5, 4, 2, 70
+    cap = prefix + L
+    cache = Cache(cache_dtype, n, kv_heads, hd, cap)
+    k = rng.standard_normal((n, kv_heads, cap, hd), dtype=np.float32)
+    v = rng.standard_normal((n, kv_heads, cap, hd), dtype=np.float32)
+    cache.append(k, v)
+    cache.set_lengths(np.full(n, prefix, dtype=np.int32))
+    q = rng.standard_normal((n * L, heads, hd), dtype=np.float32)
+    got = attention(q, cache, L, heads, cap).reshape(n, L, heads, hd)
+    if cache_dtype == B.BF16:
+        k, v = W.bf16_to_f32(W.bf16_bits(k)), W.bf16_to_f32(W.bf16_bits(v))
+    want = oracle.gqa_attention(q.reshape(n, L, heads, hd).transpose(0, 2, 1, 3), k, v, causal_offset=prefix)
+    assert rel(got, want.transpose(0, 2, 1, 3)) < (1e-5 if cache_dtype == B.F32 else 1e-2)
+
+
+def test_attention_linearity_in_values_at_long_context():
+    """Size-independent property at a context the oracle would take minutes for: attention is linear in V, and
+    with all keys equal it returns the mean of V."""
+    rng = np.random.default_rng(31)
+    n, heads, kv_heads, hd, length = 2, 32, 8, 128, 20000
+    cache = Cache(B.BF16, n, kv_heads, hd, length)
+    k = np.broadcast_to(rng.standard_normal((n, kv_heads, 1, hd), dtype=np.float32), (n, kv_heads, length, hd)).copy()
+    v = W.bf16_to_f32(W.bf16_bits(rng.standard_normal((n, kv_heads, length, hd), dtype=np.float32)))
+    cache.append(k, v)
+    cache.set_lengths(np.full(n, length - 1, dtype=np.int32))
+    q = rng.standard_normal((n, heads, hd), dtype=np.float32)
+    got = attention(q, cache, 1, heads, length).reshape(n, heads, hd)
+    mean = v.mean(axis=2)                                   # [n, kv_heads, hd]
+    want = np.repeat(mean, heads // kv_heads, axis=1)
+    assert np.abs(got - want).max() < 2e-3
+
+
+def test_rotary_permute_feedback_helpers():
+    rng = np.random.default_rng(41)
+    x = rng.standard_normal((3, 2, 4, 16), dtype=np.float32)
+    cos, sin = oracle.rope_tables(16, 12)
+    xd, cd, sd = dev(x), dev(cos[3:7]), dev(sin[3:7])
+    y = torch.empty_like(xd)
+    torch.cuda.synchronize()
+    B.kcheck(B.lib().b200_rotary(xd.data_ptr(), 6, 4, 16, cd.data_ptr(), sd.data_ptr(), y.data_ptr(), stream()))
+    sync()
+    assert np.array_equal(y.cpu().numpy(), oracle.rotary(x, 10000.0, 12, 3))
+    p = torch.empty((3, 4, 2, 16), dtype=torch.float32, device="cuda")
+    torch.cuda.synchronize()
+    B.kcheck(B.lib().b200_permute_0213(xd.data_ptr(), 3, 2, 4, 16, p.data_ptr(), stream()))
+    sync()
+    assert np.array_equal(p.cpu().numpy(), x.transpose(0, 2, 1, 3))

@@ -1,0 +1,88 @@
+"""CPU-side checks of the shipped library: it loads without a GPU or driver, exports every symbol the headers
+under include/ declare, and refuses to compute without a CUDA device (no CPU fallback)."""
+import ctypes as C
+import os
+import re
+
+import numpy as np
+import pytest
+
+import ctorch_b200 as B
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def declared_symbols():
+    names = []
+    for header in ("ctorch_b200_c_api.h", "ctorch_b200_kernels.h"):
+        text = open(os.path.join(ROOT, "include", header)).read()
+        names += [n for n in re.findall(r"(?:DL_API|B200_API)[^;(]*?\b(\w+)\s*\(", text) if n != "__attribute__"]
+    return names
+
+
+def test_library_exports_every_declared_symbol():
+    lib = B.lib()
+    names = declared_symbols()
+    assert len(names) > 90
+    missing = [n for n in names if not hasattr(lib, n)]
+    assert not missing, missing
+    assert lib.dl_version() == b"0.3.0"
+
+
+def test_python_binding_declares_every_symbol():
+    lib = B.lib()
+    undeclared = [n for n in declared_symbols() if getattr(lib, n).argtypes is None]
+    assert not undeclared, undeclared
+
+
+def test_host_tensors_are_containers():
+    x = np.arange(24, dtype=np.float32).reshape(2, 3, 4)
+    t = B.Tensor.from_numpy(x)
+    assert t.shape == (2, 3, 4) and t.dtype == B.F32 and t.device.type == B.CPU
+    assert np.array_equal(t.numpy(), x)
+    assert np.array_equal(t.select(1, 2).numpy(), x[:, 2])
+    assert np.array_equal(t.narrow(2, 1, 2).numpy(), x[:, :, 1:3])
+    assert np.array_equal(t.narrow(0, 1, 1).numpy(), x[1:2])
+
+
+def test_modules_build_on_the_host_with_reference_state_names():
+    dec = C.c_void_p()
+    B.check(B.lib().dl_transformer_decoder_create(2, 8, 4, 2, 12, 16, B.options(B.BF16), C.byref(dec)))
+    module = B.Module(dec)
+    names = module.state_names()
+    expected = []
+    for i in range(2):
+        p = f"layer{i}."
+        expected += [p + "attention.query.weight", p + "attention.key.weight", p + "attention.value.weight",
+                     p + "attention.output.weight", p + "feedforward.gate.weight", p + "feedforward.up.weight",
+                     p + "feedforward.down.weight", p + "attention_norm.weight", p + "feedforward_norm.weight"]
+    expected.append("normalization.weight")
+    assert [n for n in names if "rotary" not in n] == expected
+    assert [n for n in names if "rotary" in n] == ["layer0.attention.rotary.cosine", "layer0.attention.rotary.sine",
+                                                   "layer1.attention.rotary.cosine", "layer1.attention.rotary.sine"]
+    state = module.state()
+    assert state["layer0.attention.key.weight"].shape == (4, 8) and state["layer0.attention.key.weight"].dtype == B.BF16
+    assert state["layer0.attention.rotary.cosine"].dtype == B.F32
+    # a state with a wrong shape is rejected and names the entry
+    state["normalization.weight"] = B.Tensor.from_numpy(np.ones(7, dtype=np.uint16), dtype=B.BF16)
+    with pytest.raises(B.B200Error, match="normalization.weight"):
+        module.load_state(state)
+
+
+def test_argument_errors_follow_the_reference_messages():
+    dec = C.c_void_p(1)
+    assert B.lib().dl_transformer_decoder_create(0, 8, 4, 2, 12, 16, B.options(B.F32), C.byref(dec)) == 1
+    assert not dec.value and b"at least one layer" in B.lib().dl_last_error()
+    assert B.lib().dl_transformer_decoder_create(1, 8, 3, 2, 12, 16, B.options(B.F32), C.byref(dec)) == 1
+    assert b"divide evenly" in B.lib().dl_last_error()
+    assert B.lib().dl_transformer_decoder_create(1, 8, 4, 2, 12, 16, B.options(B.F64), C.byref(dec)) == 1
+    assert b"f32 or bf16" in B.lib().dl_last_error()
+
+
+def test_no_cpu_fallback():
+    """Operators on host tensors fail loudly instead of computing on the CPU."""
+    x = B.Tensor.from_numpy(np.ones((2, 8), dtype=np.float32))
+    w = B.Tensor.from_numpy(np.ones((4, 8), dtype=np.float32))
+    out = C.c_void_p()
+    assert B.lib().dl_linear(x.h, w.h, None, C.byref(out)) == 1
+    assert b"no CPU compute path" in B.lib().dl_last_error()
