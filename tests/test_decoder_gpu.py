@@ -167,12 +167,8 @@ def test_adapters_match_oracle(dtype):
         assert rel(model.decode_ids(ids[:, lo:hi]), port.decode_ids(ids[:, lo:hi])) < tolerance(spec)
     # without adapters the answer differs (the adapters are not a no-op)
     plain = B.DecoderModel(spec, weights)
-    assert rel(plain.decode_ids(ids[:, :5]), port.decode_ids(ids[:, :5]) if False else model_first(port, ids)) > 1e-3
-
-
-def model_first(port, ids):
     port.new_cache()
-    return port.decode_ids(ids[:, :5])
+    assert rel(plain.decode_ids(ids[:, :5]), port.decode_ids(ids[:, :5])) > 1e-3
 
 
 def test_lora_module_forward_and_merge():
@@ -184,7 +180,8 @@ def test_lora_module_forward_and_merge():
     x = rng.standard_normal((3, 40), dtype=np.float32)
     dev = B.cuda(0)
     base, adapter, merged = C.c_void_p(), C.c_void_p(), C.c_void_p()
-    B.check(l.dl_linear_from_tensors(B.Tensor.from_numpy(w, device=dev).h, None, C.byref(base)))
+    weight = B.Tensor.from_numpy(w, device=dev)   # must outlive the call that reads its handle
+    B.check(l.dl_linear_from_tensors(weight.h, None, C.byref(base)))
     B.check(l.dl_lora_linear_create(base, 4, 8.0, C.byref(adapter)))
     adapter = B.Module(adapter)
     st = adapter.state()
