@@ -123,6 +123,7 @@ def _declare(l: C.CDLL) -> None:
         "b200_linear": (C.c_int, [vp, i64, i64, vp, i32, i64, vp, i32, C.c_double, C.c_int, vp, C.POINTER(QkvArgs), vp, vp]),
         "b200_attention_scratch_bytes": (sz, [i64, i32, i32, i32, i32, i32]),
         "b200_attention_decode": (C.c_int, [vp, i64, i32, i32, vp, i32, i32, vp, sz, vp, vp]),
+        "b200_attention_decode_static": (C.c_int, [vp, i64, i32, i32, vp, i32, i32, vp, vp]),
         "b200_argmax": (C.c_int, [vp, i64, i64, vp, vp]), "b200_select_rows": (C.c_int, [vp, i64, i64, i64, i64, vp, vp]),
         "b200_rotary": (C.c_int, [vp, i64, i64, i64, vp, vp, vp, vp]),
         "b200_permute_0213": (C.c_int, [vp, i64, i64, i64, i64, vp, vp]),

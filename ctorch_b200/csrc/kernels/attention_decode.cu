@@ -20,6 +20,7 @@
 #include "kv_cache.cuh"
 
 #include <cmath>
+#include <mutex>
 
 namespace b200 {
 namespace {
@@ -459,4 +460,58 @@ extern "C" int b200_attention_decode(const float* q, int64_t rows, int32_t token
     if (status != B200_OK || plan.num_splits == 1) return status;
     attention_combine_kernel<<<static_cast<unsigned>(rows) * heads, 128, 0, s>>>(p);
     return cuda_status(cudaGetLastError(), "attention_combine_kernel launch");
+}
+
+// ---- allocation-free variant ------------------------------------------------------------------------------
+// Split partials live in this fixed array of the library image instead of a caller workspace.  In host code the
+// name below is only a handle for the runtime: the device address comes from cudaGetSymbolAddress, looked up once
+// per device with that device current, and that address is what the kernels receive.
+static __device__ __align__(256) unsigned char attention_static_scratch[B200_STATIC_SCRATCH_BYTES];
+
+namespace {
+std::mutex static_scratch_mutex;
+void* static_scratch_address[64];
+
+int static_scratch_for(int device, void** address) {
+    std::lock_guard<std::mutex> lock(static_scratch_mutex);
+    if (device < 0 || device >= 64) { set_error("b200_attention_decode_static: device %d out of range", device); return B200_BAD_ARGUMENT; }
+    if (!static_scratch_address[device]) {
+        int current = -1;
+        B200_CUDA(cudaGetDevice(&current));
+        if (current != device) B200_CUDA(cudaSetDevice(device));
+        void* found = nullptr;
+        const cudaError_t status = cudaGetSymbolAddress(&found, attention_static_scratch);
+        if (current != device) cudaSetDevice(current);
+        if (status != cudaSuccess || !found) return cuda_status(status == cudaSuccess ? cudaErrorInvalidSymbol : status,
+                                                                "cudaGetSymbolAddress(attention_static_scratch)");
+        static_scratch_address[device] = found;
+    }
+    *address = static_scratch_address[device];
+    return B200_OK;
+}
+}  // namespace
+
+extern "C" int b200_attention_decode_static(const float* q, int64_t rows, int32_t tokens_per_sequence, int32_t heads,
+                                            const b200_kv_cache* cache, int32_t max_length, int32_t causal, float* out,
+                                            void* stream) {
+    if (!cache || rows <= 0 || heads <= 0 || max_length <= 0) {
+        set_error("b200_attention_decode_static: bad pointer or size");
+        return B200_BAD_ARGUMENT;
+    }
+    const int32_t bounded = max_length > cache->capacity ? cache->capacity : max_length;
+    const size_t need = b200_attention_scratch_bytes(rows, heads, cache->kv_heads, cache->head_dim, bounded, cache->page_size);
+    if (need > B200_STATIC_SCRATCH_BYTES) {
+        set_error("b200_attention_decode_static: this shape needs %zu bytes of split partials, the built-in array holds %u; "
+                  "call b200_attention_decode with a workspace of your own", need, static_cast<unsigned>(B200_STATIC_SCRATCH_BYTES));
+        return B200_BAD_ARGUMENT;
+    }
+    if (!device_status_word_if_allocated(cache->device)) {
+        set_error("b200_attention_decode_static: no status word on device %d (create the KV cache through b200_kv_cache_create)", cache->device);
+        return B200_BAD_ARGUMENT;
+    }
+    void* scratch = nullptr;
+    const int status = static_scratch_for(cache->device, &scratch);
+    if (status != B200_OK) return status;
+    return b200_attention_decode(q, rows, tokens_per_sequence, heads, cache, max_length, causal, scratch,
+                                 B200_STATIC_SCRATCH_BYTES, out, stream);
 }

@@ -27,6 +27,8 @@ inline cudaStream_t as_stream(void* stream) { return static_cast<cudaStream_t>(s
 
 // Device-resident health word (one per device), set by kernels that abandon a bounded wait.
 int32_t* device_status_word(int device);
+// The same word if it already exists (it is created with the first KV cache of a device), else nullptr; never allocates.
+int32_t* device_status_word_if_allocated(int device);
 
 // ---- device helpers -------------------------------------------------------------------------------------
 __device__ __forceinline__ float bf16_lo(uint32_t packed) { return __uint_as_float(packed << 16); }

@@ -42,6 +42,11 @@ int32_t* device_status_word(int device) {
     return status_words[device];
 }
 
+int32_t* device_status_word_if_allocated(int device) {
+    std::lock_guard<std::mutex> lock(status_mutex);
+    return device >= 0 && device < 64 ? status_words[device] : nullptr;
+}
+
 encode_tiled_fn tensor_map_encoder() {
     static encode_tiled_fn cached = [] {
         void* entry = nullptr;

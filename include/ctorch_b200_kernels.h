@@ -133,6 +133,26 @@ B200_API int b200_attention_decode(const float* q, int64_t rows, int32_t tokens_
                                    const b200_kv_cache* cache, int32_t max_length, int32_t causal, void* scratch,
                                    size_t scratch_bytes, float* out, void* stream);
 
+/* No counterpart in the reference.  b200_attention_decode for callers that must not allocate and have no workspace
+ * of their own to hand in: a serving loop whose device memory was budgeted once at start-up, a host runtime whose
+ * device memory belongs to a pool it does not control (the reference keeps such a per-device pool), or code for
+ * which the implicit device-wide synchronisation of cudaMalloc/cudaFree is not acceptable on the token path.
+ * Same arguments and results as b200_attention_decode, minus the scratch: the split partials go to a fixed
+ * B200_STATIC_SCRATCH_BYTES array that is part of the library image (every GPU that loads the library holds that
+ * much memory until the process exits).  The call allocates nothing and frees nothing.
+ *   - Shapes whose partials need more than B200_STATIC_SCRATCH_BYTES are rejected with B200_BAD_ARGUMENT and a
+ *     message that states both sizes; use b200_attention_decode with your own workspace for those.
+ *   - The first call on a device looks up the array's device address (once per device, with that device current);
+ *     make that first call during set-up, before any stream capture is started.
+ *   - All calls on a device share the one array and it keeps the previous call's contents.  Nothing in it has to
+ *     start at zero: every split partial that the merge step reads was written by the same call.  Two calls that
+ *     overlap on the GPU (different streams, or several host threads) race on the array: serialise them.
+ *   - The KV cache object must exist before the call (creating it is where the per-device status word is allocated). */
+#define B200_STATIC_SCRATCH_BYTES (8u << 20)
+B200_API int b200_attention_decode_static(const float* q, int64_t rows, int32_t tokens_per_sequence, int32_t heads,
+                                          const b200_kv_cache* cache, int32_t max_length, int32_t causal, float* out,
+                                          void* stream);
+
 /* dl::argmax along the last axis (src/ops/reduction.cpp:95-110; rule src/kernels/cpu/reduction.cpp:141-145:
  * first maximum wins, the first NaN wins over everything after it). */
 B200_API int b200_argmax(const float* x, int64_t rows, int64_t width, int64_t* index, void* stream);
