@@ -101,6 +101,9 @@ __global__ void __launch_bounds__(kFastThreads) attention_mma_kernel(const __gri
     uint64_t* full = reinterpret_cast<uint64_t*>(smem + S::stages * S::stage_bytes);
     uint64_t* empty = full + S::stages;
 
+    const int trace = trace_begin(20);
+    grid_dependency_wait();   // q, the cache and the lengths come from the preceding kernels
+    grid_launch_dependents();
     const int item = blockIdx.x, split = blockIdx.y;
     const int row = item / p.kv.kv_heads, kvh = item % p.kv.kv_heads;
     const int sequence = row / p.tokens_per_sequence;
@@ -108,7 +111,7 @@ __global__ void __launch_bounds__(kFastThreads) attention_mma_kernel(const __gri
     const int page_begin = split * p.pages_per_split;
     int page_end = (kv_len + kFastPageSize - 1) / kFastPageSize;
     if (page_end > page_begin + p.pages_per_split) page_end = page_begin + p.pages_per_split;
-    if (page_begin >= page_end) return;  // uniform for the CTA
+    if (page_begin >= page_end) { trace_end(trace); return; }  // uniform for the CTA
     const int pages = page_end - page_begin;
     const int group = p.heads / p.kv.kv_heads;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -301,6 +304,7 @@ __global__ void __launch_bounds__(kFastThreads) attention_mma_kernel(const __gri
             }
         }
     }
+    trace_end(trace);
 }
 
 // Generic path: one (row, head) per CTA, four warps stride over the tokens of the split.
@@ -310,6 +314,8 @@ constexpr int kMaxDimsPerLane = 8;  // head_dim <= 256
 __global__ void __launch_bounds__(kGenericThreads) attention_generic_kernel(const AttnParams p) {
     __shared__ float merge_ml[4][2];
     extern __shared__ float merge_o[];  // [4][head_dim]
+    grid_dependency_wait();
+    grid_launch_dependents();
     const int hd = p.kv.head_dim;
     const int item = blockIdx.x, split = blockIdx.y;
     const int row = item / p.heads, head = item % p.heads;
@@ -380,6 +386,9 @@ __global__ void __launch_bounds__(kGenericThreads) attention_generic_kernel(cons
 
 // Merge of the split partials: one (row, head) per CTA.
 __global__ void attention_combine_kernel(const AttnParams p) {
+    const int trace = trace_begin(21);
+    grid_dependency_wait();
+    grid_launch_dependents();
     const int hd = p.kv.head_dim;
     const int64_t head_item = blockIdx.x;
     const int row = static_cast<int>(head_item / p.heads);
@@ -398,6 +407,7 @@ __global__ void attention_combine_kernel(const AttnParams p) {
         for (int s = 0; s < valid; ++s) acc += expf(ml[2 * s] - m) * p.part_o[(head_item * p.num_splits + s) * hd + d];
         p.out[head_item * hd + d] = acc / l;
     }
+    trace_end(trace);
 }
 
 template <int HD> int launch_fast(const b200_kv_cache* cache, const AttnParams& p, cudaStream_t stream) {
@@ -405,8 +415,8 @@ template <int HD> int launch_fast(const b200_kv_cache* cache, const AttnParams& 
     auto kernel = attention_mma_kernel<HD>;
     B200_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, S::smem_bytes));
     const dim3 grid(static_cast<unsigned>(p.rows) * p.kv.kv_heads, p.num_splits);
-    kernel<<<grid, kFastThreads, S::smem_bytes, stream>>>(*kv_tensor_map(cache, 0), *kv_tensor_map(cache, 1), p);
-    return cuda_status(cudaGetLastError(), "attention_mma_kernel launch");
+    return cuda_status(launch_dependent(kernel, grid, dim3(kFastThreads), S::smem_bytes, stream, *kv_tensor_map(cache, 0),
+                                        *kv_tensor_map(cache, 1), p), "attention_mma_kernel launch");
 }
 
 }  // namespace
@@ -454,12 +464,12 @@ extern "C" int b200_attention_decode(const float* q, int64_t rows, int32_t token
         status = cache->head_dim == 128 ? launch_fast<128>(cache, p, s) : launch_fast<64>(cache, p, s);
     } else {
         const dim3 grid(static_cast<unsigned>(rows) * heads, plan.num_splits);
-        attention_generic_kernel<<<grid, kGenericThreads, sizeof(float) * 4 * cache->head_dim, s>>>(p);
-        status = cuda_status(cudaGetLastError(), "attention_generic_kernel launch");
+        status = cuda_status(launch_dependent(attention_generic_kernel, grid, dim3(kGenericThreads), sizeof(float) * 4 * cache->head_dim, s, p),
+                             "attention_generic_kernel launch");
     }
     if (status != B200_OK || plan.num_splits == 1) return status;
-    attention_combine_kernel<<<static_cast<unsigned>(rows) * heads, 128, 0, s>>>(p);
-    return cuda_status(cudaGetLastError(), "attention_combine_kernel launch");
+    return cuda_status(launch_dependent(attention_combine_kernel, dim3(static_cast<unsigned>(rows) * heads), dim3(128), 0, s, p),
+                       "attention_combine_kernel launch");
 }
 
 // ---- allocation-free variant ------------------------------------------------------------------------------

@@ -21,6 +21,8 @@ __global__ void fill_lengths_kernel(int32_t* lengths, int n, int32_t value) {
 
 struct AdvanceList { int32_t* lengths[64]; int32_t counts[64]; };
 __global__ void advance_kernel(AdvanceList list, int caches, int32_t delta) {
+    grid_dependency_wait();   // earlier kernels of the step still read the old lengths
+    grid_launch_dependents();
     const int c = blockIdx.x;
     if (c >= caches) return;
     for (int i = threadIdx.x; i < list.counts[c]; i += blockDim.x) list.lengths[c][i] += delta;
@@ -179,8 +181,7 @@ int b200_kv_cache_advance(b200_kv_cache* const* caches, int32_t count, int32_t d
         AdvanceList list{};
         const int n = count - first < 64 ? count - first : 64;
         for (int i = 0; i < n; ++i) { list.lengths[i] = caches[first + i]->lengths; list.counts[i] = caches[first + i]->sequences; }
-        advance_kernel<<<n, 128, 0, as_stream(stream)>>>(list, n, delta);
-        const int status = cuda_status(cudaGetLastError(), "advance_kernel launch");
+        const int status = cuda_status(launch_dependent(advance_kernel, dim3(n), dim3(128), 0, as_stream(stream), list, n, delta), "advance_kernel launch");
         if (status != B200_OK) return status;
     }
     return B200_OK;

@@ -1,0 +1,93 @@
+// Operands and epilogues shared by the skinny-linear kernels.
+#pragma once
+
+#include "common.cuh"
+#include "kv_cache.cuh"
+
+namespace b200 {
+
+struct LinearParams {
+    const float* x;
+    int rows, in, out;
+    const void* weight;
+    const void* norm_weight;
+    int norm_dtype, weight_dtype;
+    double eps;
+    const float* residual;
+    float* y;
+    // B200_EPI_QKV
+    int heads, kv_heads, head_dim, tokens_per_sequence, context;
+    const float *cosine, *sine;
+    KvView kv;
+    float* q_out;
+    int lora_rank;
+    float lora_scale;
+    const float* low;
+    const void *q_up, *v_up;
+};
+
+// Finishes one pair of adjacent output features (feature0 even) of activation row `row`.
+//   store | residual add (src/nn/decoder.cpp:104-105) | SiLU(gate)*up on interleaved rows (src/nn/decoder.cpp:16) |
+//   q|k|v: adapter delta (src/nn/decoder.cpp:26-28), adjacent-pair RoPE (src/ops/contraction.cpp:44-49), q store,
+//   k/v append to the paged cache (src/nn/kv_cache.cpp:24-28)
+template <int EPI>
+__device__ __forceinline__ void linear_epilogue(const LinearParams& p, int row, int feature0, float a, float b) {
+    const bool second = feature0 + 1 < p.out;
+    if constexpr (EPI == B200_EPI_STORE) {
+        p.y[static_cast<int64_t>(row) * p.out + feature0] = a;
+        if (second) p.y[static_cast<int64_t>(row) * p.out + feature0 + 1] = b;
+    } else if constexpr (EPI == B200_EPI_RESIDUAL) {
+        const int64_t at = static_cast<int64_t>(row) * p.out + feature0;
+        p.y[at] = __fadd_rn(p.residual[at], a);
+        if (second) p.y[at + 1] = __fadd_rn(p.residual[at + 1], b);
+    } else if constexpr (EPI == B200_EPI_SWIGLU) {
+        // rows 2j (gate_j) and 2j+1 (up_j) of the interleaved weight
+        p.y[static_cast<int64_t>(row) * (p.out >> 1) + (feature0 >> 1)] = __fmul_rn(silu_reference(a), b);
+    } else {
+        const int D = p.heads * p.head_dim, KV = p.kv_heads * p.head_dim;
+        const int sequence = row / p.tokens_per_sequence;
+        const int position = p.kv.lengths[sequence] + row % p.tokens_per_sequence;
+        int region = 0, local = feature0;  // 0 = q, 1 = k, 2 = v
+        if (local >= D) { region = 1; local -= D; }
+        if (region == 1 && local >= KV) { region = 2; local -= KV; }
+        if (p.lora_rank > 0 && region != 1) {
+            // LoRALinear::forward: base + up(down(x)) * f32(alpha/rank)
+            const float* low = p.low + static_cast<int64_t>(row) * 2 * p.lora_rank + (region == 2 ? p.lora_rank : 0);
+            const void* up = region == 0 ? p.q_up : p.v_up;
+            float da = 0.0f, db = 0.0f;
+            for (int j = 0; j < p.lora_rank; ++j) {
+                const int64_t at = static_cast<int64_t>(local) * p.lora_rank + j;
+                const float ua = p.weight_dtype == B200_BF16 ? load_as_f32(static_cast<const __nv_bfloat16*>(up), at)
+                                                           : load_as_f32(static_cast<const float*>(up), at);
+                const float ub = p.weight_dtype == B200_BF16 ? load_as_f32(static_cast<const __nv_bfloat16*>(up), at + p.lora_rank)
+                                                           : load_as_f32(static_cast<const float*>(up), at + p.lora_rank);
+                da = __fadd_rn(da, __fmul_rn(low[j], ua));
+                db = __fadd_rn(db, __fmul_rn(low[j], ub));
+            }
+            a = __fadd_rn(a, __fmul_rn(da, p.lora_scale));
+            b = __fadd_rn(b, __fmul_rn(db, p.lora_scale));
+        }
+        const int head = local / p.head_dim, d = local % p.head_dim;
+        if (region != 2 && position < p.context) {
+            // adjacent-pair rotation, each product rounded before the add (src/ops/contraction.cpp:44-49)
+            const float c = p.cosine[static_cast<int64_t>(position) * (p.head_dim >> 1) + (d >> 1)];
+            const float s = p.sine[static_cast<int64_t>(position) * (p.head_dim >> 1) + (d >> 1)];
+            const float even = a, odd = b;
+            a = __fsub_rn(__fmul_rn(even, c), __fmul_rn(odd, s));
+            b = __fadd_rn(__fmul_rn(even, s), __fmul_rn(odd, c));
+        }
+        if (region == 0) {
+            float* q = p.q_out + static_cast<int64_t>(row) * D + local;
+            q[0] = a;
+            q[1] = b;
+        } else {
+            kv_store_pair(p.kv, region - 1, sequence, position, head, d, a, b);
+        }
+    }
+}
+
+// Tensor-core streaming kernel for bf16 weights (linear_stream.cu); returns B200_UNSUPPORTED when the shape is
+// outside what it handles, in which case the caller uses the CUDA-core kernel.
+int launch_linear_stream(const LinearParams& p, int epilogue, cudaStream_t stream);
+
+}  // namespace b200

@@ -7,8 +7,7 @@
 // Fused around the contraction (reference: src/nn/decoder.cpp:77-106 runs these as separate ops):
 //   prologue  RMSNorm of x in f64 (src/kernels/cpu/normalization.cpp:39-51)
 //   epilogue  store | residual add | SiLU(gate)*up on interleaved rows | RoPE + KV-cache append (+ LoRA delta)
-#include "common.cuh"
-#include "kv_cache.cuh"
+#include "linear_common.cuh"
 
 namespace b200 {
 namespace {
@@ -18,25 +17,6 @@ constexpr int kWarps = kThreads / 32;
 constexpr int kNF = 2;           // output features per warp (RoPE and SwiGLU consume adjacent pairs)
 constexpr int kChunk = 2048;     // activation columns staged per pass
 
-struct LinearParams {
-    const float* x;
-    int rows, in, out;
-    const void* weight;
-    const void* norm_weight;
-    int norm_dtype, weight_dtype;
-    double eps;
-    const float* residual;
-    float* y;
-    // B200_EPI_QKV
-    int heads, kv_heads, head_dim, tokens_per_sequence, context;
-    const float *cosine, *sine;
-    KvView kv;
-    float* q_out;
-    int lora_rank;
-    float lora_scale;
-    const float* low;
-    const void *q_up, *v_up;
-};
 
 template <class W> struct Vec;
 template <> struct Vec<__nv_bfloat16> { static constexpr int n = 8; };
@@ -180,59 +160,7 @@ __global__ void __launch_bounds__(kThreads) linear_small_kernel(const LinearPara
         if (lane != r) continue;
         const int row = row0 + r;
         if (row >= p.rows) continue;
-        const bool second = feature0 + 1 < p.out;
-        float a = acc[0][r], b = acc[1][r];
-        if constexpr (EPI == B200_EPI_STORE) {
-            p.y[static_cast<int64_t>(row) * p.out + feature0] = a;
-            if (second) p.y[static_cast<int64_t>(row) * p.out + feature0 + 1] = b;
-        } else if constexpr (EPI == B200_EPI_RESIDUAL) {
-            const int64_t at = static_cast<int64_t>(row) * p.out + feature0;
-            p.y[at] = __fadd_rn(p.residual[at], a);
-            if (second) p.y[at + 1] = __fadd_rn(p.residual[at + 1], b);
-        } else if constexpr (EPI == B200_EPI_SWIGLU) {
-            // rows 2j (gate_j) and 2j+1 (up_j) of the interleaved weight
-            p.y[static_cast<int64_t>(row) * (p.out >> 1) + (feature0 >> 1)] = __fmul_rn(silu_reference(a), b);
-        } else {
-            const int D = p.heads * p.head_dim, KV = p.kv_heads * p.head_dim;
-            const int sequence = row / p.tokens_per_sequence;
-            const int position = p.kv.lengths[sequence] + row % p.tokens_per_sequence;
-            int region = 0, local = feature0;  // 0 = q, 1 = k, 2 = v
-            if (local >= D) { region = 1; local -= D; }
-            if (region == 1 && local >= KV) { region = 2; local -= KV; }
-            if (p.lora_rank > 0 && region != 1) {
-                // LoRALinear::forward: base + up(down(x)) * f32(alpha/rank)
-                const float* low = p.low + static_cast<int64_t>(row) * 2 * p.lora_rank + (region == 2 ? p.lora_rank : 0);
-                const void* up = region == 0 ? p.q_up : p.v_up;
-                float da = 0.0f, db = 0.0f;
-                for (int j = 0; j < p.lora_rank; ++j) {
-                    const int64_t at = static_cast<int64_t>(local) * p.lora_rank + j;
-                    const float ua = p.weight_dtype == B200_BF16 ? load_as_f32(static_cast<const __nv_bfloat16*>(up), at)
-                                                               : load_as_f32(static_cast<const float*>(up), at);
-                    const float ub = p.weight_dtype == B200_BF16 ? load_as_f32(static_cast<const __nv_bfloat16*>(up), at + p.lora_rank)
-                                                               : load_as_f32(static_cast<const float*>(up), at + p.lora_rank);
-                    da = __fadd_rn(da, __fmul_rn(low[j], ua));
-                    db = __fadd_rn(db, __fmul_rn(low[j], ub));
-                }
-                a = __fadd_rn(a, __fmul_rn(da, p.lora_scale));
-                b = __fadd_rn(b, __fmul_rn(db, p.lora_scale));
-            }
-            const int head = local / p.head_dim, d = local % p.head_dim;
-            if (region != 2 && position < p.context) {
-                // adjacent-pair rotation, each product rounded before the add (src/ops/contraction.cpp:44-49)
-                const float c = p.cosine[static_cast<int64_t>(position) * (p.head_dim >> 1) + (d >> 1)];
-                const float s = p.sine[static_cast<int64_t>(position) * (p.head_dim >> 1) + (d >> 1)];
-                const float even = a, odd = b;
-                a = __fsub_rn(__fmul_rn(even, c), __fmul_rn(odd, s));
-                b = __fadd_rn(__fmul_rn(even, s), __fmul_rn(odd, c));
-            }
-            if (region == 0) {
-                float* q = p.q_out + static_cast<int64_t>(row) * D + local;
-                q[0] = a;
-                q[1] = b;
-            } else {
-                kv_store_pair(p.kv, region - 1, sequence, position, head, d, a, b);
-            }
-        }
+        linear_epilogue<EPI>(p, row, feature0, acc[0][r], acc[1][r]);
     }
 }
 
@@ -306,9 +234,14 @@ extern "C" int b200_linear(const float* x, int64_t rows, int64_t in, const void*
         p.lora_rank = qkv->lora_rank; p.lora_scale = qkv->lora_scale; p.low = qkv->low; p.q_up = qkv->q_up; p.v_up = qkv->v_up;
         if (p.lora_rank > 0 && (!p.low || !p.q_up || !p.v_up)) { set_error("b200_linear: adapter pointers missing"); return B200_BAD_ARGUMENT; }
     }
+    cudaStream_t s = as_stream(stream);
+    {
+        // bf16 weights with a moderate inner size go to the tensor-core streaming kernel
+        const int status = launch_linear_stream(p, epilogue, s);
+        if (status != B200_UNSUPPORTED) return status;
+    }
     const size_t element = weight_dtype == B200_BF16 ? 2 : 4;
     const bool vector = (in * element) % 16 == 0 && reinterpret_cast<uintptr_t>(weight) % 16 == 0;
-    cudaStream_t s = as_stream(stream);
     return weight_dtype == B200_BF16 ? pick_epilogue<__nv_bfloat16>(p, epilogue, vector, s)
                                      : pick_epilogue<float>(p, epilogue, vector, s);
 }

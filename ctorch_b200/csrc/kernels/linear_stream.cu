@@ -1,0 +1,364 @@
+// Streaming skinny linear for bf16 weights and up to 16 activation rows per tile (the decode batch):
+// y = epilogue(rmsnorm?(x) @ W^T).  The work is weight streaming, so the kernel is built around keeping many
+// kilobytes of weights in flight per SM:
+//   * persistent CTAs (one per SM) walk feature tiles of TF rows of W; a producer warp streams every tile through
+//     a ring of shared-memory slots with bulk TMA copies (cp.async.bulk, one per weight row, mbarrier completion,
+//     no multicast, no descriptor to fetch) and runs ahead across tile boundaries; the first slots are requested
+//     before the activations are touched, so DRAM latency overlaps the prologue; rows land with a padded stride
+//     so that ldmatrix reads them without bank conflicts;
+//   * the activation rows are staged once per CTA: RMSNorm in f64 (src/kernels/cpu/normalization.cpp:39-51 of the
+//     reference), then split into bf16 hi + bf16 lo so that the tensor cores see ~16 mantissa bits of the f32 value;
+//   * eight consumer warps split K: warp w takes the 16-column k-steps w, w+8, ... of every stage, multiplies the
+//     [16 x 16] activation fragments (hi and lo) with the [16 x TF] weight fragments using mma.sync m16n8k16 bf16
+//     with f32 accumulation (fragments via ldmatrix from the swizzled stage), and the per-warp partial sums are
+//     added through shared memory before the shared epilogue (linear_common.cuh) runs.
+// Rows beyond 16 are covered by blockIdx.y (weights then come from L2).  Shapes it does not take (f32 weights,
+// in > 2048 or in % 8 != 0) stay on the CUDA-core kernel.
+#include "linear_common.cuh"
+
+#include <mutex>
+#include <type_traits>
+
+#define B200_MARK(i) trace_mark(trace, (i))
+
+namespace b200 {
+namespace {
+
+constexpr int kConsumers = 8;
+constexpr int kThreads = (kConsumers + 1) * 32;
+constexpr int kRows = 16;
+constexpr int kMaxIn = 2048;
+
+struct StreamParams {
+    LinearParams base;
+    int tile_features;   // TF: 8, 16, 32 or 64
+    int slots;           // ring depth, one whole tile [TF][in_padded + 8] per slot
+    int tiles;           // ceil(out / TF)
+    int in_padded;       // in rounded up to 64
+    int32_t* status;
+};
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t address) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(address));
+}
+__device__ __forceinline__ void ldmatrix_x2(uint32_t (&r)[2], uint32_t address) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x2.shared.b16 {%0,%1}, [%2];" : "=r"(r[0]), "=r"(r[1]) : "r"(address));
+}
+__device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void consumer_barrier() { asm volatile("bar.sync 1, %0;" ::"n"(kConsumers * 32) : "memory"); }
+
+// 1-D bulk copy global -> shared of `bytes` (multiple of 16, both addresses 16-byte aligned), completion on an mbarrier.
+__device__ __forceinline__ void bulk_load(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar)) : "memory");
+}
+
+// Shared memory map (offsets from a 128-byte aligned base):
+//   [0, slots * slot_bytes)         weight tiles, [TF rows][in_padded + 8] bf16 each (row stride = 16 mod 128 bytes)
+//   then x_hi, x_lo                 [16][in_padded + 8] bf16 each
+//   then partial sums               [8 warps][16 rows][TF] f32
+//   then mbarriers                  full[slots], empty[slots]
+template <int TF, int EPI>
+__global__ void __launch_bounds__(kThreads, 2) linear_stream_kernel(const StreamParams sp) {
+    constexpr int NT = TF / 8;  // n-tiles of 8 features
+    const LinearParams& p = sp.base;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 127) & ~static_cast<uintptr_t>(127));
+    const int x_stride = sp.in_padded + 8;  // bf16 elements per staged row (activations and weights)
+    const int slot_bytes = TF * x_stride * 2;
+    uint8_t* slot_base = smem;
+    __nv_bfloat16* x_hi = reinterpret_cast<__nv_bfloat16*>(smem + sp.slots * slot_bytes);
+    __nv_bfloat16* x_lo = x_hi + kRows * x_stride;
+    float* partial = reinterpret_cast<float*>(x_lo + kRows * x_stride);
+    uint64_t* full = reinterpret_cast<uint64_t*>(partial + kConsumers * kRows * TF);
+    uint64_t* empty = full + sp.slots;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int row0 = blockIdx.y * kRows;
+    const int trace = trace_begin(EPI);
+    const int my_tiles = (sp.tiles - static_cast<int>(blockIdx.x) + static_cast<int>(gridDim.x) - 1) / static_cast<int>(gridDim.x);
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < sp.slots; ++s) {
+            mbar_init(&full[s], 1);
+            mbar_init(&empty[s], kConsumers);
+        }
+        mbar_fence_init();
+    }
+    // Columns in .. in_padded+8 of the weight slots are never written by the copies; the last k-step may read up to
+    // 8 of them, so they are cleared once (stale bit patterns could be NaN, and 0 * NaN is NaN).
+    if (p.in & 15) {
+        for (int i = threadIdx.x; i < sp.slots * TF; i += kThreads) {
+            __nv_bfloat16* row = reinterpret_cast<__nv_bfloat16*>(slot_base) + static_cast<size_t>(i) * x_stride;
+            for (int k = p.in; k < x_stride; ++k) row[k] = __float2bfloat16_rn(0.0f);
+        }
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy stores before async-proxy copies
+    }
+    __syncthreads();
+    grid_launch_dependents();  // the next kernel may start its own weight stream while this one computes
+
+    if (warp == kConsumers) {
+        // ---- producer: lane i requests rows i, i+32, ... of every tile; lane 0 owns the barriers ----
+        bool alive = true;
+        for (int t = 0; t < my_tiles && alive; ++t) {
+            const int tile = blockIdx.x + t * gridDim.x;
+            const int s = t % sp.slots;
+            const uint32_t phase = (t / sp.slots) & 1;
+            int rows = p.out - tile * TF;
+            if (rows > TF) rows = TF;
+            if (lane == 0) {
+                if (!mbar_wait(&empty[s], phase ^ 1)) {
+                    atomicExch(sp.status, B200_DEVICE_TIMEOUT);
+                    alive = false;
+                } else {
+                    mbar_expect_tx(&full[s], static_cast<uint32_t>(rows * p.in * 2));
+                }
+            }
+            alive = __shfl_sync(0xffffffffu, alive, 0);
+            if (!alive) break;
+            const __nv_bfloat16* source = static_cast<const __nv_bfloat16*>(p.weight) + static_cast<int64_t>(tile) * TF * p.in;
+            uint8_t* dst = slot_base + s * slot_bytes;
+            for (int r = lane; r < rows; r += 32)
+                bulk_load(dst + r * x_stride * 2, source + static_cast<int64_t>(r) * p.in, static_cast<uint32_t>(p.in * 2), &full[s]);
+        }
+        return;
+    }
+
+    // Weights are constants; the activations (and residual, cache, q) come from the preceding kernels.
+    B200_MARK(0);
+    grid_dependency_wait();
+    B200_MARK(1);
+    // ---- consumers: stage the activations (the weight stream is already in flight) ----
+    // Warp w owns rows w and w+8.  Both rows are read with independent 16-byte loads into registers (one L2 round
+    // trip), reduced to their RMS (f32 squares per lane, f64 across lanes and for the square root), normalised,
+    // split into bf16 hi + lo and written to shared memory.  Rows longer than 1024 are handled one after the other.
+    {
+        const int vectors = p.in >> 2;             // float4 per row (in % 8 == 0)
+        const int per_lane = (vectors + 31) >> 5;  // float4 per lane and row, at most 16
+        auto stage_rows = [&](auto count_tag, int first_row) {
+            constexpr int ROWS = decltype(count_tag)::value;  // rows handled together by this warp
+            constexpr int MAXV = ROWS == 2 ? 8 : 16;
+            float4 v[ROWS][MAXV];
+#pragma unroll
+            for (int q = 0; q < ROWS; ++q) {
+                const int r = first_row + q * kConsumers;
+                const bool valid = row0 + r < p.rows;
+                const float4* source = reinterpret_cast<const float4*>(p.x + static_cast<int64_t>(valid ? row0 + r : 0) * p.in);
+#pragma unroll
+                for (int u = 0; u < MAXV; ++u) {
+                    const int at = u * 32 + lane;
+                    v[q][u] = (u < per_lane && valid && at < vectors) ? __ldg(source + at) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                }
+            }
+#pragma unroll
+            for (int q = 0; q < ROWS; ++q) {
+                const int r = first_row + q * kConsumers;
+                float scale = 1.0f;
+                if (p.norm_weight) {
+                    float squares = 0.0f;
+#pragma unroll
+                    for (int u = 0; u < MAXV; ++u)
+                        if (u < per_lane) squares += v[q][u].x * v[q][u].x + v[q][u].y * v[q][u].y + v[q][u].z * v[q][u].z + v[q][u].w * v[q][u].w;
+                    const float total = warp_sum(squares);
+                    scale = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(total, static_cast<float>(p.in)), static_cast<float>(p.eps))));
+                }
+#pragma unroll
+                for (int u = 0; u < MAXV; ++u) {
+                    const int k = (u * 32 + lane) * 4;
+                    if (u >= per_lane || k >= sp.in_padded) continue;
+                    float e[4] = {v[q][u].x, v[q][u].y, v[q][u].z, v[q][u].w};
+                    if (p.norm_weight && k < p.in) {
+                        float w[4];
+                        if (p.norm_dtype == B200_BF16) {
+                            const uint2 packed = __ldg(reinterpret_cast<const uint2*>(static_cast<const __nv_bfloat16*>(p.norm_weight) + k));
+                            w[0] = bf16_lo(packed.x); w[1] = bf16_hi(packed.x); w[2] = bf16_lo(packed.y); w[3] = bf16_hi(packed.y);
+                        } else {
+                            const float4 f = __ldg(reinterpret_cast<const float4*>(static_cast<const float*>(p.norm_weight) + k));
+                            w[0] = f.x; w[1] = f.y; w[2] = f.z; w[3] = f.w;
+                        }
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) e[i] = __fmul_rn(__fmul_rn(e[i], scale), w[i]);
+                    }
+                    const __nv_bfloat162 h0 = __floats2bfloat162_rn(e[0], e[1]), h1 = __floats2bfloat162_rn(e[2], e[3]);
+                    const __nv_bfloat162 l0 = __floats2bfloat162_rn(e[0] - __low2float(h0), e[1] - __high2float(h0));
+                    const __nv_bfloat162 l1 = __floats2bfloat162_rn(e[2] - __low2float(h1), e[3] - __high2float(h1));
+                    uint2 hi, lo;
+                    hi.x = *reinterpret_cast<const uint32_t*>(&h0); hi.y = *reinterpret_cast<const uint32_t*>(&h1);
+                    lo.x = *reinterpret_cast<const uint32_t*>(&l0); lo.y = *reinterpret_cast<const uint32_t*>(&l1);
+                    *reinterpret_cast<uint2*>(x_hi + r * x_stride + k) = hi;
+                    *reinterpret_cast<uint2*>(x_lo + r * x_stride + k) = lo;
+                }
+            }
+        };
+        // in_padded beyond in: the tail columns of a row are written as zeros by the lanes that own them
+        if (per_lane <= 8) {
+            stage_rows(std::integral_constant<int, 2>{}, warp);
+        } else {
+            stage_rows(std::integral_constant<int, 1>{}, warp);
+            stage_rows(std::integral_constant<int, 1>{}, warp + kConsumers);
+        }
+        consumer_barrier();
+        B200_MARK(2);
+    }
+
+    const int mi = lane >> 3, ri = lane & 7;
+    // ldmatrix row address of the activation fragment: matrices (rows 0-7, k 0-7), (rows 8-15, k 0-7), (rows 0-7, k 8-15), (rows 8-15, k 8-15)
+    const uint32_t a_lane = static_cast<uint32_t>((((mi & 1) * 8 + ri) * x_stride + (mi >> 1) * 8) * 2);
+    const uint32_t a_hi = smem_u32(x_hi) + a_lane, a_lo = smem_u32(x_lo) + a_lane;
+    const int ksteps = (p.in + 15) >> 4;
+
+    bool alive = true;
+    for (int t = 0; t < my_tiles && alive; ++t) {
+        const int tile = blockIdx.x + t * gridDim.x;
+        float acc[NT][4];
+#pragma unroll
+        for (int n = 0; n < NT; ++n) acc[n][0] = acc[n][1] = acc[n][2] = acc[n][3] = 0.0f;
+        {
+            const int s = t % sp.slots;
+            const uint32_t phase = (t / sp.slots) & 1;
+            if (!mbar_wait(&full[s], phase)) {
+                if (lane == 0) atomicExch(sp.status, B200_DEVICE_TIMEOUT);
+                alive = false;
+                break;
+            }
+            if (t == 0) B200_MARK(3);
+            const uint32_t slot = smem_u32(slot_base + s * slot_bytes);
+            // ldmatrix row addresses of the weight fragments: x4 = (features n*8.., k 0-7), (same, k 8-15),
+            // (features (n+1)*8.., k 0-7), (same, k 8-15); x2 = the first two
+            const uint32_t b_lane = slot + static_cast<uint32_t>((((NT == 1 ? 0 : (mi >> 1)) * 8 + ri) * x_stride + (mi & 1) * 8) * 2);
+            for (int j = warp; j < ksteps; j += kConsumers) {
+                uint32_t ah[4], al[4];
+                const uint32_t column_bytes = static_cast<uint32_t>(j * 32);
+                ldmatrix_x4(ah, a_hi + column_bytes);
+                ldmatrix_x4(al, a_lo + column_bytes);
+                if constexpr (NT == 1) {
+                    uint32_t b[2];
+                    ldmatrix_x2(b, b_lane + column_bytes);
+                    mma_bf16(acc[0], ah, b[0], b[1]);
+                    mma_bf16(acc[0], al, b[0], b[1]);
+                } else {
+#pragma unroll
+                    for (int n = 0; n < NT; n += 2) {
+                        uint32_t b[4];
+                        ldmatrix_x4(b, b_lane + static_cast<uint32_t>(n * 8 * x_stride * 2) + column_bytes);
+                        mma_bf16(acc[n], ah, b[0], b[1]);
+                        mma_bf16(acc[n], al, b[0], b[1]);
+                        mma_bf16(acc[n + 1], ah, b[2], b[3]);
+                        mma_bf16(acc[n + 1], al, b[2], b[3]);
+                    }
+                }
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&empty[s]);
+            if (t == 0) B200_MARK(4);
+        }
+        if (!alive) break;
+        // ---- add the eight K-slices and finish the tile ----
+        {
+            const int g = lane >> 2, tq = lane & 3;
+            float* mine = partial + warp * kRows * TF;
+#pragma unroll
+            for (int n = 0; n < NT; ++n) {
+                *reinterpret_cast<float2*>(mine + g * TF + n * 8 + 2 * tq) = make_float2(acc[n][0], acc[n][1]);
+                *reinterpret_cast<float2*>(mine + (g + 8) * TF + n * 8 + 2 * tq) = make_float2(acc[n][2], acc[n][3]);
+            }
+        }
+        consumer_barrier();
+        if (t == 0) B200_MARK(5);
+        for (int i = threadIdx.x; i < kRows * (TF / 2); i += kConsumers * 32) {
+            const int r = i / (TF / 2), f = (i - r * (TF / 2)) * 2;
+            float a = 0.0f, b = 0.0f;
+#pragma unroll
+            for (int w = 0; w < kConsumers; ++w) {
+                const float2 v = *reinterpret_cast<const float2*>(partial + (w * kRows + r) * TF + f);
+                a += v.x;
+                b += v.y;
+            }
+            const int row = row0 + r, feature0 = tile * TF + f;
+            if (row < p.rows && feature0 < p.out) linear_epilogue<EPI>(p, row, feature0, a, b);
+        }
+        consumer_barrier();
+        if (t == 0) B200_MARK(6);
+    }
+    B200_MARK(7);
+    trace_end(trace);
+}
+
+template <int TF, int EPI> int launch_tile(const StreamParams& sp, size_t smem, int ctas, int row_tiles, cudaStream_t stream) {
+    auto kernel = linear_stream_kernel<TF, EPI>;
+    B200_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+    return cuda_status(launch_dependent(kernel, dim3(ctas, row_tiles), dim3(kThreads), smem, stream, sp), "linear_stream_kernel launch");
+}
+
+template <int EPI> int pick_tile(const StreamParams& sp, size_t smem, int ctas, int row_tiles, cudaStream_t stream) {
+    switch (sp.tile_features) {
+    case 8: return launch_tile<8, EPI>(sp, smem, ctas, row_tiles, stream);
+    case 16: return launch_tile<16, EPI>(sp, smem, ctas, row_tiles, stream);
+    case 32: return launch_tile<32, EPI>(sp, smem, ctas, row_tiles, stream);
+    default: return launch_tile<64, EPI>(sp, smem, ctas, row_tiles, stream);
+    }
+}
+
+int sm_count(int device) {
+    static std::mutex mutex;
+    static int counts[64];
+    std::lock_guard<std::mutex> lock(mutex);
+    if (device < 0 || device >= 64) return 148;
+    if (!counts[device] && cudaDeviceGetAttribute(&counts[device], cudaDevAttrMultiProcessorCount, device) != cudaSuccess) counts[device] = 148;
+    return counts[device];
+}
+
+}  // namespace
+
+int launch_linear_stream(const LinearParams& p, int epilogue, cudaStream_t stream) {
+    if (p.weight_dtype != B200_BF16 || p.in > kMaxIn || (p.in & 7) || (reinterpret_cast<uintptr_t>(p.weight) & 15)
+        || (reinterpret_cast<uintptr_t>(p.x) & 15))
+        return B200_UNSUPPORTED;
+    int device = 0;
+    B200_CUDA(cudaGetDevice(&device));
+    const int sms = sm_count(device);
+
+    StreamParams sp{};
+    sp.base = p;
+    sp.in_padded = (p.in + 63) & ~63;
+    sp.status = device_status_word(device);
+    const size_t row_bytes = static_cast<size_t>(sp.in_padded + 8) * 2;
+    // Two CTAs per SM (this kernel's tail next to the early-started successor) when the activations leave room
+    // for at least two weight slots in half of the shared memory; else one CTA per SM.
+    const size_t half = 110 * 1024, whole = 220 * 1024;
+    const size_t budget = 2 * kRows * row_bytes + kConsumers * kRows * 8 * 4 + 384 + 2 * 8 * row_bytes <= half ? half : whole;
+    // Largest tile that still gives every SM several tiles; smaller tiles when the ring would not hold two of them.
+    int tf = 64;
+    while (tf > 8 && (p.out + tf - 1) / tf < 4 * sms) tf >>= 1;
+    size_t fixed = 0;
+    int slots = 0;
+    for (;; tf >>= 1) {
+        fixed = 2 * kRows * row_bytes + static_cast<size_t>(kConsumers) * kRows * tf * 4 + 128 + 256;
+        slots = fixed < budget ? static_cast<int>((budget - fixed) / (tf * row_bytes)) : 0;
+        if (slots >= 2 || tf == 8) break;
+    }
+    if (slots < 2) return B200_UNSUPPORTED;
+    if (slots > 8) slots = 8;
+    sp.tile_features = tf;
+    sp.slots = slots;
+    sp.tiles = (p.out + tf - 1) / tf;
+    const size_t smem = fixed + static_cast<size_t>(slots) * tf * row_bytes;
+
+    const int row_tiles = (p.rows + kRows - 1) / kRows;
+    const int ctas = sp.tiles < sms ? sp.tiles : sms;
+    switch (epilogue) {
+    case B200_EPI_STORE: return pick_tile<B200_EPI_STORE>(sp, smem, ctas, row_tiles, stream);
+    case B200_EPI_RESIDUAL: return pick_tile<B200_EPI_RESIDUAL>(sp, smem, ctas, row_tiles, stream);
+    case B200_EPI_SWIGLU: return pick_tile<B200_EPI_SWIGLU>(sp, smem, ctas, row_tiles, stream);
+    case B200_EPI_QKV: return pick_tile<B200_EPI_QKV>(sp, smem, ctas, row_tiles, stream);
+    }
+    return B200_UNSUPPORTED;
+}
+
+}  // namespace b200
+

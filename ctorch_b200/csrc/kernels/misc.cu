@@ -5,6 +5,23 @@
 #include <cstring>
 #include <mutex>
 
+#ifdef B200_TRACE
+namespace b200 {
+__device__ unsigned long long b200_step_trace[4096 * 3];
+__device__ unsigned int b200_step_trace_count;
+__device__ unsigned long long b200_step_marks[4096 * 8];
+}
+extern "C" __attribute__((visibility("default"))) int b200_step_marks_read(unsigned long long* host) {
+    return static_cast<int>(cudaMemcpyFromSymbol(host, b200::b200_step_marks, sizeof(unsigned long long) * 4096 * 8));
+}
+extern "C" __attribute__((visibility("default"))) int b200_step_trace_read(unsigned long long* host, unsigned int* count) {
+    cudaMemcpyFromSymbol(count, b200::b200_step_trace_count, sizeof(unsigned int));
+    const unsigned int zero = 0;
+    cudaMemcpyFromSymbol(host, b200::b200_step_trace, sizeof(unsigned long long) * 4096 * 3);
+    return static_cast<int>(cudaMemcpyToSymbol(b200::b200_step_trace_count, &zero, sizeof zero));
+}
+#endif
+
 namespace b200 {
 
 namespace {
@@ -64,6 +81,9 @@ namespace {
 template <class T>
 __global__ void embedding_kernel(const T* table, const int64_t* ids, int64_t rows, int64_t vocab, int64_t width, float* out,
                                  int32_t* status) {
+    const int trace = trace_begin(10);
+    grid_dependency_wait();   // the ids may come from the previous step's token feedback
+    grid_launch_dependents();
     const int64_t row = blockIdx.x;
     int64_t id = ids[row];
     if (id < 0 || id >= vocab) {  // the host API validates ids it can see; device-resident ids are clamped and flagged
@@ -71,6 +91,7 @@ __global__ void embedding_kernel(const T* table, const int64_t* ids, int64_t row
         id = id < 0 ? 0 : vocab - 1;
     }
     for (int64_t c = threadIdx.x; c < width; c += blockDim.x) out[row * width + c] = load_as_f32(table, id * width + c);
+    trace_end(trace);
 }
 
 // One CTA per row; f64 accumulation and f64 scale, one rounding (src/kernels/cpu/normalization.cpp:39-51).
@@ -109,6 +130,9 @@ __device__ __forceinline__ bool better(const Best& a, const Best& b) {  // is a 
 }
 __global__ void argmax_kernel(const float* x, int64_t width, int64_t* index) {
     __shared__ Best partial[32];
+    const int trace = trace_begin(11);
+    grid_dependency_wait();
+    grid_launch_dependents();
     const float* row = x + blockIdx.x * width;
     Best best{row[0], 0};
     for (int64_t c = threadIdx.x; c < width; c += blockDim.x) {
@@ -129,6 +153,7 @@ __global__ void argmax_kernel(const float* x, int64_t width, int64_t* index) {
         }
         if (threadIdx.x == 0) index[blockIdx.x] = best.index;
     }
+    trace_end(trace);
 }
 
 __global__ void select_rows_kernel(const float* x, int64_t first, int64_t stride, int64_t width, float* out) {
@@ -154,11 +179,13 @@ int b200_embedding(const void* table, int32_t table_dtype, const int64_t* ids, i
     int32_t* status = device_status_word(device);
     const int threads = width >= 256 ? 256 : 64;
     if (table_dtype == B200_BF16)
-        embedding_kernel<<<static_cast<unsigned>(rows), threads, 0, as_stream(stream)>>>(static_cast<const __nv_bfloat16*>(table), ids, rows, vocab, width, out, status);
-    else if (table_dtype == B200_F32)
-        embedding_kernel<<<static_cast<unsigned>(rows), threads, 0, as_stream(stream)>>>(static_cast<const float*>(table), ids, rows, vocab, width, out, status);
-    else { set_error("b200_embedding: table dtype %d is not f32 or bf16", table_dtype); return B200_UNSUPPORTED; }
-    return cuda_status(cudaGetLastError(), "embedding_kernel launch");
+        return cuda_status(launch_dependent(embedding_kernel<__nv_bfloat16>, dim3(static_cast<unsigned>(rows)), dim3(threads), 0, as_stream(stream),
+                                            static_cast<const __nv_bfloat16*>(table), ids, rows, vocab, width, out, status), "embedding_kernel launch");
+    if (table_dtype == B200_F32)
+        return cuda_status(launch_dependent(embedding_kernel<float>, dim3(static_cast<unsigned>(rows)), dim3(threads), 0, as_stream(stream),
+                                            static_cast<const float*>(table), ids, rows, vocab, width, out, status), "embedding_kernel launch");
+    set_error("b200_embedding: table dtype %d is not f32 or bf16", table_dtype);
+    return B200_UNSUPPORTED;
 }
 
 int b200_rms_norm(const float* x, const void* weight, int32_t weight_dtype, int64_t rows, int64_t width, double eps,
@@ -176,8 +203,8 @@ int b200_rms_norm(const float* x, const void* weight, int32_t weight_dtype, int6
 int b200_argmax(const float* x, int64_t rows, int64_t width, int64_t* index, void* stream) {
     if (!x || !index || rows < 0 || width <= 0) { set_error("b200_argmax: bad pointer or size"); return B200_BAD_ARGUMENT; }
     if (rows == 0) return B200_OK;
-    argmax_kernel<<<static_cast<unsigned>(rows), width >= 4096 ? 1024 : 256, 0, as_stream(stream)>>>(x, width, index);
-    return cuda_status(cudaGetLastError(), "argmax_kernel launch");
+    return cuda_status(launch_dependent(argmax_kernel, dim3(static_cast<unsigned>(rows)), dim3(width >= 4096 ? 1024 : 256), 0, as_stream(stream),
+                                        x, width, index), "argmax_kernel launch");
 }
 
 int b200_select_rows(const float* x, int64_t first, int64_t stride, int64_t rows_out, int64_t width, float* out, void* stream) {
@@ -225,6 +252,8 @@ __global__ void permute_0213_kernel(const float* in, int64_t a, int64_t b, int64
 
 __global__ void token_feedback_kernel(const int64_t* next, int64_t batch, int64_t* ids, int64_t* history,
                                       int64_t history_rows, int32_t* counter) {
+    grid_dependency_wait();
+    grid_launch_dependents();
     const int32_t step = *counter;
     for (int64_t s = threadIdx.x; s < batch; s += blockDim.x) {
         const int64_t token = next[s];
@@ -261,8 +290,8 @@ int b200_permute_0213(const float* in, int64_t a, int64_t b, int64_t c, int64_t 
 int b200_token_feedback(const int64_t* next, int64_t batch, int64_t* ids, int64_t* history, int64_t history_rows,
                         int32_t* counter, void* stream) {
     if (!next || !counter || batch <= 0) { set_error("b200_token_feedback: bad pointer or size"); return B200_BAD_ARGUMENT; }
-    b200::token_feedback_kernel<<<1, 256, 0, as_stream(stream)>>>(next, batch, ids, history, history_rows, counter);
-    return cuda_status(cudaGetLastError(), "token_feedback_kernel launch");
+    return cuda_status(launch_dependent(b200::token_feedback_kernel, dim3(1), dim3(256), 0, as_stream(stream), next, batch, ids, history,
+                                        history_rows, counter), "token_feedback_kernel launch");
 }
 
 }  // extern "C"
