@@ -42,6 +42,13 @@ class QkvArgs(C.Structure):
                 ("q_up", C.c_void_p), ("v_up", C.c_void_p)]
 
 
+class ShadowLinearArgs(C.Structure):
+    _fields_ = [("x_hi", C.c_void_p), ("x_lo", C.c_void_p), ("rows", C.c_int64), ("inner", C.c_int64), ("weight", C.c_void_p),
+                ("out", C.c_int64), ("sumsq_in", C.c_void_p), ("parts_in", C.c_int32), ("eps", C.c_double), ("epilogue", C.c_int),
+                ("residual", C.c_void_p), ("qkv", C.POINTER(QkvArgs)), ("y", C.c_void_p), ("out_hi", C.c_void_p),
+                ("out_lo", C.c_void_p), ("out_norm_weight", C.c_void_p), ("out_norm_dtype", C.c_int32), ("sumsq_out", C.c_void_p)]
+
+
 class B200Error(RuntimeError):
     pass
 
@@ -124,6 +131,11 @@ def _declare(l: C.CDLL) -> None:
         "b200_attention_scratch_bytes": (sz, [i64, i32, i32, i32, i32, i32]),
         "b200_attention_decode": (C.c_int, [vp, i64, i32, i32, vp, i32, i32, vp, sz, vp, vp]),
         "b200_attention_decode_static": (C.c_int, [vp, i64, i32, i32, vp, i32, i32, vp, vp]),
+        "b200_linear_shadow": (C.c_int, [C.POINTER(ShadowLinearArgs), vp]),
+        "b200_linear_shadow_parts": (i32, [i64, i64]),
+        "b200_embedding_shadow": (C.c_int, [vp, i32, vp, i64, i64, i64, vp, i32, vp, vp, vp, vp, vp]),
+        "b200_shadow_from_rows": (C.c_int, [vp, i64, i64, vp, i32, vp, vp, vp, vp]),
+        "b200_attention_decode_shadow": (C.c_int, [vp, i64, i32, i32, vp, i32, i32, vp, sz, vp, vp, vp]),
         "b200_argmax": (C.c_int, [vp, i64, i64, vp, vp]), "b200_select_rows": (C.c_int, [vp, i64, i64, i64, i64, vp, vp]),
         "b200_rotary": (C.c_int, [vp, i64, i64, i64, vp, vp, vp, vp]),
         "b200_permute_0213": (C.c_int, [vp, i64, i64, i64, i64, vp, vp]),

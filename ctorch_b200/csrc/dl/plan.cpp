@@ -203,6 +203,16 @@ void DecodePlan::refresh() {
     }
     synchronize(probe.device());
     packed_version_ = version;
+    // Shadow protocol: bf16 weights and every projection inside the streaming kernel's limits.
+    const Index D = owner_.dimensions(), F = owner_.hidden(), KV = owner_.kv_heads() * (D / owner_.heads());
+    parts_o_ = b200_linear_shadow_parts(D, D);
+    parts_down_ = b200_linear_shadow_parts(F, D);
+    shadow_ = owner_.dtype() == DType::bf16 && parts_o_ > 0 && parts_down_ > 0 && b200_linear_shadow_parts(D, D + 2 * KV) > 0
+        && b200_linear_shadow_parts(D, 2 * F) > 0;
+    for (Index i = 0; shadow_ && i < owner_.layer_count(); ++i) {
+        auto& layer = owner_.layer(i);
+        shadow_ = layer.attention_norm().weight()->dtype() == DType::bf16 && layer.feedforward_norm().weight()->dtype() == DType::bf16;
+    }
 }
 
 void DecodePlan::reserve(Index rows, Index max_length, int device) {
@@ -210,12 +220,20 @@ void DecodePlan::reserve(Index rows, Index max_length, int device) {
     const std::size_t need = b200_attention_scratch_bytes(rows, static_cast<int32_t>(owner_.heads()), static_cast<int32_t>(owner_.kv_heads()),
                                                           static_cast<int32_t>(D / owner_.heads()), static_cast<int32_t>(max_length), 64);
     const TensorOptions f32{DType::f32, Device::cuda(device)};
-    if (rows > reserved_rows_ || !h_.defined() || h_.device().index != device) {
+    if (rows > reserved_rows_ || !h_.defined() || h_.device().index != device || (shadow_ && !hs_hi_.defined())) {
         synchronize(Device::cuda(device));
         int max_rank = 0;
         for (const auto& layer : layers_) max_rank = std::max(max_rank, layer.rank);
         h_ = empty({rows, D}, f32); q_ = empty({rows, D}, f32); attended_ = empty({rows, D}, f32);
         activated_ = empty({rows, F}, f32); low_ = empty({rows, std::max(1, 2 * max_rank)}, f32);
+        if (shadow_) {
+            const TensorOptions half{DType::bf16, Device::cuda(device)};
+            hs_hi_ = empty({rows, D}, half); hs_lo_ = empty({rows, D}, half);
+            att_hi_ = empty({rows, D}, half); att_lo_ = empty({rows, D}, half);
+            act_hi_ = empty({rows, F}, half); act_lo_ = empty({rows, F}, half);
+            const Index parts = std::max<Index>(1, std::max(parts_o_, parts_down_));
+            sq_attn_ = empty({parts, rows}, f32); sq_ffn_ = empty({parts, rows}, f32);
+        }
         reserved_rows_ = rows;
         ++buffer_epoch_;
     }
@@ -243,11 +261,115 @@ void DecodePlan::validate(Index batch, Index length, std::span<KVCache> cache, i
     for (auto& layer : cache) layer.ensure(device, batch, owner_.kv_heads(), hd);
 }
 
-void DecodePlan::run_layers(const float* x, Index batch, Index length, std::span<KVCache> cache, Index max_length, void* stream) {
+namespace {
+void shadow_linear(const b200_shadow_linear_args& args, void* stream, const char* what) {
+    runtime::check(b200_linear_shadow(&args, stream), what);
+    probe(0);
+}
+}  // namespace
+
+void DecodePlan::embed(const Embedding& tokens, const Index* ids, Index rows, float* x, void* stream) {
+    const Tensor& table = tokens.weight();
+    if (!shadow_) {
+        runtime::check(b200_embedding(table.raw_data(), code_of(table.dtype()), ids, rows, table.size(0), table.size(1), x, stream), "embedding");
+        probe(2);
+        return;
+    }
+    const Tensor* norm = owner_.layer(0).attention_norm().weight();
+    runtime::check(b200_embedding_shadow(table.raw_data(), code_of(table.dtype()), ids, rows, table.size(0), table.size(1), norm->raw_data(),
+                                         code_of(norm->dtype()), x, hs_hi_.mutable_data(), hs_lo_.mutable_data(),
+                                         static_cast<float*>(sq_attn_.mutable_data()), stream), "embedding");
+    probe(2);
+}
+
+void DecodePlan::logits(const Linear& output, Index rows, float* out, void* stream) {
+    const Tensor* norm = owner_.normalization().weight();
+    const Index V = output.weight().size(0), D = owner_.dimensions();
+    if (shadow_ && output.weight().dtype() == DType::bf16 && b200_linear_shadow_parts(D, V) > 0) {
+        b200_shadow_linear_args args{};
+        args.x_hi = hs_hi_.raw_data(); args.x_lo = hs_lo_.raw_data(); args.rows = rows; args.in = D;
+        args.weight = output.weight().raw_data(); args.out = V;
+        args.sumsq_in = sq_attn_.data<float>(); args.parts_in = last_parts_; args.eps = owner_.normalization().epsilon();
+        args.epilogue = B200_EPI_STORE; args.y = out;
+        shadow_linear(args, stream, "logits");
+        return;
+    }
+    runtime::check(b200_linear(hidden(), rows, D, output.weight().raw_data(), code_of(output.weight().dtype()), V, norm->raw_data(),
+                               code_of(norm->dtype()), owner_.normalization().epsilon(), B200_EPI_STORE, nullptr, nullptr, out, stream),
+                   "logits");
+    probe(0);
+}
+
+void DecodePlan::run_layers(const float* x, Index batch, Index length, std::span<KVCache> cache, Index max_length, void* stream,
+                            bool shadow_ready) {
     const Index D = owner_.dimensions(), F = owner_.hidden(), rows = batch * length;
     const int device = h_.device().index;
     const double eps = TransformerDecoderLayer::norm_epsilon;
     float* h = hidden();
+    if (shadow_) {
+        const Index H = owner_.heads(), HK = owner_.kv_heads(), hd = D / H;
+        auto* sq_attn = static_cast<float*>(sq_attn_.mutable_data());
+        auto* sq_ffn = static_cast<float*>(sq_ffn_.mutable_data());
+        if (!shadow_ready) {
+            const Tensor* norm = owner_.layer(0).attention_norm().weight();
+            runtime::check(b200_shadow_from_rows(x, rows, D, norm->raw_data(), code_of(norm->dtype()), hs_hi_.mutable_data(),
+                                                 hs_lo_.mutable_data(), sq_attn, stream), "input shadow");
+            probe(2);
+        }
+        int parts_attn = 1;
+        for (Index i = 0; i < owner_.layer_count(); ++i) {
+            auto& layer = owner_.layer(i);
+            const auto& a = layer.attention();
+            const Layer& packed = layers_[static_cast<std::size_t>(i)];
+            const float* in = i == 0 ? x : h;
+            b200_kv_cache* kv = cache[static_cast<std::size_t>(i)].ensure(device, batch, HK, hd);
+            b200_qkv_args qkv{};
+            qkv.heads = static_cast<int32_t>(H); qkv.kv_heads = static_cast<int32_t>(HK); qkv.head_dim = static_cast<int32_t>(hd);
+            qkv.tokens_per_sequence = static_cast<int32_t>(length);
+            qkv.cosine = a.rotary().cosine().data<float>(); qkv.sine = a.rotary().sine().data<float>();
+            qkv.context = static_cast<int32_t>(a.rotary().cosine().size(0));
+            qkv.cache = kv; qkv.q_out = static_cast<float*>(q_.mutable_data());
+            b200_shadow_linear_args base{};
+            base.x_hi = hs_hi_.raw_data(); base.x_lo = hs_lo_.raw_data(); base.rows = rows; base.in = D;
+            base.sumsq_in = sq_attn; base.parts_in = parts_attn; base.eps = eps;
+            if (packed.rank > 0) {
+                b200_shadow_linear_args low = base;
+                low.weight = packed.lora_down.raw_data(); low.out = 2 * packed.rank; low.epilogue = B200_EPI_STORE;
+                low.y = static_cast<float*>(low_.mutable_data());
+                shadow_linear(low, stream, "adapter down-projection");
+                qkv.lora_rank = packed.rank; qkv.lora_scale = packed.scale; qkv.low = low.y; qkv.q_up = packed.q_up; qkv.v_up = packed.v_up;
+            }
+            b200_shadow_linear_args project = base;
+            project.weight = packed.wqkv.raw_data(); project.out = D + 2 * HK * hd; project.epilogue = B200_EPI_QKV; project.qkv = &qkv;
+            shadow_linear(project, stream, "q/k/v projection");
+            runtime::check(b200_attention_decode_shadow(qkv.q_out, rows, static_cast<int32_t>(length), static_cast<int32_t>(H), kv,
+                                                        static_cast<int32_t>(max_length), 1, scratch_.mutable_data(), scratch_bytes_,
+                                                        att_hi_.mutable_data(), att_lo_.mutable_data(), stream), "attention");
+            probe(1);
+            const Tensor* ffn_norm = layer.feedforward_norm().weight();
+            b200_shadow_linear_args out_proj{};
+            out_proj.x_hi = att_hi_.raw_data(); out_proj.x_lo = att_lo_.raw_data(); out_proj.rows = rows; out_proj.in = D;
+            out_proj.weight = packed.wo; out_proj.out = D; out_proj.epilogue = B200_EPI_RESIDUAL; out_proj.residual = in; out_proj.y = h;
+            out_proj.out_hi = hs_hi_.mutable_data(); out_proj.out_lo = hs_lo_.mutable_data();
+            out_proj.out_norm_weight = ffn_norm->raw_data(); out_proj.out_norm_dtype = code_of(ffn_norm->dtype()); out_proj.sumsq_out = sq_ffn;
+            shadow_linear(out_proj, stream, "output projection");
+            b200_shadow_linear_args gate_up{};
+            gate_up.x_hi = hs_hi_.raw_data(); gate_up.x_lo = hs_lo_.raw_data(); gate_up.rows = rows; gate_up.in = D;
+            gate_up.weight = packed.wgu.raw_data(); gate_up.out = 2 * F; gate_up.sumsq_in = sq_ffn; gate_up.parts_in = parts_o_; gate_up.eps = eps;
+            gate_up.epilogue = B200_EPI_SWIGLU; gate_up.out_hi = act_hi_.mutable_data(); gate_up.out_lo = act_lo_.mutable_data();
+            shadow_linear(gate_up, stream, "gate/up projection");
+            const Tensor* next_norm = i + 1 < owner_.layer_count() ? owner_.layer(i + 1).attention_norm().weight() : owner_.normalization().weight();
+            b200_shadow_linear_args down{};
+            down.x_hi = act_hi_.raw_data(); down.x_lo = act_lo_.raw_data(); down.rows = rows; down.in = F;
+            down.weight = packed.wd; down.out = D; down.epilogue = B200_EPI_RESIDUAL; down.residual = h; down.y = h;
+            down.out_hi = hs_hi_.mutable_data(); down.out_lo = hs_lo_.mutable_data();
+            down.out_norm_weight = next_norm->raw_data(); down.out_norm_dtype = code_of(next_norm->dtype()); down.sumsq_out = sq_attn;
+            shadow_linear(down, stream, "down projection");
+            parts_attn = parts_down_;
+        }
+        last_parts_ = parts_attn;
+        return;
+    }
     auto* act = static_cast<float*>(activated_.mutable_data());
     for (Index i = 0; i < owner_.layer_count(); ++i) {
         auto& layer = owner_.layer(i);
@@ -383,16 +505,18 @@ void Generation::prefill(const Tensor& prompt) {
 void Generation::enqueue_step(void* stream, Index max_length) {
     auto& plan = decoder_->plan();
     const Index D = decoder_->dimensions();
-    runtime::check(b200_embedding(tokens_->weight().raw_data(), code_of(tokens_->weight().dtype()), ids_.data<Index>(), batch_,
-                                  tokens_->weight().size(0), D, static_cast<float*>(x_.mutable_data()), stream), "embedding");
-    plan.run_layers(x_.data<float>(), batch_, 1, *cache_, max_length, stream);
+    plan.embed(*tokens_, ids_.data<Index>(), batch_, static_cast<float*>(x_.mutable_data()), stream);
+    plan.run_layers(x_.data<float>(), batch_, 1, *cache_, max_length, stream, plan.uses_shadows());
     std::vector<b200_kv_cache*> handles;
     for (auto& layer : *cache_) handles.push_back(layer.handle());
     runtime::check(b200_kv_cache_advance(handles.data(), static_cast<int32_t>(handles.size()), 1, stream), "KV advance");
     probe(2);
-    enqueue_head(*decoder_, *output_, plan.hidden(), batch_, static_cast<float*>(logits_.mutable_data()),
-                 static_cast<Index*>(next_.mutable_data()), static_cast<Index*>(ids_.mutable_data()),
-                 static_cast<Index*>(history_.mutable_data()), max_steps_, static_cast<int32_t*>(counter_.mutable_data()), stream);
+    plan.logits(*output_, batch_, static_cast<float*>(logits_.mutable_data()), stream);
+    runtime::check(b200_argmax(logits_.data<float>(), batch_, output_->weight().size(0), static_cast<Index*>(next_.mutable_data()), stream), "argmax");
+    runtime::check(b200_token_feedback(next_.data<Index>(), batch_, static_cast<Index*>(ids_.mutable_data()),
+                                       static_cast<Index*>(history_.mutable_data()), max_steps_,
+                                       static_cast<int32_t*>(counter_.mutable_data()), stream), "token feedback");
+    probe(2);
 }
 
 void Generation::capture() {

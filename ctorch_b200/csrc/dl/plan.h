@@ -30,7 +30,14 @@ public:
 
     // Pieces used by Generation.  `x` holds rows = batch*length feature rows; the residual stream ends in hidden().
     void validate(Index batch, Index length, std::span<KVCache> cache, int device);
-    void run_layers(const float* x, Index batch, Index length, std::span<KVCache> cache, Index max_length, void* stream);
+    // `shadow_ready`: the caller already produced the input shadow and its sums of squares (token path, see embed()).
+    void run_layers(const float* x, Index batch, Index length, std::span<KVCache> cache, Index max_length, void* stream,
+                    bool shadow_ready = false);
+    // Token ids -> first hidden rows `x` (plus the input shadow when the shadow protocol is active).
+    void embed(const Embedding& tokens, const Index* ids, Index rows, float* x, void* stream);
+    // Logits of the last run_layers' rows (decode step: final norm folded into the projection).
+    void logits(const Linear& output, Index rows, float* out, void* stream);
+    bool uses_shadows() const { return shadow_; }
     void reserve(Index rows, Index max_length, int device);
     float* hidden() const { return static_cast<float*>(h_.mutable_data()); }
     void refresh();  // re-pack weights when the owner's parameters moved
@@ -50,6 +57,10 @@ private:
     std::size_t scratch_bytes_ = 0;
     std::uint64_t buffer_epoch_ = 0;
     Tensor h_, q_, attended_, activated_, low_, scratch_;
+    // shadow protocol (bf16 models whose widths fit the streaming kernel): activations travel as bf16 hi + lo planes
+    bool shadow_ = false;
+    int parts_o_ = 0, parts_down_ = 0, last_parts_ = 0;
+    Tensor hs_hi_, hs_lo_, att_hi_, att_lo_, act_hi_, act_lo_, sq_attn_, sq_ffn_;
 };
 
 // Greedy generation with the token loop resident on the device (the loop of examples/decoder_generate.cpp:20-31).

@@ -33,6 +33,7 @@ struct AttnParams {
     float* part_o;     // [rows*heads, num_splits, head_dim]
     float* part_ml;    // [rows*heads, num_splits, 2]
     float* out;        // [rows, heads*head_dim]
+    __nv_bfloat16 *out_hi, *out_lo;  // optional: result as a shadow (bf16 hi + lo planes) instead of `out`
     float scale;
     int32_t* status;
 };
@@ -50,10 +51,22 @@ SplitPlan plan_splits(int64_t rows, int kv_heads, int max_length, int page_size)
         const int64_t splits16 = (s.pages_total + 15) / 16;
         pps = items * splits16 <= 32768 ? 16 : s.pages_total;
     }
+    if (s.pages_total <= 16) pps = s.pages_total;  // short contexts: one CTA per (row, KV head), no merge kernel
     if (pps > s.pages_total) pps = s.pages_total;
     s.pages_per_split = static_cast<int>(pps);
     s.num_splits = (s.pages_total + s.pages_per_split - 1) / s.pages_per_split;
     return s;
+}
+
+// Final attention value: f32, or the shadow planes when the caller asked for them.
+__device__ __forceinline__ void store_result(const AttnParams& p, int64_t at, float value) {
+    if (p.out_hi) {
+        const __nv_bfloat16 hi = __float2bfloat16_rn(value);
+        p.out_hi[at] = hi;
+        p.out_lo[at] = __float2bfloat16_rn(value - __bfloat162float(hi));
+    } else {
+        p.out[at] = value;
+    }
 }
 
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
@@ -82,7 +95,7 @@ template <int HD> struct FastShape {
     static constexpr int halves = HD / 64;
     static constexpr int tile_bytes = halves * kHalfTileBytes;  // K or V page
     static constexpr int stage_bytes = 2 * tile_bytes;
-    static constexpr int stages = HD == 128 ? 3 : 4;
+    static constexpr int stages = HD == 128 ? 6 : 8;  // 192 KB / 128 KB of K and V in flight per CTA
     static constexpr int smem_bytes = stages * stage_bytes + 1024 + 2 * stages * 8;
 };
 
@@ -102,7 +115,9 @@ __global__ void __launch_bounds__(kFastThreads) attention_mma_kernel(const __gri
     uint64_t* empty = full + S::stages;
 
     const int trace = trace_begin(20);
+    trace_mark(trace, 0);
     grid_dependency_wait();   // q, the cache and the lengths come from the preceding kernels
+    trace_mark(trace, 1);
     grid_launch_dependents();
     const int item = blockIdx.x, split = blockIdx.y;
     const int row = item / p.kv.kv_heads, kvh = item % p.kv.kv_heads;
@@ -175,6 +190,7 @@ __global__ void __launch_bounds__(kFastThreads) attention_mma_kernel(const __gri
             }
         }
         const int tok0 = warp * 16;
+        trace_mark(trace, 2);
         const int mi = lane >> 3, ri = lane & 7;
         bool alive = true;
         for (int i = 0; i < pages && alive; ++i) {
@@ -185,6 +201,7 @@ __global__ void __launch_bounds__(kFastThreads) attention_mma_kernel(const __gri
                 alive = false;
                 break;
             }
+            if (i == 0) trace_mark(trace, 3);
             const uint32_t kbase = smem_u32(smem + s * S::stage_bytes);
             const uint32_t vbase = kbase + S::tile_bytes;
 
@@ -257,6 +274,7 @@ __global__ void __launch_bounds__(kFastThreads) attention_mma_kernel(const __gri
         }
     }
     __syncthreads();  // every page has been consumed: the stage memory can be reused for the merge
+    trace_mark(trace, 4);
 
     float* merge_o = reinterpret_cast<float*>(smem);                       // [warps][group][HD]
     float* merge_ml = merge_o + kConsumerWarps * 16 * HD;                   // [warps][16][2]
@@ -295,7 +313,7 @@ __global__ void __launch_bounds__(kFastThreads) attention_mma_kernel(const __gri
         }
         const int64_t head_item = static_cast<int64_t>(row) * p.heads + kvh * group + r;
         if (p.num_splits == 1) {
-            p.out[head_item * HD + d] = acc / l;
+            store_result(p, head_item * HD + d, acc / l);
         } else {
             p.part_o[(head_item * p.num_splits + split) * HD + d] = acc;
             if (d == 0) {
@@ -373,7 +391,7 @@ __global__ void __launch_bounds__(kGenericThreads) attention_generic_kernel(cons
             ll += weight * merge_ml[w][1];
         }
         if (p.num_splits == 1) {
-            p.out[head_item * hd + d] = a / ll;
+            store_result(p, head_item * hd + d, a / ll);
         } else {
             p.part_o[(head_item * p.num_splits + split) * hd + d] = a;
             if (d == 0) {
@@ -405,7 +423,7 @@ __global__ void attention_combine_kernel(const AttnParams p) {
     for (int d = threadIdx.x; d < hd; d += blockDim.x) {
         float acc = 0.0f;
         for (int s = 0; s < valid; ++s) acc += expf(ml[2 * s] - m) * p.part_o[(head_item * p.num_splits + s) * hd + d];
-        p.out[head_item * hd + d] = acc / l;
+        store_result(p, head_item * hd + d, acc / l);
     }
     trace_end(trace);
 }
@@ -432,10 +450,11 @@ extern "C" size_t b200_attention_scratch_bytes(int64_t rows, int32_t heads, int3
     return static_cast<size_t>(rows) * heads * s.num_splits * (head_dim + 2) * sizeof(float) + 256;
 }
 
-extern "C" int b200_attention_decode(const float* q, int64_t rows, int32_t tokens_per_sequence, int32_t heads,
-                                     const b200_kv_cache* cache, int32_t max_length, int32_t causal, void* scratch,
-                                     size_t scratch_bytes, float* out, void* stream) {
-    if (!q || !cache || !out || rows <= 0 || tokens_per_sequence <= 0 || heads <= 0 || heads % cache->kv_heads
+namespace {
+int attention_launch(const float* q, int64_t rows, int32_t tokens_per_sequence, int32_t heads, const b200_kv_cache* cache,
+                     int32_t max_length, int32_t causal, void* scratch, size_t scratch_bytes, float* out, __nv_bfloat16* out_hi,
+                     __nv_bfloat16* out_lo, void* stream) {
+    if (!q || !cache || (!out && !(out_hi && out_lo)) || rows <= 0 || tokens_per_sequence <= 0 || heads <= 0 || heads % cache->kv_heads
         || rows != static_cast<int64_t>(cache->sequences) * tokens_per_sequence || max_length <= 0) {
         set_error("b200_attention_decode: bad pointer, size or head grouping");
         return B200_BAD_ARGUMENT;
@@ -454,7 +473,7 @@ extern "C" int b200_attention_decode(const float* q, int64_t rows, int32_t token
     p.pages_per_split = plan.pages_per_split; p.num_splits = plan.num_splits;
     p.part_o = static_cast<float*>(scratch);
     p.part_ml = p.part_o ? p.part_o + static_cast<size_t>(rows) * heads * plan.num_splits * cache->head_dim : nullptr;
-    p.out = out;
+    p.out = out; p.out_hi = out_hi; p.out_lo = out_lo;
     p.scale = static_cast<float>(1.0 / std::sqrt(static_cast<double>(cache->head_dim)));
     p.status = device_status_word(cache->device);
     cudaStream_t s = as_stream(stream);
@@ -470,6 +489,22 @@ extern "C" int b200_attention_decode(const float* q, int64_t rows, int32_t token
     if (status != B200_OK || plan.num_splits == 1) return status;
     return cuda_status(launch_dependent(attention_combine_kernel, dim3(static_cast<unsigned>(rows) * heads), dim3(128), 0, s, p),
                        "attention_combine_kernel launch");
+}
+}  // namespace
+
+extern "C" int b200_attention_decode(const float* q, int64_t rows, int32_t tokens_per_sequence, int32_t heads,
+                                     const b200_kv_cache* cache, int32_t max_length, int32_t causal, void* scratch,
+                                     size_t scratch_bytes, float* out, void* stream) {
+    if (!out) { set_error("b200_attention_decode: bad pointer, size or head grouping"); return B200_BAD_ARGUMENT; }
+    return attention_launch(q, rows, tokens_per_sequence, heads, cache, max_length, causal, scratch, scratch_bytes, out, nullptr, nullptr, stream);
+}
+
+extern "C" int b200_attention_decode_shadow(const float* q, int64_t rows, int32_t tokens_per_sequence, int32_t heads,
+                                            const b200_kv_cache* cache, int32_t max_length, int32_t causal, void* scratch,
+                                            size_t scratch_bytes, void* out_hi, void* out_lo, void* stream) {
+    if (!out_hi || !out_lo) { set_error("b200_attention_decode_shadow: shadow planes missing"); return B200_BAD_ARGUMENT; }
+    return attention_launch(q, rows, tokens_per_sequence, heads, cache, max_length, causal, scratch, scratch_bytes, nullptr,
+                            static_cast<__nv_bfloat16*>(out_hi), static_cast<__nv_bfloat16*>(out_lo), stream);
 }
 
 // ---- allocation-free variant ------------------------------------------------------------------------------

@@ -24,6 +24,15 @@ struct LinearParams {
     float lora_scale;
     const float* low;
     const void *q_up, *v_up;
+    // Activation shadows (streaming kernel only, all optional).  A shadow is an f32 matrix stored as two bf16
+    // planes hi + lo (hi = bf16(v), lo = bf16(v - hi)), the form the tensor cores consume.
+    const __nv_bfloat16 *x_hi, *x_lo;  // input shadow [rows, in]; replaces x
+    const float* sumsq_in;             // [parts_in][rows] partial sums of squares of the input rows before their
+    int parts_in;                      //   norm weight was folded in: the result is scaled by 1/sqrt(mean + eps)
+    __nv_bfloat16 *out_hi, *out_lo;    // output shadow (residual: [rows, out]; SwiGLU: [rows, out/2])
+    const void* out_norm_weight;       // weight of the RMSNorm that follows, folded into the output shadow
+    int out_norm_dtype;
+    float* sumsq_out;                  // [tiles][rows] per-tile sums of squares of the (un-weighted) result rows
 };
 
 // Finishes one pair of adjacent output features (feature0 even) of activation row `row`.
@@ -31,18 +40,21 @@ struct LinearParams {
 //   q|k|v: adapter delta (src/nn/decoder.cpp:26-28), adjacent-pair RoPE (src/ops/contraction.cpp:44-49), q store,
 //   k/v append to the paged cache (src/nn/kv_cache.cpp:24-28)
 template <int EPI>
-__device__ __forceinline__ void linear_epilogue(const LinearParams& p, int row, int feature0, float a, float b) {
+__device__ __forceinline__ void linear_epilogue(const LinearParams& p, int row, int feature0, float& a, float& b) {
     const bool second = feature0 + 1 < p.out;
     if constexpr (EPI == B200_EPI_STORE) {
         p.y[static_cast<int64_t>(row) * p.out + feature0] = a;
         if (second) p.y[static_cast<int64_t>(row) * p.out + feature0 + 1] = b;
     } else if constexpr (EPI == B200_EPI_RESIDUAL) {
         const int64_t at = static_cast<int64_t>(row) * p.out + feature0;
-        p.y[at] = __fadd_rn(p.residual[at], a);
-        if (second) p.y[at + 1] = __fadd_rn(p.residual[at + 1], b);
+        a = __fadd_rn(p.residual[at], a);
+        b = second ? __fadd_rn(p.residual[at + 1], b) : 0.0f;
+        p.y[at] = a;
+        if (second) p.y[at + 1] = b;
     } else if constexpr (EPI == B200_EPI_SWIGLU) {
         // rows 2j (gate_j) and 2j+1 (up_j) of the interleaved weight
-        p.y[static_cast<int64_t>(row) * (p.out >> 1) + (feature0 >> 1)] = __fmul_rn(silu_reference(a), b);
+        a = __fmul_rn(silu_reference(a), b);
+        if (p.y) p.y[static_cast<int64_t>(row) * (p.out >> 1) + (feature0 >> 1)] = a;
     } else {
         const int D = p.heads * p.head_dim, KV = p.kv_heads * p.head_dim;
         const int sequence = row / p.tokens_per_sequence;
@@ -89,5 +101,7 @@ __device__ __forceinline__ void linear_epilogue(const LinearParams& p, int row, 
 // Tensor-core streaming kernel for bf16 weights (linear_stream.cu); returns B200_UNSUPPORTED when the shape is
 // outside what it handles, in which case the caller uses the CUDA-core kernel.
 int launch_linear_stream(const LinearParams& p, int epilogue, cudaStream_t stream);
+// Feature tiles the streaming kernel cuts a [out, in] weight into on the current device (0: unsupported shape).
+int linear_stream_parts(int in, int out);
 
 }  // namespace b200

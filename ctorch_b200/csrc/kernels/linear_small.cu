@@ -160,7 +160,8 @@ __global__ void __launch_bounds__(kThreads) linear_small_kernel(const LinearPara
         if (lane != r) continue;
         const int row = row0 + r;
         if (row >= p.rows) continue;
-        linear_epilogue<EPI>(p, row, feature0, acc[0][r], acc[1][r]);
+        float a = acc[0][r], b = acc[1][r];
+        linear_epilogue<EPI>(p, row, feature0, a, b);
     }
 }
 
@@ -197,6 +198,31 @@ template <class W> int pick_epilogue(const LinearParams& p, int epilogue, bool v
 }  // namespace
 }  // namespace b200
 
+namespace b200 {
+namespace {
+// Copies and checks the operands of the q|k|v epilogue.
+int fill_qkv(LinearParams& p, int epilogue, const b200_qkv_args* qkv, int64_t rows, int64_t out) {
+    if (epilogue != B200_EPI_QKV) return B200_OK;
+        if (!qkv || !qkv->cache || !qkv->q_out || !qkv->cosine || !qkv->sine || qkv->tokens_per_sequence <= 0 || (qkv->head_dim & 1)
+            || out != static_cast<int64_t>(qkv->heads + 2 * qkv->kv_heads) * qkv->head_dim) {
+            set_error("b200_linear: inconsistent QKV epilogue arguments");
+            return B200_BAD_ARGUMENT;
+        }
+        p.heads = qkv->heads; p.kv_heads = qkv->kv_heads; p.head_dim = qkv->head_dim;
+        p.tokens_per_sequence = qkv->tokens_per_sequence; p.context = qkv->context;
+        p.cosine = qkv->cosine; p.sine = qkv->sine; p.kv = kv_view(qkv->cache); p.q_out = qkv->q_out;
+        if (p.kv.kv_heads != qkv->kv_heads || p.kv.head_dim != qkv->head_dim
+            || rows != static_cast<int64_t>(p.kv.sequences) * qkv->tokens_per_sequence) {
+            set_error("b200_linear: KV cache shape does not match the projection");
+            return B200_BAD_ARGUMENT;
+        }
+        p.lora_rank = qkv->lora_rank; p.lora_scale = qkv->lora_scale; p.low = qkv->low; p.q_up = qkv->q_up; p.v_up = qkv->v_up;
+        if (p.lora_rank > 0 && (!p.low || !p.q_up || !p.v_up)) { set_error("b200_linear: adapter pointers missing"); return B200_BAD_ARGUMENT; }
+        return B200_OK;
+}
+}  // namespace
+}  // namespace b200
+
 extern "C" int b200_linear(const float* x, int64_t rows, int64_t in, const void* weight, int32_t weight_dtype,
                            int64_t out, const void* norm_weight, int32_t norm_dtype, double eps,
                            b200_epilogue epilogue, const float* residual, const b200_qkv_args* qkv, float* y,
@@ -217,22 +243,9 @@ extern "C" int b200_linear(const float* x, int64_t rows, int64_t in, const void*
     p.residual = residual; p.y = y;
     if (epilogue == B200_EPI_RESIDUAL && !residual) { set_error("b200_linear: residual epilogue without residual"); return B200_BAD_ARGUMENT; }
     if (epilogue == B200_EPI_SWIGLU && (out & 1)) { set_error("b200_linear: SwiGLU epilogue needs interleaved gate/up rows"); return B200_BAD_ARGUMENT; }
-    if (epilogue == B200_EPI_QKV) {
-        if (!qkv || !qkv->cache || !qkv->q_out || !qkv->cosine || !qkv->sine || qkv->tokens_per_sequence <= 0 || (qkv->head_dim & 1)
-            || out != static_cast<int64_t>(qkv->heads + 2 * qkv->kv_heads) * qkv->head_dim) {
-            set_error("b200_linear: inconsistent QKV epilogue arguments");
-            return B200_BAD_ARGUMENT;
-        }
-        p.heads = qkv->heads; p.kv_heads = qkv->kv_heads; p.head_dim = qkv->head_dim;
-        p.tokens_per_sequence = qkv->tokens_per_sequence; p.context = qkv->context;
-        p.cosine = qkv->cosine; p.sine = qkv->sine; p.kv = kv_view(qkv->cache); p.q_out = qkv->q_out;
-        if (p.kv.kv_heads != qkv->kv_heads || p.kv.head_dim != qkv->head_dim
-            || rows != static_cast<int64_t>(p.kv.sequences) * qkv->tokens_per_sequence) {
-            set_error("b200_linear: KV cache shape does not match the projection");
-            return B200_BAD_ARGUMENT;
-        }
-        p.lora_rank = qkv->lora_rank; p.lora_scale = qkv->lora_scale; p.low = qkv->low; p.q_up = qkv->q_up; p.v_up = qkv->v_up;
-        if (p.lora_rank > 0 && (!p.low || !p.q_up || !p.v_up)) { set_error("b200_linear: adapter pointers missing"); return B200_BAD_ARGUMENT; }
+    {
+        const int status = fill_qkv(p, epilogue, qkv, rows, out);
+        if (status != B200_OK) return status;
     }
     cudaStream_t s = as_stream(stream);
     {
@@ -244,4 +257,39 @@ extern "C" int b200_linear(const float* x, int64_t rows, int64_t in, const void*
     const bool vector = (in * element) % 16 == 0 && reinterpret_cast<uintptr_t>(weight) % 16 == 0;
     return weight_dtype == B200_BF16 ? pick_epilogue<__nv_bfloat16>(p, epilogue, vector, s)
                                      : pick_epilogue<float>(p, epilogue, vector, s);
+}
+
+extern "C" int b200_linear_shadow(const b200_shadow_linear_args* args, void* stream) {
+    using namespace b200;
+    if (!args || !args->x_hi || !args->x_lo || !args->weight || args->rows < 0 || args->in <= 0 || args->out <= 0
+        || args->rows > INT32_MAX || args->in > INT32_MAX || args->out > INT32_MAX) {
+        set_error("b200_linear_shadow: bad pointer or size");
+        return B200_BAD_ARGUMENT;
+    }
+    if (args->rows == 0) return B200_OK;
+    const int epilogue = args->epilogue;
+    if ((epilogue != B200_EPI_SWIGLU && !args->y && epilogue != B200_EPI_QKV) || (epilogue == B200_EPI_RESIDUAL && !args->residual)
+        || (epilogue == B200_EPI_SWIGLU && (args->out & 1)) || (epilogue == B200_EPI_SWIGLU && !args->y && !args->out_hi)
+        || (args->out_hi && !args->out_lo) || (args->sumsq_in && args->parts_in <= 0)) {
+        set_error("b200_linear_shadow: inconsistent epilogue operands");
+        return B200_BAD_ARGUMENT;
+    }
+    LinearParams p{};
+    p.rows = static_cast<int>(args->rows); p.in = static_cast<int>(args->in); p.out = static_cast<int>(args->out);
+    p.weight = args->weight; p.weight_dtype = B200_BF16; p.eps = args->eps;
+    p.residual = args->residual; p.y = args->y;
+    p.x_hi = static_cast<const __nv_bfloat16*>(args->x_hi); p.x_lo = static_cast<const __nv_bfloat16*>(args->x_lo);
+    p.sumsq_in = args->sumsq_in; p.parts_in = args->parts_in;
+    p.out_hi = static_cast<__nv_bfloat16*>(args->out_hi); p.out_lo = static_cast<__nv_bfloat16*>(args->out_lo);
+    p.out_norm_weight = args->out_norm_weight; p.out_norm_dtype = args->out_norm_dtype; p.sumsq_out = args->sumsq_out;
+    const int status = fill_qkv(p, epilogue, args->qkv, args->rows, args->out);
+    if (status != B200_OK) return status;
+    const int launched = launch_linear_stream(p, epilogue, as_stream(stream));
+    if (launched == B200_UNSUPPORTED) set_error("b200_linear_shadow: shape [%d, %d] is outside the streaming kernel", p.out, p.in);
+    return launched;
+}
+
+extern "C" int32_t b200_linear_shadow_parts(int64_t in, int64_t out) {
+    if (in <= 0 || out <= 0 || in > INT32_MAX || out > INT32_MAX) return 0;
+    return b200::linear_stream_parts(static_cast<int>(in), static_cast<int>(out));
 }

@@ -63,7 +63,7 @@ __device__ __forceinline__ void bulk_load(void* dst, const void* src, uint32_t b
 //   then x_hi, x_lo                 [16][in_padded + 8] bf16 each
 //   then partial sums               [8 warps][16 rows][TF] f32
 //   then mbarriers                  full[slots], empty[slots]
-template <int TF, int EPI>
+template <int TF, int EPI, bool SHADOW>
 __global__ void __launch_bounds__(kThreads, 2) linear_stream_kernel(const StreamParams sp) {
     constexpr int NT = TF / 8;  // n-tiles of 8 features
     const LinearParams& p = sp.base;
@@ -77,6 +77,9 @@ __global__ void __launch_bounds__(kThreads, 2) linear_stream_kernel(const Stream
     float* partial = reinterpret_cast<float*>(x_lo + kRows * x_stride);
     uint64_t* full = reinterpret_cast<uint64_t*>(partial + kConsumers * kRows * TF);
     uint64_t* empty = full + sp.slots;
+    uint64_t* xbar = empty + sp.slots;                                   // shadow input copies
+    float* row_scale = reinterpret_cast<float*>(xbar + 1);               // [16]
+    float* slices = row_scale + kRows;                                   // [16 slices][16 rows] sums of squares
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int row0 = blockIdx.y * kRows;
@@ -88,6 +91,7 @@ __global__ void __launch_bounds__(kThreads, 2) linear_stream_kernel(const Stream
             mbar_init(&full[s], 1);
             mbar_init(&empty[s], kConsumers);
         }
+        mbar_init(xbar, 1);
         mbar_fence_init();
     }
     // Columns in .. in_padded+8 of the weight slots are never written by the copies; the last k-step may read up to
@@ -100,7 +104,6 @@ __global__ void __launch_bounds__(kThreads, 2) linear_stream_kernel(const Stream
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy stores before async-proxy copies
     }
     __syncthreads();
-    grid_launch_dependents();  // the next kernel may start its own weight stream while this one computes
 
     if (warp == kConsumers) {
         // ---- producer: lane i requests rows i, i+32, ... of every tile; lane 0 owns the barriers ----
@@ -133,6 +136,70 @@ __global__ void __launch_bounds__(kThreads, 2) linear_stream_kernel(const Stream
     B200_MARK(0);
     grid_dependency_wait();
     B200_MARK(1);
+    if constexpr (SHADOW) {
+        // ---- consumers, shadow input: the rows arrive by bulk copy in their final form (one memory round trip, no
+        // instructions); the row scales come from the producer's per-tile sums of squares.
+        const int valid = p.rows - row0 < kRows ? p.rows - row0 : kRows;
+        if (warp == 0) {
+            if (lane == 0) mbar_expect_tx(xbar, static_cast<uint32_t>(2 * valid * p.in * 2));
+            __syncwarp();
+            const int r = lane & 15;
+            if (r < valid) {
+                const __nv_bfloat16* plane = lane < 16 ? p.x_hi : p.x_lo;
+                bulk_load((lane < 16 ? x_hi : x_lo) + r * x_stride, plane + static_cast<int64_t>(row0 + r) * p.in,
+                          static_cast<uint32_t>(p.in * 2), xbar);
+            }
+        }
+        // Row scales: 16 threads per row-partial slice read the producer's per-tile sums of squares with independent
+        // loads, the slices are added in a fixed order (deterministic), thread r finishes row r.
+        {
+            const int r = threadIdx.x & 15, slice = threadIdx.x >> 4;  // 16 slices of the partials
+            float mine = 0.0f;
+            if (p.sumsq_in && row0 + r < p.rows) {
+                float v[8];
+#pragma unroll
+                for (int u = 0; u < 8; ++u) {
+                    const int i = slice + u * 16;
+                    v[u] = i < p.parts_in ? __ldg(p.sumsq_in + static_cast<int64_t>(i) * p.rows + row0 + r) : 0.0f;
+                }
+#pragma unroll
+                for (int u = 0; u < 8; ++u) mine += v[u];
+                for (int i = slice + 128; i < p.parts_in; i += 16) mine += __ldg(p.sumsq_in + static_cast<int64_t>(i) * p.rows + row0 + r);
+            }
+            slices[slice * kRows + r] = mine;
+        }
+        // The pad columns (in .. in_padded + 8) of all rows and the rows beyond the batch are zeros.
+        {
+            const int pad_words = (x_stride - p.in) >> 1;
+            for (int i = threadIdx.x; i < 2 * kRows * pad_words; i += kConsumers * 32) {
+                const int line = i / pad_words, word = i - line * pad_words;  // line = plane * 16 + row
+                reinterpret_cast<uint32_t*>((line >= kRows ? x_lo : x_hi) + (line & (kRows - 1)) * x_stride + p.in)[word] = 0u;
+            }
+            const int row_words = p.in >> 1;
+            for (int i = threadIdx.x; i < 2 * (kRows - valid) * row_words; i += kConsumers * 32) {
+                const int line = i / row_words, word = i - line * row_words;
+                const int plane = line / (kRows - valid), r = valid + line - plane * (kRows - valid);
+                reinterpret_cast<uint32_t*>((plane ? x_lo : x_hi) + r * x_stride)[word] = 0u;
+            }
+        }
+        if (!mbar_wait(xbar, 0)) {
+            if (lane == 0) atomicExch(sp.status, B200_DEVICE_TIMEOUT);
+        }
+        consumer_barrier();
+        if (threadIdx.x < kRows) {  // read again only after the barrier that follows the first tile's products
+            float scale = 1.0f;
+            if (p.sumsq_in && row0 + threadIdx.x < p.rows) {
+                float total = 0.0f;
+#pragma unroll
+                for (int slice = 0; slice < 16; ++slice) total += slices[slice * kRows + threadIdx.x];
+                scale = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(total, static_cast<float>(p.in)), static_cast<float>(p.eps))));
+            }
+            row_scale[threadIdx.x] = scale;
+        }
+        // Only now may the successor start: its weight prefetch would otherwise queue ahead of the copies above.
+        grid_launch_dependents();
+        B200_MARK(2);
+    } else
     // ---- consumers: stage the activations (the weight stream is already in flight) ----
     // Warp w owns rows w and w+8.  Both rows are read with independent 16-byte loads into registers (one L2 round
     // trip), reduced to their RMS (f32 squares per lane, f64 across lanes and for the square root), normalised,
@@ -203,6 +270,7 @@ __global__ void __launch_bounds__(kThreads, 2) linear_stream_kernel(const Stream
             stage_rows(std::integral_constant<int, 1>{}, warp + kConsumers);
         }
         consumer_barrier();
+        grid_launch_dependents();
         B200_MARK(2);
     }
 
@@ -218,6 +286,14 @@ __global__ void __launch_bounds__(kThreads, 2) linear_stream_kernel(const Stream
         float acc[NT][4];
 #pragma unroll
         for (int n = 0; n < NT; ++n) acc[n][0] = acc[n][1] = acc[n][2] = acc[n][3] = 0.0f;
+        // The residual values this thread will add in the tile's epilogue are requested now, under the products.
+        float2 carried = make_float2(0.0f, 0.0f);
+        if constexpr (SHADOW && EPI == B200_EPI_RESIDUAL && TF <= 32) {
+            const int r = threadIdx.x / (TF / 2), f = (threadIdx.x - r * (TF / 2)) * 2;
+            const int row = row0 + r, feature0 = tile * TF + f;
+            if (r < kRows && row < p.rows && feature0 + 1 < p.out)
+                carried = *reinterpret_cast<const float2*>(p.residual + static_cast<int64_t>(row) * p.out + feature0);
+        }
         {
             const int s = t % sp.slots;
             const uint32_t phase = (t / sp.slots) & 1;
@@ -270,17 +346,70 @@ __global__ void __launch_bounds__(kThreads, 2) linear_stream_kernel(const Stream
         }
         consumer_barrier();
         if (t == 0) B200_MARK(5);
-        for (int i = threadIdx.x; i < kRows * (TF / 2); i += kConsumers * 32) {
+        // items of one row are TF/2 consecutive threads of a warp: thread i finishes the feature pair (r, f)
+        for (int base = 0; base < kRows * (TF / 2); base += kConsumers * 32) {
+            const int i = base + threadIdx.x;
             const int r = i / (TF / 2), f = (i - r * (TF / 2)) * 2;
+            const bool in_tile = i < kRows * (TF / 2);
             float a = 0.0f, b = 0.0f;
+            if (in_tile) {
 #pragma unroll
-            for (int w = 0; w < kConsumers; ++w) {
-                const float2 v = *reinterpret_cast<const float2*>(partial + (w * kRows + r) * TF + f);
-                a += v.x;
-                b += v.y;
+                for (int w = 0; w < kConsumers; ++w) {
+                    const float2 v = *reinterpret_cast<const float2*>(partial + (w * kRows + r) * TF + f);
+                    a += v.x;
+                    b += v.y;
+                }
             }
             const int row = row0 + r, feature0 = tile * TF + f;
-            if (row < p.rows && feature0 < p.out) linear_epilogue<EPI>(p, row, feature0, a, b);
+            const bool live = in_tile && row < p.rows && feature0 < p.out;
+            if constexpr (SHADOW) {
+                if (in_tile) { a *= row_scale[r]; b *= row_scale[r]; }
+            }
+            if constexpr (SHADOW && EPI == B200_EPI_RESIDUAL && TF <= 32) {
+                if (live) {  // out is even on the shadow path, so the pair is complete
+                    a = __fadd_rn(carried.x, a);
+                    b = __fadd_rn(carried.y, b);
+                    *reinterpret_cast<float2*>(p.y + static_cast<int64_t>(row) * p.out + feature0) = make_float2(a, b);
+                }
+            } else {
+                if (live) linear_epilogue<EPI>(p, row, feature0, a, b);
+            }
+            if constexpr (SHADOW && EPI == B200_EPI_RESIDUAL) {
+                // a, b now hold the new residual-stream values: shadow for the consumer, row sums of squares for its norm
+                float square = live ? a * a + (feature0 + 1 < p.out ? b * b : 0.0f) : 0.0f;
+#pragma unroll
+                for (int o = 1; o < TF / 2; o <<= 1) square += __shfl_xor_sync(0xffffffffu, square, o);
+                if (p.sumsq_out && f == 0 && in_tile && row < p.rows) p.sumsq_out[static_cast<int64_t>(tile) * p.rows + row] = square;
+                if (p.out_hi && live) {
+                    float wa = 1.0f, wb = 1.0f;
+                    if (p.out_norm_weight) {
+                        const bool second = feature0 + 1 < p.out;
+                        if (p.out_norm_dtype == B200_BF16) {
+                            const __nv_bfloat16* w = static_cast<const __nv_bfloat16*>(p.out_norm_weight) + feature0;
+                            wa = __bfloat162float(w[0]);
+                            wb = second ? __bfloat162float(w[1]) : 0.0f;
+                        } else {
+                            const float* w = static_cast<const float*>(p.out_norm_weight) + feature0;
+                            wa = w[0];
+                            wb = second ? w[1] : 0.0f;
+                        }
+                    }
+                    const float va = __fmul_rn(a, wa), vb = __fmul_rn(b, wb);
+                    const __nv_bfloat162 hi = __floats2bfloat162_rn(va, vb);
+                    const __nv_bfloat162 lo = __floats2bfloat162_rn(va - __low2float(hi), vb - __high2float(hi));
+                    const int64_t at = static_cast<int64_t>(row) * p.out + feature0;  // out is even on this path
+                    *reinterpret_cast<__nv_bfloat162*>(p.out_hi + at) = hi;
+                    *reinterpret_cast<__nv_bfloat162*>(p.out_lo + at) = lo;
+                }
+            }
+            if constexpr (SHADOW && EPI == B200_EPI_SWIGLU) {
+                if (p.out_hi && live) {
+                    const __nv_bfloat16 hi = __float2bfloat16_rn(a);
+                    const int64_t at = static_cast<int64_t>(row) * (p.out >> 1) + (feature0 >> 1);
+                    p.out_hi[at] = hi;
+                    p.out_lo[at] = __float2bfloat16_rn(a - __bfloat162float(hi));
+                }
+            }
         }
         consumer_barrier();
         if (t == 0) B200_MARK(6);
@@ -289,10 +418,15 @@ __global__ void __launch_bounds__(kThreads, 2) linear_stream_kernel(const Stream
     trace_end(trace);
 }
 
-template <int TF, int EPI> int launch_tile(const StreamParams& sp, size_t smem, int ctas, int row_tiles, cudaStream_t stream) {
-    auto kernel = linear_stream_kernel<TF, EPI>;
+template <int TF, int EPI, bool SHADOW> int launch_mode(const StreamParams& sp, size_t smem, int ctas, int row_tiles, cudaStream_t stream) {
+    auto kernel = linear_stream_kernel<TF, EPI, SHADOW>;
     B200_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
     return cuda_status(launch_dependent(kernel, dim3(ctas, row_tiles), dim3(kThreads), smem, stream, sp), "linear_stream_kernel launch");
+}
+
+template <int TF, int EPI> int launch_tile(const StreamParams& sp, size_t smem, int ctas, int row_tiles, cudaStream_t stream) {
+    return sp.base.x_hi ? launch_mode<TF, EPI, true>(sp, smem, ctas, row_tiles, stream)
+                        : launch_mode<TF, EPI, false>(sp, smem, ctas, row_tiles, stream);
 }
 
 template <int EPI> int pick_tile(const StreamParams& sp, size_t smem, int ctas, int row_tiles, cudaStream_t stream) {
@@ -313,41 +447,61 @@ int sm_count(int device) {
     return counts[device];
 }
 
+// Tile size, ring depth and shared-memory size for a weight matrix [out, in]; false when nothing fits.
+bool choose_tiling(int in, int out, int sms, StreamParams& sp, size_t& smem) {
+    sp.in_padded = (in + 63) & ~63;
+    const size_t row_bytes = static_cast<size_t>(sp.in_padded + 8) * 2;
+    // Two CTAs per SM (this kernel's tail next to the early-started successor) when the activations leave room
+    // for at least two weight slots in half of the shared memory; else one CTA per SM.
+    const size_t half = 110 * 1024, whole = 220 * 1024;
+    const size_t budget = 2 * kRows * row_bytes + kConsumers * kRows * 8 * 4 + 1664 + 2 * 8 * row_bytes <= half ? half : whole;
+    // Smallest tile with which one round of CTAs covers the matrix (every further tile of a CTA costs a reduction
+    // round); smaller tiles when the ring would not hold two of them.
+    int tf = 8;
+    while (tf < 64 && (out + tf - 1) / tf > sms) tf <<= 1;
+    size_t fixed = 0;
+    int slots = 0;
+    for (;; tf >>= 1) {
+        fixed = 2 * kRows * row_bytes + static_cast<size_t>(kConsumers) * kRows * tf * 4 + 128 + 1536;
+        slots = fixed < budget ? static_cast<int>((budget - fixed) / (tf * row_bytes)) : 0;
+        if (slots >= 2 || tf == 8) break;
+    }
+    if (slots < 2) return false;
+    if (slots > 8) slots = 8;
+    sp.tile_features = tf;
+    sp.slots = slots;
+    sp.tiles = (out + tf - 1) / tf;
+    smem = fixed + static_cast<size_t>(slots) * tf * row_bytes;
+    return true;
+}
+
 }  // namespace
 
+int linear_stream_parts(int in, int out) {
+    if (in > kMaxIn || (in & 7) || in <= 0 || out <= 0) return 0;
+    int device = 0;
+    if (cudaGetDevice(&device) != cudaSuccess) return 0;
+    StreamParams sp{};
+    size_t smem = 0;
+    return choose_tiling(in, out, sm_count(device), sp, smem) ? sp.tiles : 0;
+}
+
 int launch_linear_stream(const LinearParams& p, int epilogue, cudaStream_t stream) {
-    if (p.weight_dtype != B200_BF16 || p.in > kMaxIn || (p.in & 7) || (reinterpret_cast<uintptr_t>(p.weight) & 15)
-        || (reinterpret_cast<uintptr_t>(p.x) & 15))
+    if (p.weight_dtype != B200_BF16 || p.in > kMaxIn || (p.in & 7) || (reinterpret_cast<uintptr_t>(p.weight) & 15))
         return B200_UNSUPPORTED;
+    if (p.x_hi ? ((reinterpret_cast<uintptr_t>(p.x_hi) | reinterpret_cast<uintptr_t>(p.x_lo)) & 15) || !p.x_lo
+               : (reinterpret_cast<uintptr_t>(p.x) & 15) != 0)
+        return B200_UNSUPPORTED;
+    if (p.out_hi && (p.out & 1)) return B200_UNSUPPORTED;
     int device = 0;
     B200_CUDA(cudaGetDevice(&device));
     const int sms = sm_count(device);
 
     StreamParams sp{};
     sp.base = p;
-    sp.in_padded = (p.in + 63) & ~63;
     sp.status = device_status_word(device);
-    const size_t row_bytes = static_cast<size_t>(sp.in_padded + 8) * 2;
-    // Two CTAs per SM (this kernel's tail next to the early-started successor) when the activations leave room
-    // for at least two weight slots in half of the shared memory; else one CTA per SM.
-    const size_t half = 110 * 1024, whole = 220 * 1024;
-    const size_t budget = 2 * kRows * row_bytes + kConsumers * kRows * 8 * 4 + 384 + 2 * 8 * row_bytes <= half ? half : whole;
-    // Largest tile that still gives every SM several tiles; smaller tiles when the ring would not hold two of them.
-    int tf = 64;
-    while (tf > 8 && (p.out + tf - 1) / tf < 4 * sms) tf >>= 1;
-    size_t fixed = 0;
-    int slots = 0;
-    for (;; tf >>= 1) {
-        fixed = 2 * kRows * row_bytes + static_cast<size_t>(kConsumers) * kRows * tf * 4 + 128 + 256;
-        slots = fixed < budget ? static_cast<int>((budget - fixed) / (tf * row_bytes)) : 0;
-        if (slots >= 2 || tf == 8) break;
-    }
-    if (slots < 2) return B200_UNSUPPORTED;
-    if (slots > 8) slots = 8;
-    sp.tile_features = tf;
-    sp.slots = slots;
-    sp.tiles = (p.out + tf - 1) / tf;
-    const size_t smem = fixed + static_cast<size_t>(slots) * tf * row_bytes;
+    size_t smem = 0;
+    if (!choose_tiling(p.in, p.out, sms, sp, smem)) return B200_UNSUPPORTED;
 
     const int row_tiles = (p.rows + kRows - 1) / kRows;
     const int ctas = sp.tiles < sms ? sp.tiles : sms;

@@ -312,3 +312,82 @@ extern "C" int b200_scaled_add(float* y, const float* x, float scale, int64_t co
     b200::scaled_add_kernel<<<b200::blocks_for(count), 256, 0, as_stream(stream)>>>(y, x, scale, count);
     return cuda_status(cudaGetLastError(), "scaled_add_kernel launch");
 }
+
+namespace b200 {
+namespace {
+// One CTA per row: gather, f32 copy, shadow of row * norm_weight, the row's sum of squares (parts = 1).
+template <class T>
+__global__ void embedding_shadow_kernel(const T* table, const int64_t* ids, int64_t vocab, int64_t width, const void* norm_weight,
+                                        int norm_dtype, float* out, __nv_bfloat16* out_hi, __nv_bfloat16* out_lo,
+                                        float* sumsq_out, int32_t* status) {
+    __shared__ float partial[32];
+    grid_dependency_wait();   // the ids may come from the previous step's token feedback
+    grid_launch_dependents();
+    const int64_t row = blockIdx.x;
+    int64_t id = ids ? ids[row] : row;   // without ids the table is the activation matrix itself
+    if (id < 0 || id >= vocab) {
+        if (threadIdx.x == 0) atomicExch(status, B200_BAD_ARGUMENT);
+        id = id < 0 ? 0 : vocab - 1;
+    }
+    float squares = 0.0f;
+    for (int64_t c = threadIdx.x; c < width; c += blockDim.x) {
+        const float v = load_as_f32(table, id * width + c);
+        if (out) out[row * width + c] = v;
+        squares += v * v;
+        float w = 1.0f;
+        if (norm_weight)
+            w = norm_dtype == B200_BF16 ? __bfloat162float(static_cast<const __nv_bfloat16*>(norm_weight)[c])
+                                        : static_cast<const float*>(norm_weight)[c];
+        const float scaled = __fmul_rn(v, w);
+        const __nv_bfloat16 hi = __float2bfloat16_rn(scaled);
+        out_hi[row * width + c] = hi;
+        out_lo[row * width + c] = __float2bfloat16_rn(scaled - __bfloat162float(hi));
+    }
+    squares = warp_sum(squares);
+    if ((threadIdx.x & 31) == 0) partial[threadIdx.x >> 5] = squares;
+    __syncthreads();
+    if (threadIdx.x < 32) {
+        float v = threadIdx.x < (blockDim.x >> 5) ? partial[threadIdx.x] : 0.0f;
+        v = warp_sum(v);
+        if (threadIdx.x == 0) sumsq_out[row] = v;
+    }
+}
+}  // namespace
+}  // namespace b200
+
+extern "C" int b200_embedding_shadow(const void* table, int32_t table_dtype, const int64_t* ids, int64_t rows, int64_t vocab,
+                                     int64_t width, const void* norm_weight, int32_t norm_dtype, float* out, void* out_hi,
+                                     void* out_lo, float* sumsq_out, void* stream) {
+    if (!table || !ids || !out || !out_hi || !out_lo || !sumsq_out || rows < 0 || vocab <= 0 || width <= 0) {
+        set_error("b200_embedding_shadow: bad pointer or size");
+        return B200_BAD_ARGUMENT;
+    }
+    if (rows == 0) return B200_OK;
+    int device = 0;
+    B200_CUDA(cudaGetDevice(&device));
+    int32_t* status = device_status_word(device);
+    auto* hi = static_cast<__nv_bfloat16*>(out_hi);
+    auto* lo = static_cast<__nv_bfloat16*>(out_lo);
+    if (table_dtype == B200_BF16)
+        return cuda_status(launch_dependent(b200::embedding_shadow_kernel<__nv_bfloat16>, dim3(static_cast<unsigned>(rows)), dim3(256), 0,
+                                            as_stream(stream), static_cast<const __nv_bfloat16*>(table), ids, vocab, width, norm_weight,
+                                            static_cast<int>(norm_dtype), out, hi, lo, sumsq_out, status), "embedding_shadow_kernel launch");
+    if (table_dtype == B200_F32)
+        return cuda_status(launch_dependent(b200::embedding_shadow_kernel<float>, dim3(static_cast<unsigned>(rows)), dim3(256), 0,
+                                            as_stream(stream), static_cast<const float*>(table), ids, vocab, width, norm_weight,
+                                            static_cast<int>(norm_dtype), out, hi, lo, sumsq_out, status), "embedding_shadow_kernel launch");
+    set_error("b200_embedding_shadow: table dtype %d is not f32 or bf16", table_dtype);
+    return B200_UNSUPPORTED;
+}
+
+extern "C" int b200_shadow_from_rows(const float* x, int64_t rows, int64_t width, const void* norm_weight, int32_t norm_dtype,
+                                     void* out_hi, void* out_lo, float* sumsq_out, void* stream) {
+    if (!x || !out_hi || !out_lo || !sumsq_out || rows < 0 || width <= 0) { set_error("b200_shadow_from_rows: bad pointer or size"); return B200_BAD_ARGUMENT; }
+    if (rows == 0) return B200_OK;
+    int device = 0;
+    B200_CUDA(cudaGetDevice(&device));
+    return cuda_status(launch_dependent(b200::embedding_shadow_kernel<float>, dim3(static_cast<unsigned>(rows)), dim3(256), 0, as_stream(stream),
+                                        x, static_cast<const int64_t*>(nullptr), rows, width, norm_weight, static_cast<int>(norm_dtype),
+                                        static_cast<float*>(nullptr), static_cast<__nv_bfloat16*>(out_hi), static_cast<__nv_bfloat16*>(out_lo),
+                                        sumsq_out, device_status_word(device)), "shadow_from_rows launch");
+}

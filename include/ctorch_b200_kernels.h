@@ -116,6 +116,46 @@ B200_API int b200_linear(const float* x, int64_t rows, int64_t in, const void* w
                          int64_t out, const void* norm_weight, int32_t norm_dtype, double eps,
                          b200_epilogue epilogue, const float* residual, const b200_qkv_args* qkv, float* y, void* stream);
 
+/* ---- activation shadows (no counterpart in the reference) -------------------------------------------------------
+ * Between the kernels of a decode step an f32 activation matrix can travel as a "shadow": two bf16 planes hi + lo
+ * (hi = bf16(v), lo = bf16(v - hi), about 16 mantissa bits together), the operand form of the tensor cores.  The
+ * consumer fetches its rows with bulk copies straight into shared memory instead of converting f32 in every CTA.
+ * An RMSNorm between producer and consumer is split: the producer folds the norm weight into the shadow and leaves
+ * per-row partial sums of squares of the un-weighted values; the consumer multiplies its results by
+ * 1/sqrt(sum/width + eps).  The f32 arithmetic differs from the reference's f64 norm by rounding only. */
+typedef struct b200_shadow_linear_args {
+    const void* x_hi;              /* bf16 [rows, in] */
+    const void* x_lo;
+    int64_t rows, in;
+    const void* weight;            /* bf16 [out, in] */
+    int64_t out;
+    const float* sumsq_in;         /* [parts_in][rows] or NULL (no row scale) */
+    int32_t parts_in;
+    double eps;
+    b200_epilogue epilogue;
+    const float* residual;         /* B200_EPI_RESIDUAL */
+    const b200_qkv_args* qkv;      /* B200_EPI_QKV */
+    float* y;                      /* f32 result; may be NULL for B200_EPI_SWIGLU when only the shadow is wanted */
+    void* out_hi;                  /* optional output shadow: residual epilogue [rows, out], SwiGLU epilogue [rows, out/2] */
+    void* out_lo;
+    const void* out_norm_weight;   /* residual epilogue: weight [out] of the norm that follows, folded into the shadow */
+    int32_t out_norm_dtype;
+    float* sumsq_out;              /* residual epilogue: [b200_linear_shadow_parts(in, out)][rows] */
+} b200_shadow_linear_args;
+/* B200_UNSUPPORTED when the shape is outside the streaming kernel (in > 2048 or in % 8 != 0). */
+B200_API int b200_linear_shadow(const b200_shadow_linear_args* args, void* stream);
+/* Number of row-sum partials a residual-epilogue call with these sizes writes (its feature tiles), 0 if unsupported. */
+B200_API int32_t b200_linear_shadow_parts(int64_t in, int64_t out);
+/* b200_embedding that also writes the shadow of out * norm_weight and one partial sum of squares per row ([1][rows]). */
+B200_API int b200_embedding_shadow(const void* table, int32_t table_dtype, const int64_t* ids, int64_t rows, int64_t vocab,
+                                   int64_t width, const void* norm_weight, int32_t norm_dtype, float* out, void* out_hi,
+                                   void* out_lo, float* sumsq_out, void* stream);
+
+/* Shadow of x * norm_weight (norm_weight may be NULL) and one partial sum of squares per row ([1][rows]) for f32 rows
+ * that did not come out of one of the kernels above. */
+B200_API int b200_shadow_from_rows(const float* x, int64_t rows, int64_t width, const void* norm_weight, int32_t norm_dtype,
+                                   void* out_hi, void* out_lo, float* sumsq_out, void* stream);
+
 /* Split-K flash-decode grouped-query attention over the paged cache.
  * Replaces detail::grouped_attention / grouped_block / attention_weights (src/ops/attention.cpp:65-95,161-188)
  * and the softmax of src/kernels/cpu/reduction.cpp:155-203 for queries whose keys are the cache:
@@ -132,6 +172,12 @@ B200_API size_t b200_attention_scratch_bytes(int64_t rows, int32_t heads, int32_
 B200_API int b200_attention_decode(const float* q, int64_t rows, int32_t tokens_per_sequence, int32_t heads,
                                    const b200_kv_cache* cache, int32_t max_length, int32_t causal, void* scratch,
                                    size_t scratch_bytes, float* out, void* stream);
+
+/* b200_attention_decode writing its result as a shadow (bf16 planes [rows, heads*head_dim]) for a following
+ * b200_linear_shadow instead of f32. */
+B200_API int b200_attention_decode_shadow(const float* q, int64_t rows, int32_t tokens_per_sequence, int32_t heads,
+                                          const b200_kv_cache* cache, int32_t max_length, int32_t causal, void* scratch,
+                                          size_t scratch_bytes, void* out_hi, void* out_lo, void* stream);
 
 /* No counterpart in the reference.  b200_attention_decode for callers that must not allocate and have no workspace
  * of their own to hand in: a serving loop whose device memory was budgeted once at start-up, a host runtime whose

@@ -306,3 +306,87 @@ def test_rotary_permute_feedback_helpers():
     B.kcheck(B.lib().b200_permute_0213(xd.data_ptr(), 3, 2, 4, 16, p.data_ptr(), stream()))
     sync()
     assert np.array_equal(p.cpu().numpy(), x.transpose(0, 2, 1, 3))
+
+
+def shadow_to_f32(hi, lo):
+    return (hi.float() + lo.float()).cpu().numpy()
+
+
+@pytest.mark.parametrize("rows,inner,out", [(16, 768, 1280), (5, 2048, 768), (16, 768, 4096), (3, 72, 40)])
+def test_shadow_protocol_norm_linear_residual(rows, inner, out):
+    """Activations travelling as bf16 hi + lo planes: producer folds the norm weight and leaves row sums of squares,
+    the consumer applies 1/sqrt(mean + eps); residual epilogue writes the next shadow and its partial sums."""
+    l = B.lib()
+    rng = np.random.default_rng(rows + inner + out)
+    x = rng.standard_normal((rows, inner), dtype=np.float32) * 2
+    norm = W.bf16_bits((1 + 0.1 * rng.standard_normal(inner)).astype(np.float32))
+    w = W.bf16_bits(0.05 * rng.standard_normal((out, inner), dtype=np.float32))
+    res = rng.standard_normal((rows, out), dtype=np.float32)
+    next_norm = W.bf16_bits((1 + 0.1 * rng.standard_normal(out)).astype(np.float32))
+    xd, nd, wd, rd, nnd = dev(x), bf16_dev(norm), bf16_dev(w), dev(res), bf16_dev(next_norm)
+    hi = torch.zeros((rows, inner), dtype=torch.bfloat16, device="cuda")
+    lo = torch.zeros_like(hi)
+    sq = torch.zeros((1, rows), dtype=torch.float32, device="cuda")
+    torch.cuda.synchronize()
+    B.kcheck(l.b200_shadow_from_rows(xd.data_ptr(), rows, inner, nd.data_ptr(), B.BF16, hi.data_ptr(), lo.data_ptr(), sq.data_ptr(), stream()))
+    sync()
+    assert rel(shadow_to_f32(hi, lo), x * W.bf16_to_f32(norm)) < 2e-5
+    assert rel(sq.cpu().numpy()[0], (x.astype(np.float64) ** 2).sum(axis=1)) < 1e-5
+    parts = l.b200_linear_shadow_parts(inner, out)
+    assert parts > 0
+    y = torch.zeros((rows, out), dtype=torch.float32, device="cuda")
+    ohi = torch.zeros((rows, out), dtype=torch.bfloat16, device="cuda")
+    olo = torch.zeros_like(ohi)
+    osq = torch.zeros((parts, rows), dtype=torch.float32, device="cuda")
+    torch.cuda.synchronize()
+    args = B.ShadowLinearArgs(hi.data_ptr(), lo.data_ptr(), rows, inner, wd.data_ptr(), out, sq.data_ptr(), 1, 1e-5, 1, rd.data_ptr(), None,
+                              y.data_ptr(), ohi.data_ptr(), olo.data_ptr(), nnd.data_ptr(), B.BF16, osq.data_ptr())
+    B.kcheck(l.b200_linear_shadow(C.byref(args), stream()))
+    sync()
+    want = res + oracle.linear(oracle.rms_norm(x, W.bf16_to_f32(norm), 1e-5), w)
+    assert rel(y.cpu().numpy(), want) < 2e-5
+    assert rel(shadow_to_f32(ohi, olo), want * W.bf16_to_f32(next_norm)) < 3e-5
+    assert rel(osq.cpu().numpy().sum(axis=0), (want.astype(np.float64) ** 2).sum(axis=1)) < 1e-4
+
+
+def test_shadow_protocol_swiglu_and_attention_output():
+    l = B.lib()
+    rng = np.random.default_rng(77)
+    rows, inner, hidden = 16, 768, 2048
+    x = rng.standard_normal((rows, inner), dtype=np.float32)
+    gate = W.bf16_bits(0.05 * rng.standard_normal((hidden, inner), dtype=np.float32))
+    up = W.bf16_bits(0.05 * rng.standard_normal((hidden, inner), dtype=np.float32))
+    inter = np.empty((2 * hidden, inner), dtype=np.uint16)
+    inter[0::2], inter[1::2] = gate, up
+    xd, wd = dev(x), bf16_dev(inter)
+    hi = torch.zeros((rows, inner), dtype=torch.bfloat16, device="cuda")
+    lo = torch.zeros_like(hi)
+    sq = torch.zeros((1, rows), dtype=torch.float32, device="cuda")
+    ahi = torch.zeros((rows, hidden), dtype=torch.bfloat16, device="cuda")
+    alo = torch.zeros_like(ahi)
+    torch.cuda.synchronize()
+    B.kcheck(l.b200_shadow_from_rows(xd.data_ptr(), rows, inner, None, 0, hi.data_ptr(), lo.data_ptr(), sq.data_ptr(), stream()))
+    args = B.ShadowLinearArgs(hi.data_ptr(), lo.data_ptr(), rows, inner, wd.data_ptr(), 2 * hidden, None, 0, 0.0, 2, None, None, None,
+                              ahi.data_ptr(), alo.data_ptr(), None, 0, None)
+    B.kcheck(l.b200_linear_shadow(C.byref(args), stream()))
+    sync()
+    want = oracle.silu_mul(oracle.linear(x, gate), oracle.linear(x, up))
+    assert rel(shadow_to_f32(ahi, alo), want) < 3e-5
+    # attention result as a shadow equals the f32 result
+    n, heads, kv_heads, hd, cap = 4, 12, 4, 64, 300
+    cache = Cache(B.BF16, n, kv_heads, hd, cap)
+    k = rng.standard_normal((n, kv_heads, cap, hd), dtype=np.float32)
+    v = rng.standard_normal((n, kv_heads, cap, hd), dtype=np.float32)
+    cache.append(k, v)
+    cache.set_lengths(np.array([299, 10, 64, 128], dtype=np.int32))
+    q = rng.standard_normal((n, heads, hd), dtype=np.float32)
+    plain = attention(q, cache, 1, heads, cap)
+    qd = dev(q)
+    shi = torch.zeros((n, heads * hd), dtype=torch.bfloat16, device="cuda")
+    slo = torch.zeros_like(shi)
+    scratch = torch.empty((1 << 20,), dtype=torch.uint8, device="cuda")
+    torch.cuda.synchronize()
+    B.kcheck(l.b200_attention_decode_shadow(qd.data_ptr(), n, 1, heads, cache.h, cap, 1, scratch.data_ptr(), 1 << 20, shi.data_ptr(),
+                                            slo.data_ptr(), stream()))
+    sync()
+    assert rel(shadow_to_f32(shi, slo), plain) < 2e-5

@@ -45,8 +45,8 @@ def test_static_scratch_matches_caller_scratch_twice(dtype, head_dim, heads, kv_
     l = B.lib()
     stream = l.dl_b200_stream(B.cuda(0))
     rng = np.random.default_rng(head_dim)
-    sequences, capacity = 6, 700
-    lengths = np.array([699, 5, 130, 64, 400, 257], dtype=np.int32)    # several splits, ragged
+    sequences, capacity = 6, 1200
+    lengths = np.array([1199, 5, 130, 64, 400, 1025], dtype=np.int32)    # several splits, ragged
     cache = _cache(dtype, sequences, kv_heads, head_dim, capacity)
     try:
         k = rng.standard_normal((sequences, kv_heads, capacity, head_dim), dtype=np.float32)
