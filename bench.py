@@ -231,18 +231,112 @@ def run_b200(args, spec, weights) -> dict:
     return line if rank == 0 else {}
 
 
+def run_c3(args) -> dict:
+    """BASELINE configuration 3: decode attention only (batch 64, 32 query / 8 KV heads, head_dim 128, bf16 cache,
+    per-sequence contexts uniform in [1024, 32768], one new token per sequence per step)."""
+    import ctypes as C
+
+    import torch
+
+    import ctorch_b200 as B
+    rank, world, local, dist = distributed()
+    cfg = dict(W.CONFIGS["c3"])
+    if args.small:   # profiling-sized case of the same kernel: a few hundred MB of K and V, still far above L2
+        cfg.update(batch=16, min_context=1024, max_context=8192)
+    n, heads, kv_heads, hd = cfg["batch"], cfg["heads"], cfg["kv_heads"], cfg["head_dim"]
+    capacity = cfg["max_context"]
+    l = B.lib()
+    torch.cuda.set_device(local)
+    stream = l.dl_b200_stream(B.cuda(local))
+    cache = C.c_void_p()
+    B.kcheck(l.b200_kv_cache_create(local, B.BF16, n, kv_heads, hd, capacity, 64, C.byref(cache)))
+    generator = torch.Generator(device="cuda").manual_seed(7 + rank)
+    chunk = 1024
+    handles = (C.c_void_p * 1)(cache)
+    for _ in range(capacity // chunk):     # K, V ~ N(0, 1), appended chunk by chunk through the C ABI
+        k = torch.randn((n, kv_heads, chunk, hd), device="cuda", generator=generator)
+        v = torch.randn((n, kv_heads, chunk, hd), device="cuda", generator=generator)
+        torch.cuda.synchronize()
+        B.kcheck(l.b200_kv_cache_append(cache, k.data_ptr(), v.data_ptr(), chunk, stream))
+        B.kcheck(l.b200_kv_cache_advance(handles, 1, chunk, stream))
+        B.synchronize(local)
+    lengths = np.random.default_rng(11 + rank).integers(cfg["min_context"], capacity + 1, size=n).astype(np.int32)
+    B.kcheck(l.b200_kv_cache_set_lengths(cache, (lengths - 1).ctypes.data_as(C.POINTER(C.c_int32)), stream))
+    q = torch.randn((n, heads, hd), device="cuda", generator=generator)
+    out = torch.zeros((n, heads * hd), device="cuda")
+    need = l.b200_attention_scratch_bytes(n, heads, kv_heads, hd, capacity, 64)
+    scratch = torch.empty((need,), dtype=torch.uint8, device="cuda")
+    torch.cuda.synchronize()
+
+    def step():
+        B.kcheck(l.b200_attention_decode(q.data_ptr(), n, 1, heads, cache, capacity, 1, scratch.data_ptr(), need, out.data_ptr(), stream))
+
+    sampler = ClockSampler(local)
+    sampler.start()
+    for _ in range(args.warmup):
+        step()
+    B.synchronize(local)
+    barrier(dist, local)
+    B.timer_start(local)
+    for _ in range(args.steps):
+        step()
+    ms = max_over_ranks(B.timer_stop(local), dist, local)
+    # host in the loop: q from pinned host memory every step, result read back
+    q_host = q.cpu().pin_memory()
+    out_host = torch.empty((n, heads * hd)).pin_memory()
+    barrier(dist, local)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        q.copy_(q_host, non_blocking=True)
+        torch.cuda.synchronize()
+        step()
+        B.synchronize(local)
+        out_host.copy_(out, non_blocking=True)
+        torch.cuda.synchronize()
+    e2e_ms = max_over_ranks((time.perf_counter() - t0) * 1000.0, dist, local)
+    clocks = sampler.stop()
+    status = C.c_int32()
+    B.kcheck(l.b200_take_device_status(local, stream, C.byref(status)))
+    assert status.value == 0 and bool(torch.isfinite(out).all())
+    l.b200_kv_cache_release(cache)
+    bytes_per_step = float(lengths.astype(np.int64).sum()) * 2 * kv_heads * hd * 2
+    peak, peak_kind = measured_peaks()
+    achieved = bytes_per_step / (ms / args.steps / 1000.0) / 1e9
+    line = {"metric": METRIC, "value": world * n * args.steps / (ms / 1000.0), "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "bf16 KV, f32 accumulate", "data": "synthetic",
+            "config": {"workload": "c3 decode-attention microbench" + (" (small)" if args.small else ""), "batch_per_gpu": n, "heads": heads, "kv_heads": kv_heads,
+                       "head_dim": hd, "mean_context": float(lengths.mean()), "l2": "inputs larger than L2: %.2f GB of K and V per step" % (bytes_per_step / 1e9)},
+            "clocks": clocks,
+            "e2e": {"value": world * n * args.steps / (e2e_ms / 1000.0), "unit": UNIT, "h2d_bytes_per_step": n * heads * hd * 4,
+                    "d2h_bytes_per_step": n * heads * hd * 4, "ms_per_step": e2e_ms / args.steps},
+            "gpu_launches": 2 * args.steps,
+            "roofline": {"bound": "hbm", "kernel": "attention_mma_kernel<128> (+ attention_combine_kernel)", "achieved": achieved, "peak": peak,
+                         "unit": "GB/s", "frac": achieved / peak, "peak_kind": peak_kind, "traffic": None,
+                         "algorithmic_bytes": bytes_per_step, "launch_ms": ms / args.steps}}
+    if dist is not None:
+        dist.destroy_process_group()
+    return line if rank == 0 else {}
+
+
 def main():
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
     parser.add_argument("--steps", type=int, default=64)
     parser.add_argument("--warmup", type=int, default=8)
     parser.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    parser.add_argument("--workload", default="c2", choices=["c1", "c2", "c4"])
+    parser.add_argument("--workload", default="c2", choices=["c1", "c2", "c3", "c4"])
     parser.add_argument("--cpu-steps", type=int, default=24, help="timed CPU-baseline steps of the default run")
     parser.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    parser.add_argument("--small", action="store_true", help="c3 only: batch 16, contexts up to 8192 (profiler captures)")
     args = parser.parse_args()
     if args.warmup < 3:
         args.warmup = 3
+    if args.workload == "c3":
+        line = run_c3(args)
+        if line:
+            print(json.dumps(line))
+        return
     spec = dict(W.CONFIGS[args.workload])
     weights = W.make_weights(spec)
     line = run_reference(args, spec, weights) if args.impl == "reference" else run_b200(args, spec, weights)

@@ -7,7 +7,7 @@
 //
 // Fast path (bf16 pools, 64-token pages, head_dim 64 or 128): a producer warp stages K and V pages with
 // non-multicast TMA (cp.async.bulk.tensor, 128-byte swizzle) through a ring of shared-memory stages guarded by
-// mbarriers; four consumer warps take 16 tokens of each page, compute Q.K^T and P.V with bf16 mma.sync
+// mbarriers; eight consumer warps in two groups (a group per page, 16 tokens per warp) compute Q.K^T and P.V with bf16 mma.sync
 // (m16n8k16, f32 accumulation, fragments fetched with ldmatrix from the swizzled tiles), keep an online softmax
 // per row, reduce row maxima and sums with quad shuffles and merge through shared memory.
 //
@@ -87,7 +87,8 @@ __device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], 
                  : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
-constexpr int kConsumerWarps = 4;
+constexpr int kConsumerWarps = 8;   // two groups of four: group g takes pages g, g+2, ... so two pages are in the
+constexpr int kGroupWarps = 4;      // tensor-core pipeline at a time; a warp owns 16 tokens of its group's page
 constexpr int kFastThreads = (kConsumerWarps + 1) * 32;
 constexpr int kHalfTileBytes = 64 * 128;  // one TMA box: 64 tokens x 64 bf16
 
@@ -134,7 +135,7 @@ __global__ void __launch_bounds__(kFastThreads) attention_mma_kernel(const __gri
     if (threadIdx.x == 0) {
         for (int s = 0; s < S::stages; ++s) {
             mbar_init(&full[s], 1);
-            mbar_init(&empty[s], kConsumerWarps);
+            mbar_init(&empty[s], kGroupWarps);
         }
         mbar_fence_init();
     }
@@ -189,11 +190,12 @@ __global__ void __launch_bounds__(kFastThreads) attention_mma_kernel(const __gri
                 qa[kk][3] = v1 ? pack_bf16(q1[c + 8], q1[c + 9]) : 0u;
             }
         }
-        const int tok0 = warp * 16;
+        const int tok0 = (warp & (kGroupWarps - 1)) * 16;
+        const int group_index = warp / kGroupWarps;
         trace_mark(trace, 2);
         const int mi = lane >> 3, ri = lane & 7;
         bool alive = true;
-        for (int i = 0; i < pages && alive; ++i) {
+        for (int i = group_index; i < pages && alive; i += kConsumerWarps / kGroupWarps) {
             const int s = i % S::stages;
             const uint32_t phase = (i / S::stages) & 1;
             if (!mbar_wait(&full[s], phase)) {
@@ -201,7 +203,7 @@ __global__ void __launch_bounds__(kFastThreads) attention_mma_kernel(const __gri
                 alive = false;
                 break;
             }
-            if (i == 0) trace_mark(trace, 3);
+            if (i == group_index) trace_mark(trace, 3);
             const uint32_t kbase = smem_u32(smem + s * S::stage_bytes);
             const uint32_t vbase = kbase + S::tile_bytes;
 

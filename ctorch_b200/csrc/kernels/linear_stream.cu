@@ -451,19 +451,18 @@ int sm_count(int device) {
 bool choose_tiling(int in, int out, int sms, StreamParams& sp, size_t& smem) {
     sp.in_padded = (in + 63) & ~63;
     const size_t row_bytes = static_cast<size_t>(sp.in_padded + 8) * 2;
-    // Two CTAs per SM (this kernel's tail next to the early-started successor) when the activations leave room
-    // for at least two weight slots in half of the shared memory; else one CTA per SM.
-    const size_t half = 110 * 1024, whole = 220 * 1024;
-    const size_t budget = 2 * kRows * row_bytes + kConsumers * kRows * 8 * 4 + 1664 + 2 * 8 * row_bytes <= half ? half : whole;
     // Smallest tile with which one round of CTAs covers the matrix (every further tile of a CTA costs a reduction
-    // round); smaller tiles when the ring would not hold two of them.
+    // round).  Half of the shared memory is preferred (two CTAs per SM: this kernel's tail next to the early-started
+    // successor), the whole when a ring of two tiles does not fit in half, a smaller tile when it does not fit at all.
+    const size_t half = 110 * 1024, whole = 220 * 1024;
     int tf = 8;
     while (tf < 64 && (out + tf - 1) / tf > sms) tf <<= 1;
     size_t fixed = 0;
     int slots = 0;
     for (;; tf >>= 1) {
         fixed = 2 * kRows * row_bytes + static_cast<size_t>(kConsumers) * kRows * tf * 4 + 128 + 1536;
-        slots = fixed < budget ? static_cast<int>((budget - fixed) / (tf * row_bytes)) : 0;
+        slots = fixed < half ? static_cast<int>((half - fixed) / (tf * row_bytes)) : 0;
+        if (slots < 2) slots = fixed < whole ? static_cast<int>((whole - fixed) / (tf * row_bytes)) : 0;
         if (slots >= 2 || tf == 8) break;
     }
     if (slots < 2) return false;
