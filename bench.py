@@ -111,9 +111,12 @@ def distributed():
     import torch
     import torch.distributed as dist
     local = int(os.environ.get("LOCAL_RANK", "0"))
-    torch.cuda.set_device(local)
     os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-    dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    if torch.cuda.is_available():
+        torch.cuda.set_device(local)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    else:   # host-only processes (tests of the rank plumbing)
+        dist.init_process_group("gloo")
     return dist.get_rank(), world, local, dist
 
 
@@ -121,7 +124,8 @@ def max_over_ranks(value: float, dist, local: int) -> float:
     if dist is None:
         return value
     import torch
-    t = torch.tensor([value], dtype=torch.float64, device=torch.device("cuda", local))
+    device = torch.device("cuda", local) if torch.cuda.is_available() else torch.device("cpu")
+    t = torch.tensor([value], dtype=torch.float64, device=device)
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
     return float(t.item())
 
@@ -129,8 +133,11 @@ def max_over_ranks(value: float, dist, local: int) -> float:
 def barrier(dist, local: int):
     if dist is not None:
         import torch
-        dist.barrier(device_ids=[local])
-        torch.cuda.synchronize(local)
+        if torch.cuda.is_available():
+            dist.barrier(device_ids=[local])
+            torch.cuda.synchronize(local)
+        else:
+            dist.barrier()
 
 
 def run_reference(args, spec, weights) -> dict:
@@ -142,7 +149,8 @@ def run_reference(args, spec, weights) -> dict:
     return {"impl": "reference", "metric": METRIC, "value": result["value"], "unit": UNIT, "n_gpus": args.gpus,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": args.workload, "batch": spec["batch"], "note": "CPU decoder of the reference, f32 math on " + spec["dtype"] + " weights"},
+            "config": {"workload": args.workload, "batch_per_gpu": spec["batch"], "layers": spec["layers"], "d_model": spec["d_model"],
+                       "vocab": spec["vocab"], "note": "CPU decoder of the reference, f32 math on " + spec["dtype"] + " weights, rank 0 only"},
             "cpu_baseline": {k: result[k] for k in ("value", "unit", "cores", "kind", "sample")},
             "e2e": {"value": result["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
             "gpu_launches": 0}
