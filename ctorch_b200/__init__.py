@@ -132,7 +132,7 @@ def _declare(l: C.CDLL) -> None:
         "b200_attention_decode": (C.c_int, [vp, i64, i32, i32, vp, i32, i32, vp, sz, vp, vp]),
         "b200_attention_decode_static": (C.c_int, [vp, i64, i32, i32, vp, i32, i32, vp, vp]),
         "b200_linear_shadow": (C.c_int, [C.POINTER(ShadowLinearArgs), vp]),
-        "b200_linear_shadow_parts": (i32, [i64, i64]),
+        "b200_linear_shadow_parts": (i32, [i64, i64, i64]),
         "b200_embedding_shadow": (C.c_int, [vp, i32, vp, i64, i64, i64, vp, i32, vp, vp, vp, vp, vp]),
         "b200_shadow_from_rows": (C.c_int, [vp, i64, i64, vp, i32, vp, vp, vp, vp]),
         "b200_attention_decode_shadow": (C.c_int, [vp, i64, i32, i32, vp, i32, i32, vp, sz, vp, vp, vp]),

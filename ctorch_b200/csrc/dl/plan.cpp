@@ -203,16 +203,19 @@ void DecodePlan::refresh() {
     }
     synchronize(probe.device());
     packed_version_ = version;
-    // Shadow protocol: bf16 weights and every projection inside the streaming kernel's limits.
-    const Index D = owner_.dimensions(), F = owner_.hidden(), KV = owner_.kv_heads() * (D / owner_.heads());
-    parts_o_ = b200_linear_shadow_parts(D, D);
-    parts_down_ = b200_linear_shadow_parts(F, D);
-    shadow_ = owner_.dtype() == DType::bf16 && parts_o_ > 0 && parts_down_ > 0 && b200_linear_shadow_parts(D, D + 2 * KV) > 0
-        && b200_linear_shadow_parts(D, 2 * F) > 0;
+    // Shadow protocol: bf16 weights and bf16 norm weights; whether a given row count can use it is decided per pass.
+    shadow_ = owner_.dtype() == DType::bf16;
     for (Index i = 0; shadow_ && i < owner_.layer_count(); ++i) {
         auto& layer = owner_.layer(i);
         shadow_ = layer.attention_norm().weight()->dtype() == DType::bf16 && layer.feedforward_norm().weight()->dtype() == DType::bf16;
     }
+}
+
+bool DecodePlan::shadows_for(Index rows) const {
+    if (!shadow_ || rows <= 0) return false;
+    const Index D = owner_.dimensions(), F = owner_.hidden(), KV = owner_.kv_heads() * (D / owner_.heads());
+    return b200_linear_shadow_parts(rows, D, D + 2 * KV) > 0 && b200_linear_shadow_parts(rows, D, D) > 0
+        && b200_linear_shadow_parts(rows, D, 2 * F) > 0 && b200_linear_shadow_parts(rows, F, D) > 0;
 }
 
 void DecodePlan::reserve(Index rows, Index max_length, int device) {
@@ -231,7 +234,7 @@ void DecodePlan::reserve(Index rows, Index max_length, int device) {
             hs_hi_ = empty({rows, D}, half); hs_lo_ = empty({rows, D}, half);
             att_hi_ = empty({rows, D}, half); att_lo_ = empty({rows, D}, half);
             act_hi_ = empty({rows, F}, half); act_lo_ = empty({rows, F}, half);
-            const Index parts = std::max<Index>(1, std::max(parts_o_, parts_down_));
+            const Index parts = std::max<Index>(256, (D + 127) / 128);  // at most one partial per feature tile of either kernel
             sq_attn_ = empty({parts, rows}, f32); sq_ffn_ = empty({parts, rows}, f32);
         }
         reserved_rows_ = rows;
@@ -270,7 +273,7 @@ void shadow_linear(const b200_shadow_linear_args& args, void* stream, const char
 
 void DecodePlan::embed(const Embedding& tokens, const Index* ids, Index rows, float* x, void* stream) {
     const Tensor& table = tokens.weight();
-    if (!shadow_) {
+    if (!shadows_for(rows)) {
         runtime::check(b200_embedding(table.raw_data(), code_of(table.dtype()), ids, rows, table.size(0), table.size(1), x, stream), "embedding");
         probe(2);
         return;
@@ -285,7 +288,7 @@ void DecodePlan::embed(const Embedding& tokens, const Index* ids, Index rows, fl
 void DecodePlan::logits(const Linear& output, Index rows, float* out, void* stream) {
     const Tensor* norm = owner_.normalization().weight();
     const Index V = output.weight().size(0), D = owner_.dimensions();
-    if (shadow_ && output.weight().dtype() == DType::bf16 && b200_linear_shadow_parts(D, V) > 0) {
+    if (shadows_for(rows) && output.weight().dtype() == DType::bf16 && b200_linear_shadow_parts(rows, D, V) > 0) {
         b200_shadow_linear_args args{};
         args.x_hi = hs_hi_.raw_data(); args.x_lo = hs_lo_.raw_data(); args.rows = rows; args.in = D;
         args.weight = output.weight().raw_data(); args.out = V;
@@ -306,8 +309,9 @@ void DecodePlan::run_layers(const float* x, Index batch, Index length, std::span
     const int device = h_.device().index;
     const double eps = TransformerDecoderLayer::norm_epsilon;
     float* h = hidden();
-    if (shadow_) {
+    if (shadows_for(rows)) {
         const Index H = owner_.heads(), HK = owner_.kv_heads(), hd = D / H;
+        const int parts_o = b200_linear_shadow_parts(rows, D, D), parts_down = b200_linear_shadow_parts(rows, F, D);
         auto* sq_attn = static_cast<float*>(sq_attn_.mutable_data());
         auto* sq_ffn = static_cast<float*>(sq_ffn_.mutable_data());
         if (!shadow_ready) {
@@ -355,7 +359,7 @@ void DecodePlan::run_layers(const float* x, Index batch, Index length, std::span
             shadow_linear(out_proj, stream, "output projection");
             b200_shadow_linear_args gate_up{};
             gate_up.x_hi = hs_hi_.raw_data(); gate_up.x_lo = hs_lo_.raw_data(); gate_up.rows = rows; gate_up.in = D;
-            gate_up.weight = packed.wgu.raw_data(); gate_up.out = 2 * F; gate_up.sumsq_in = sq_ffn; gate_up.parts_in = parts_o_; gate_up.eps = eps;
+            gate_up.weight = packed.wgu.raw_data(); gate_up.out = 2 * F; gate_up.sumsq_in = sq_ffn; gate_up.parts_in = parts_o; gate_up.eps = eps;
             gate_up.epilogue = B200_EPI_SWIGLU; gate_up.out_hi = act_hi_.mutable_data(); gate_up.out_lo = act_lo_.mutable_data();
             shadow_linear(gate_up, stream, "gate/up projection");
             const Tensor* next_norm = i + 1 < owner_.layer_count() ? owner_.layer(i + 1).attention_norm().weight() : owner_.normalization().weight();
@@ -365,7 +369,7 @@ void DecodePlan::run_layers(const float* x, Index batch, Index length, std::span
             down.out_hi = hs_hi_.mutable_data(); down.out_lo = hs_lo_.mutable_data();
             down.out_norm_weight = next_norm->raw_data(); down.out_norm_dtype = code_of(next_norm->dtype()); down.sumsq_out = sq_attn;
             shadow_linear(down, stream, "down projection");
-            parts_attn = parts_down_;
+            parts_attn = parts_down;
         }
         last_parts_ = parts_attn;
         return;
@@ -506,7 +510,7 @@ void Generation::enqueue_step(void* stream, Index max_length) {
     auto& plan = decoder_->plan();
     const Index D = decoder_->dimensions();
     plan.embed(*tokens_, ids_.data<Index>(), batch_, static_cast<float*>(x_.mutable_data()), stream);
-    plan.run_layers(x_.data<float>(), batch_, 1, *cache_, max_length, stream, plan.uses_shadows());
+    plan.run_layers(x_.data<float>(), batch_, 1, *cache_, max_length, stream, plan.shadows_for(batch_));
     std::vector<b200_kv_cache*> handles;
     for (auto& layer : *cache_) handles.push_back(layer.handle());
     runtime::check(b200_kv_cache_advance(handles.data(), static_cast<int32_t>(handles.size()), 1, stream), "KV advance");

@@ -37,7 +37,9 @@ public:
     void embed(const Embedding& tokens, const Index* ids, Index rows, float* x, void* stream);
     // Logits of the last run_layers' rows (decode step: final norm folded into the projection).
     void logits(const Linear& output, Index rows, float* out, void* stream);
-    bool uses_shadows() const { return shadow_; }
+    // Whether a pass over `rows` activation rows runs on the shadow protocol (bf16 model and every projection inside
+    // the limits of the kernel that serves that row count).
+    bool shadows_for(Index rows) const;
     void reserve(Index rows, Index max_length, int device);
     float* hidden() const { return static_cast<float*>(h_.mutable_data()); }
     void refresh();  // re-pack weights when the owner's parameters moved
@@ -59,7 +61,7 @@ private:
     Tensor h_, q_, attended_, activated_, low_, scratch_;
     // shadow protocol (bf16 models whose widths fit the streaming kernel): activations travel as bf16 hi + lo planes
     bool shadow_ = false;
-    int parts_o_ = 0, parts_down_ = 0, last_parts_ = 0;
+    int last_parts_ = 0;
     Tensor hs_hi_, hs_lo_, att_hi_, att_lo_, act_hi_, act_lo_, sq_attn_, sq_ffn_;
 };
 

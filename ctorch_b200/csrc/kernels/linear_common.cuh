@@ -101,7 +101,12 @@ __device__ __forceinline__ void linear_epilogue(const LinearParams& p, int row, 
 // Tensor-core streaming kernel for bf16 weights (linear_stream.cu); returns B200_UNSUPPORTED when the shape is
 // outside what it handles, in which case the caller uses the CUDA-core kernel.
 int launch_linear_stream(const LinearParams& p, int epilogue, cudaStream_t stream);
-// Feature tiles the streaming kernel cuts a [out, in] weight into on the current device (0: unsupported shape).
-int linear_stream_parts(int in, int out);
+// Number of per-row sum-of-squares partials a residual-epilogue shadow call with these sizes writes (0: unsupported).
+int linear_stream_parts(int rows, int in, int out);
+// tcgen05 GEMM for many rows (linear_gemm.cu): shadow input only; B200_UNSUPPORTED otherwise.
+int launch_linear_gemm(const LinearParams& p, int epilogue, cudaStream_t stream);
+int linear_gemm_parts(int out);
+// Row count from which the dense tensor-core kernel replaces the streaming one.
+constexpr int kGemmRows = 17;
 
 }  // namespace b200

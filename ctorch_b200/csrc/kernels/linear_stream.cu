@@ -476,8 +476,9 @@ bool choose_tiling(int in, int out, int sms, StreamParams& sp, size_t& smem) {
 
 }  // namespace
 
-int linear_stream_parts(int in, int out) {
-    if (in > kMaxIn || (in & 7) || in <= 0 || out <= 0) return 0;
+int linear_stream_parts(int rows, int in, int out) {
+    if ((in & 7) || in <= 0 || out <= 0) return 0;
+    if (rows >= kGemmRows || in > kMaxIn) return linear_gemm_parts(out);
     int device = 0;
     if (cudaGetDevice(&device) != cudaSuccess) return 0;
     StreamParams sp{};
@@ -486,6 +487,7 @@ int linear_stream_parts(int in, int out) {
 }
 
 int launch_linear_stream(const LinearParams& p, int epilogue, cudaStream_t stream) {
+    if (p.x_hi && (p.rows >= kGemmRows || p.in > kMaxIn)) return launch_linear_gemm(p, epilogue, stream);
     if (p.weight_dtype != B200_BF16 || p.in > kMaxIn || (p.in & 7) || (reinterpret_cast<uintptr_t>(p.weight) & 15))
         return B200_UNSUPPORTED;
     if (p.x_hi ? ((reinterpret_cast<uintptr_t>(p.x_hi) | reinterpret_cast<uintptr_t>(p.x_lo)) & 15) || !p.x_lo

@@ -140,12 +140,13 @@ typedef struct b200_shadow_linear_args {
     void* out_lo;
     const void* out_norm_weight;   /* residual epilogue: weight [out] of the norm that follows, folded into the shadow */
     int32_t out_norm_dtype;
-    float* sumsq_out;              /* residual epilogue: [b200_linear_shadow_parts(in, out)][rows] */
+    float* sumsq_out;              /* residual epilogue: [b200_linear_shadow_parts(rows, in, out)][rows] */
 } b200_shadow_linear_args;
-/* B200_UNSUPPORTED when the shape is outside the streaming kernel (in > 2048 or in % 8 != 0). */
+/* Up to 16 rows with in <= 2048: streaming kernel (bulk-TMA weight ring, mma.sync).  More rows or a wider input:
+ * dense tcgen05 kernel (TMA operand tiles, accumulator in tensor memory).  B200_UNSUPPORTED when in % 8 != 0. */
 B200_API int b200_linear_shadow(const b200_shadow_linear_args* args, void* stream);
 /* Number of row-sum partials a residual-epilogue call with these sizes writes (its feature tiles), 0 if unsupported. */
-B200_API int32_t b200_linear_shadow_parts(int64_t in, int64_t out);
+B200_API int32_t b200_linear_shadow_parts(int64_t rows, int64_t in, int64_t out);
 /* b200_embedding that also writes the shadow of out * norm_weight and one partial sum of squares per row ([1][rows]). */
 B200_API int b200_embedding_shadow(const void* table, int32_t table_dtype, const int64_t* ids, int64_t rows, int64_t vocab,
                                    int64_t width, const void* norm_weight, int32_t norm_dtype, float* out, void* out_hi,

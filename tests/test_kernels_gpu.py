@@ -332,7 +332,7 @@ def test_shadow_protocol_norm_linear_residual(rows, inner, out):
     sync()
     assert rel(shadow_to_f32(hi, lo), x * W.bf16_to_f32(norm)) < 2e-5
     assert rel(sq.cpu().numpy()[0], (x.astype(np.float64) ** 2).sum(axis=1)) < 1e-5
-    parts = l.b200_linear_shadow_parts(inner, out)
+    parts = l.b200_linear_shadow_parts(rows, inner, out)
     assert parts > 0
     y = torch.zeros((rows, out), dtype=torch.float32, device="cuda")
     ohi = torch.zeros((rows, out), dtype=torch.bfloat16, device="cuda")
@@ -390,3 +390,52 @@ def test_shadow_protocol_swiglu_and_attention_output():
                                             slo.data_ptr(), stream()))
     sync()
     assert rel(shadow_to_f32(shi, slo), plain) < 2e-5
+
+
+@pytest.mark.parametrize("rows,inner,out,epilogue", [(40, 768, 1280, 0), (130, 2048, 768, 1), (300, 768, 4096, 2), (17, 4096, 200, 1),
+                                                     (128, 72, 136, 0)])
+def test_dense_tensor_core_linear(rows, inner, out, epilogue):
+    """More than 16 rows (or a wide input) take the tcgen05 kernel: shadow input, split norm, every epilogue family."""
+    l = B.lib()
+    rng = np.random.default_rng(rows + inner + out)
+    x = rng.standard_normal((rows, inner), dtype=np.float32) * 2
+    norm = W.bf16_bits((1 + 0.1 * rng.standard_normal(inner)).astype(np.float32))
+    w = W.bf16_bits(0.05 * rng.standard_normal((out, inner), dtype=np.float32))
+    xd, nd, wd = dev(x), bf16_dev(norm), bf16_dev(w)
+    hi = torch.zeros((rows, inner), dtype=torch.bfloat16, device="cuda")
+    lo = torch.zeros_like(hi)
+    sq = torch.zeros((1, rows), dtype=torch.float32, device="cuda")
+    torch.cuda.synchronize()
+    B.kcheck(l.b200_shadow_from_rows(xd.data_ptr(), rows, inner, nd.data_ptr(), B.BF16, hi.data_ptr(), lo.data_ptr(), sq.data_ptr(), stream()))
+    xn = oracle.rms_norm(x, W.bf16_to_f32(norm), 1e-5)
+    full = oracle.linear(xn, w)
+    parts = l.b200_linear_shadow_parts(rows, inner, out)
+    assert parts == (out + 127) // 128
+    cols = out // 2 if epilogue == 2 else out
+    y = torch.zeros((rows, cols), dtype=torch.float32, device="cuda")
+    ohi = torch.zeros((rows, cols), dtype=torch.bfloat16, device="cuda")
+    olo = torch.zeros_like(ohi)
+    osq = torch.zeros((parts, rows), dtype=torch.float32, device="cuda")
+    res = rng.standard_normal((rows, out), dtype=np.float32)
+    rd = dev(res)
+    torch.cuda.synchronize()
+    args = B.ShadowLinearArgs(hi.data_ptr(), lo.data_ptr(), rows, inner, wd.data_ptr(), out, sq.data_ptr(), 1, 1e-5, epilogue,
+                              rd.data_ptr() if epilogue == 1 else None, None, y.data_ptr(),
+                              ohi.data_ptr() if epilogue else None, olo.data_ptr() if epilogue else None, None, 0,
+                              osq.data_ptr() if epilogue == 1 else None)
+    B.kcheck(l.b200_linear_shadow(C.byref(args), stream()))
+    sync()
+    status = C.c_int32()
+    B.kcheck(l.b200_take_device_status(0, stream(), C.byref(status)))
+    assert status.value == 0
+    if epilogue == 0:
+        want = full
+    elif epilogue == 1:
+        want = res + full
+    else:
+        want = oracle.silu_mul(np.ascontiguousarray(full[:, 0::2]), np.ascontiguousarray(full[:, 1::2]))
+    assert rel(y.cpu().numpy(), want) < 3e-5
+    if epilogue:
+        assert rel(shadow_to_f32(ohi, olo), want) < 4e-5
+    if epilogue == 1:
+        assert rel(osq.cpu().numpy().sum(axis=0), (want.astype(np.float64) ** 2).sum(axis=1)) < 1e-4
