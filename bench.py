@@ -162,9 +162,14 @@ def run_b200(args, spec, weights) -> dict:
     batch, prompt_len = spec["batch"], spec["prompt"]
     total_steps = 2 * (args.warmup + args.steps) + 4
     spec = dict(spec, context=max(spec["context"], prompt_len + total_steps + 1))
-    model = B.DecoderModel(spec, weights, device=local)
+    # Configuration 5 on more than one GPU is ONE model sliced over the ranks (KV-head tensor parallel): every rank
+    # feeds the same sequences and the job's tokens are counted once.  Every other workload runs independent replicas.
+    sliced = args.workload == "c5" and world > 1
+    if sliced:
+        B.tensor_parallel_init(rank, world, local)
+    model = B.DecoderModel(spec, weights, lora=W.make_lora(spec), device=local, tensor_parallel=(rank, world) if sliced else None)
     gen = B.Generation(model, batch, total_steps + 1)
-    prompt = W.make_prompts(spec, seed=99 + rank)
+    prompt = W.make_prompts(spec, seed=99 if sliced else 99 + rank)
     sampler = ClockSampler(local)
     sampler.start()  # nvidia-smi needs about a second to start: it runs from the prefill to the end of the timed loops
     B.timer_start(local)
@@ -203,12 +208,16 @@ def run_b200(args, spec, weights) -> dict:
         profile = {k: min(profile[k], more[k]) for k in profile}
     launches = gen.launches_per_step()
 
-    tokens = world * batch * args.steps
+    tokens = (1 if sliced else world) * batch * args.steps
     value = tokens / (device_ms / 1000.0)
     mean_context = start_length + args.steps / 2.0
     kv_dtype = "bf16" if spec["dtype"] == "bf16" else "f32"
     linear_bytes = W.weight_bytes(spec)
     kv_bytes = W.kv_bytes_per_token(spec, kv_dtype) * mean_context * batch
+    if sliced:   # per GPU: the slice of the layer weights and of the KV heads, plus the replicated logits table
+        table = spec["vocab"] * spec["d_model"] * 2
+        linear_bytes = (linear_bytes - table) // world + table
+        kv_bytes /= world
     peak, peak_kind = measured_peaks()
     # Device time of the linear launches inside the timed graph replays: the timed step duration times the linear
     # kernels' share of device time in the per-launch event profile (the profile itself runs eagerly, without the
@@ -218,11 +227,11 @@ def run_b200(args, spec, weights) -> dict:
     achieved = linear_bytes / (linear_ms / 1000.0) / 1e9 if linear_ms > 0 else None
     line = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
-        "ms_per_step": device_ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "ms_per_step": device_ms / args.steps, "higher_is_better": True, "scaling": "strong" if sliced else "weak", "vs_baseline": None,
         "dtype": "bf16 weights and KV, f32 accumulate and activations" if spec["dtype"] == "bf16" else "f32",
         "data": "synthetic",
         "config": {"workload": args.workload, "batch_per_gpu": batch, "prompt": prompt_len, "mean_context": mean_context,
-                   "layers": spec["layers"], "d_model": spec["d_model"], "vocab": spec["vocab"], "parallelism": f"replicas x{world}",
+                   "layers": spec["layers"], "d_model": spec["d_model"], "vocab": spec["vocab"], "parallelism": f"tp{world} (heads, KV heads and SwiGLU features sliced; 2 all-reduces per layer)" if sliced else f"replicas x{world}",
                    "l2": "inputs larger than L2: %.0f MB of weights and KV are streamed per step" % ((linear_bytes + kv_bytes) / 1e6),
                    "step_bytes": linear_bytes + kv_bytes,
                    "step_gbs": (linear_bytes + kv_bytes) / (device_ms / args.steps / 1000.0) / 1e9,
@@ -240,7 +249,10 @@ def run_b200(args, spec, weights) -> dict:
                      "traffic": 1.04 * linear_bytes if spec["dtype"] == "bf16" else None,
                      "algorithmic_bytes": linear_bytes, "launch_ms": linear_ms, "eager_profile_ms": profile["linear_ms"]},
     }
-    if rank == 0 and world == 1 and not args.no_cpu:
+    if sliced:
+        del gen, model
+        B.tensor_parallel_finalize(local)
+    if rank == 0 and world == 1 and not args.no_cpu and args.workload != "c5":
         cpu = cpu_reference(spec, weights, args.cpu_steps, 1)
         line["cpu_baseline"] = {k: cpu[k] for k in ("value", "unit", "cores", "kind", "sample")}
     if dist is not None:
@@ -342,7 +354,7 @@ def main():
     parser.add_argument("--steps", type=int, default=64)
     parser.add_argument("--warmup", type=int, default=8)
     parser.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    parser.add_argument("--workload", default="c2", choices=["c1", "c2", "c3", "c4"])
+    parser.add_argument("--workload", default="c2", choices=["c1", "c2", "c3", "c4", "c5"])
     parser.add_argument("--cpu-steps", type=int, default=24, help="timed CPU-baseline steps of the default run")
     parser.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     parser.add_argument("--small", action="store_true", help="c3 only: batch 16, contexts up to 8192 (profiler captures)")

@@ -114,6 +114,8 @@ def _declare(l: C.CDLL) -> None:
         "dl_generation_launches_per_step": (i64, [vp]),
         "dl_decoder_generate": (C.c_int, [vp, vp, vp, vp, i64, vp, pp]),
         "dl_generation_profile_step": (C.c_int, [vp, C.POINTER(C.c_double)]),
+        "dl_b200_tp_unique_id": (C.c_int, [vp]), "dl_b200_tp_init": (C.c_int, [Device, i32, i32, vp]),
+        "dl_b200_tp_finalize": (C.c_int, [Device]), "dl_transformer_decoder_set_tensor_parallel": (C.c_int, [vp, i32, i32]),
         "dl_b200_timer_start": (C.c_int, [Device]), "dl_b200_timer_stop": (C.c_int, [Device, C.POINTER(C.c_double)]),
         "dl_b200_stream": (vp, [Device]),
         # kernel-level ABI
@@ -291,7 +293,7 @@ class DecoderModel:
     through the C ABI from the canonical ordered tensor list (see ctorch_b200.workloads.tensor_shapes)."""
 
     def __init__(self, spec: dict, tensors: list[np.ndarray], lora: list[np.ndarray] | None = None, device: int = 0,
-                 cache_dtype: str | None = None):
+                 cache_dtype: str | None = None, tensor_parallel: tuple[int, int] | None = None):
         l = lib()
         self.spec = spec
         self.dev = cuda(device)
@@ -346,6 +348,8 @@ class DecoderModel:
                     pair.append(adapter)
                 check(l.dl_transformer_decoder_set_adapters(self.decoder.h, i, pair[0].h, pair[1].h))
                 self._adapters.append(pair)
+        if tensor_parallel is not None:
+            check(l.dl_transformer_decoder_set_tensor_parallel(self.decoder.h, tensor_parallel[0], tensor_parallel[1]))
         self.cache = None
         self.new_cache()
 
@@ -460,3 +464,22 @@ def timer_stop(device: int = 0) -> float:
     ms = C.c_double()
     check(lib().dl_b200_timer_stop(cuda(device), C.byref(ms)))
     return ms.value
+
+
+def tensor_parallel_init(rank: int, world: int, device: int) -> None:
+    """Joins the tensor-parallel group of `world` ranks; the NCCL id travels over torch.distributed (any backend)."""
+    import torch
+    import torch.distributed as dist
+    ident = (C.c_char * 128)()
+    if rank == 0:
+        check(lib().dl_b200_tp_unique_id(ident))
+    payload = torch.tensor(list(ident.raw), dtype=torch.uint8)
+    if dist.get_backend() == "nccl":
+        payload = payload.cuda(device)
+    dist.broadcast(payload, src=0)
+    raw = bytes(payload.cpu().tolist())
+    check(lib().dl_b200_tp_init(cuda(device), rank, world, raw))
+
+
+def tensor_parallel_finalize(device: int) -> None:
+    check(lib().dl_b200_tp_finalize(cuda(device)))

@@ -353,6 +353,23 @@ dl_status dl_decoder_generate(dl_module* decoder, dl_module* embedding, dl_modul
     });
 }
 
+dl_status dl_b200_tp_unique_id(void* id128) {
+    return invoke([&] {
+        if (!id128) throw std::invalid_argument("id slot is NULL");
+        dl::runtime::tp_unique_id(id128);
+    });
+}
+dl_status dl_b200_tp_init(dl_device device, int32_t rank, int32_t world, const void* id128) {
+    return invoke([&] {
+        if (device.type != DL_CUDA) throw std::invalid_argument("tensor parallelism needs a CUDA device");
+        dl::runtime::tp_init(device.index, rank, world, id128);
+    });
+}
+dl_status dl_b200_tp_finalize(dl_device device) { return invoke([&] { dl::runtime::tp_finalize(device.index); }); }
+dl_status dl_transformer_decoder_set_tensor_parallel(dl_module* decoder, int32_t rank, int32_t world) {
+    return invoke([&] { as<dl::nn::TransformerDecoder>(decoder, "TransformerDecoder").set_tensor_parallel(rank, world); });
+}
+
 dl_status dl_b200_timer_start(dl_device device) {
     return invoke([&] {
         if (device.type != DL_CUDA || device.index < 0 || device.index >= 64) throw std::invalid_argument("timer needs a CUDA device");

@@ -342,12 +342,19 @@ public:
     TransformerDecoderLayer& layer(Index i) const { return *layers_[static_cast<std::size_t>(i)]; }
     const RMSNorm& normalization() const { return *normalization_; }
     void set_cache_dtype(DType dtype) { cache_dtype_ = dtype; }  // storage dtype of caches made by make_cache()
+    // KV-head tensor parallelism: this object computes the slice `rank` of `world` (query heads, KV heads and SwiGLU
+    // features are split evenly; norms, residual stream, embedding and logits stay replicated) and sums the partial
+    // results of the output and down projections over the device's tensor-parallel group.
+    void set_tensor_parallel(int rank, int world);
+    int tp_rank() const { return tp_rank_; }
+    int tp_world() const { return tp_world_; }
     DType cache_dtype() const { return cache_dtype_; }
     DecodePlan& plan();
 
 private:
     Index dimensions_, heads_, kv_heads_, hidden_, context_;
     DType dtype_, cache_dtype_;
+    int tp_rank_ = 0, tp_world_ = 1;
     std::vector<std::shared_ptr<TransformerDecoderLayer>> layers_;
     std::shared_ptr<RMSNorm> normalization_;
     std::unique_ptr<DecodePlan> plan_;

@@ -13,6 +13,13 @@ void check(int status, const char* what);       // throws std::runtime_error wit
 void check_cuda(int error, const char* what);   // throws "CUDA: ..." for a non-zero cudaError_t
 void set_device(int device);
 void copy_bytes(void* dst, Device dst_device, const void* src, Device src_device, std::size_t bytes);
+// KV-head tensor parallelism: one NCCL communicator per device (runtime/collective.cpp).
+void tp_unique_id(void* out128);
+void tp_init(int device, int rank, int world, const void* id128);
+void tp_finalize(int device);
+int tp_world(int device);
+int tp_rank(int device);
+void tp_all_reduce(int device, float* data, std::size_t count);
 }  // namespace runtime
 
 namespace internal {

@@ -363,6 +363,16 @@ TransformerDecoder::TransformerDecoder(Index layers, Index dimensions, Index hea
 }
 TransformerDecoder::~TransformerDecoder() = default;
 
+void TransformerDecoder::set_tensor_parallel(int rank, int world) {
+    if (world < 1 || rank < 0 || rank >= world) throw std::invalid_argument("tensor-parallel rank must lie in [0, world)");
+    const Index hd = dimensions_ / heads_;
+    if (heads_ % world || kv_heads_ % world || hidden_ % world || ((hidden_ / world) % 8) || ((heads_ / world * hd) % 8))
+        throw std::invalid_argument("query heads, KV heads and SwiGLU features must split evenly (in multiples of 8 features) over the ranks");
+    tp_rank_ = rank;
+    tp_world_ = world;
+    to(normalization_->weight()->device());  // bumps the version: plans re-pack their slices
+}
+
 Tensor TransformerDecoder::forward(const Tensor& input) {
     // A full causal pass equals decoding the whole sequence into an empty cache (the property the reference's
     // tests/state.cpp:54-63 pins); the cache is dropped afterwards.

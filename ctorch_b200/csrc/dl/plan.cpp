@@ -95,17 +95,21 @@ struct AttentionWeights {
     float scale = 0.0f;
 };
 
-AttentionWeights pack_attention(const GroupedQueryAttention& a) {
+AttentionWeights pack_attention(const GroupedQueryAttention& a, int rank = 0, int world = 1) {
     AttentionWeights w;
     const auto* qa = a.query_adapter();
     const auto* va = a.value_adapter();
-    const Tensor parts[3] = {qa ? qa->weight() : a.query().weight(), a.key().weight(), va ? va->weight() : a.value().weight()};
+    // rows of this rank's query heads and KV heads (all rows when world == 1)
+    const Index q_rows = a.dimensions() / world, kv_rows = a.kv_heads() * (a.dimensions() / a.heads()) / world;
+    const Tensor parts[3] = {(qa ? qa->weight() : a.query().weight()).narrow(0, rank * q_rows, q_rows),
+                             a.key().weight().narrow(0, rank * kv_rows, kv_rows),
+                             (va ? va->weight() : a.value().weight()).narrow(0, rank * kv_rows, kv_rows)};
     w.wqkv = concat_rows(parts);
     if (qa) {
         const Tensor downs[2] = {qa->down().weight(), va->down().weight()};
         w.lora_down = concat_rows(downs);
-        w.q_up = qa->up().weight().raw_data();
-        w.v_up = va->up().weight().raw_data();
+        w.q_up = qa->up().weight().narrow(0, rank * q_rows, q_rows).raw_data();
+        w.v_up = va->up().weight().narrow(0, rank * kv_rows, kv_rows).raw_data();
         w.rank = static_cast<int>(qa->rank());
         w.scale = static_cast<float>(qa->scale());
         if (static_cast<float>(va->scale()) != w.scale) throw std::invalid_argument("query and value adapters must share alpha/rank");
@@ -190,13 +194,22 @@ void DecodePlan::refresh() {
     layers_.clear();
     for (Index i = 0; i < owner_.layer_count(); ++i) {
         auto& layer = owner_.layer(i);
-        const AttentionWeights a = pack_attention(layer.attention());
+        const int rank = owner_.tp_rank(), world = owner_.tp_world();
+        const AttentionWeights a = pack_attention(layer.attention(), rank, world);
         Layer packed{};
         packed.wqkv = a.wqkv; packed.lora_down = a.lora_down; packed.q_up = a.q_up; packed.v_up = a.v_up;
         packed.rank = a.rank; packed.scale = a.scale;
-        packed.wgu = interleave_rows(layer.feedforward().gate().weight(), layer.feedforward().up().weight());
+        const Index f_rows = owner_.hidden() / world, d_cols = owner_.dimensions() / world;
+        packed.wgu = interleave_rows(layer.feedforward().gate().weight().narrow(0, rank * f_rows, f_rows),
+                                     layer.feedforward().up().weight().narrow(0, rank * f_rows, f_rows));
         packed.wo = layer.attention().output().weight().raw_data();
         packed.wd = layer.feedforward().down().weight().raw_data();
+        if (world > 1) {  // column cuts: this rank's input features of the two row-parallel projections
+            packed.wo_slice = layer.attention().output().weight().narrow(1, rank * d_cols, d_cols);
+            packed.wd_slice = layer.feedforward().down().weight().narrow(1, rank * f_rows, f_rows);
+            packed.wo = packed.wo_slice.raw_data();
+            packed.wd = packed.wd_slice.raw_data();
+        }
         packed.norm1 = layer.attention_norm().weight()->raw_data();
         packed.norm2 = layer.feedforward_norm().weight()->raw_data();
         layers_.push_back(std::move(packed));
@@ -213,8 +226,9 @@ void DecodePlan::refresh() {
 
 bool DecodePlan::shadows_for(Index rows) const {
     if (!shadow_ || rows <= 0) return false;
-    const Index D = owner_.dimensions(), F = owner_.hidden(), KV = owner_.kv_heads() * (D / owner_.heads());
-    return b200_linear_shadow_parts(rows, D, D + 2 * KV) > 0 && b200_linear_shadow_parts(rows, D, D) > 0
+    const Index world = owner_.tp_world();
+    const Index D = owner_.dimensions(), F = owner_.hidden() / world, KV = owner_.kv_heads() * (D / owner_.heads()) / world;
+    return b200_linear_shadow_parts(rows, D, D / world + 2 * KV) > 0 && b200_linear_shadow_parts(rows, D / world, D) > 0
         && b200_linear_shadow_parts(rows, D, 2 * F) > 0 && b200_linear_shadow_parts(rows, F, D) > 0;
 }
 
@@ -261,7 +275,7 @@ void DecodePlan::validate(Index batch, Index length, std::span<KVCache> cache, i
             throw std::invalid_argument("KV cache append exceeds capacity or has unequal key/value lengths");
     if (length > owner_.context() - prefix) throw std::out_of_range("RoPE positions exceed the table capacity");
     const Index hd = owner_.dimensions() / owner_.heads();
-    for (auto& layer : cache) layer.ensure(device, batch, owner_.kv_heads(), hd);
+    for (auto& layer : cache) layer.ensure(device, batch, owner_.kv_heads() / owner_.tp_world(), hd);
 }
 
 namespace {
@@ -309,11 +323,27 @@ void DecodePlan::run_layers(const float* x, Index batch, Index length, std::span
     const int device = h_.device().index;
     const double eps = TransformerDecoderLayer::norm_epsilon;
     float* h = hidden();
+    if (owner_.tp_world() > 1 && !shadows_for(rows))
+        throw std::invalid_argument("tensor parallelism needs a bf16 decoder whose slices fit the shadow kernels");
     if (shadows_for(rows)) {
-        const Index H = owner_.heads(), HK = owner_.kv_heads(), hd = D / H;
-        const int parts_o = b200_linear_shadow_parts(rows, D, D), parts_down = b200_linear_shadow_parts(rows, F, D);
+        // Tensor parallel (world > 1): this rank owns H/world query heads, HK/world KV heads and F/world SwiGLU features;
+        // the output and down projections produce partial sums over their input slices, rank 0 adds the residual, an
+        // all-reduce makes every rank's residual stream identical, and the next shadow is rebuilt from it.
+        const int world = owner_.tp_world(), rank = owner_.tp_rank();
+        const bool parallel = world > 1;
+        const Index hd = D / owner_.heads();
+        const Index H = owner_.heads() / world, HK = owner_.kv_heads() / world, Dl = H * hd, Fl = F / world;
+        const int parts_o = parallel ? 1 : b200_linear_shadow_parts(rows, D, D);
+        const int parts_down = parallel ? 1 : b200_linear_shadow_parts(rows, F, D);
         auto* sq_attn = static_cast<float*>(sq_attn_.mutable_data());
         auto* sq_ffn = static_cast<float*>(sq_ffn_.mutable_data());
+        auto rebuild_shadow = [&](const Tensor* norm, float* sums) {
+            runtime::tp_all_reduce(device, h, static_cast<std::size_t>(rows * D));
+            probe(2);
+            runtime::check(b200_shadow_from_rows(h, rows, D, norm->raw_data(), code_of(norm->dtype()), hs_hi_.mutable_data(),
+                                                 hs_lo_.mutable_data(), sums, stream), "shadow after all-reduce");
+            probe(2);
+        };
         if (!shadow_ready) {
             const Tensor* norm = owner_.layer(0).attention_norm().weight();
             runtime::check(b200_shadow_from_rows(x, rows, D, norm->raw_data(), code_of(norm->dtype()), hs_hi_.mutable_data(),
@@ -344,31 +374,40 @@ void DecodePlan::run_layers(const float* x, Index batch, Index length, std::span
                 qkv.lora_rank = packed.rank; qkv.lora_scale = packed.scale; qkv.low = low.y; qkv.q_up = packed.q_up; qkv.v_up = packed.v_up;
             }
             b200_shadow_linear_args project = base;
-            project.weight = packed.wqkv.raw_data(); project.out = D + 2 * HK * hd; project.epilogue = B200_EPI_QKV; project.qkv = &qkv;
+            project.weight = packed.wqkv.raw_data(); project.out = Dl + 2 * HK * hd; project.epilogue = B200_EPI_QKV; project.qkv = &qkv;
             shadow_linear(project, stream, "q/k/v projection");
             runtime::check(b200_attention_decode_shadow(qkv.q_out, rows, static_cast<int32_t>(length), static_cast<int32_t>(H), kv,
                                                         static_cast<int32_t>(max_length), 1, scratch_.mutable_data(), scratch_bytes_,
                                                         att_hi_.mutable_data(), att_lo_.mutable_data(), stream), "attention");
             probe(1);
             const Tensor* ffn_norm = layer.feedforward_norm().weight();
+            const bool adds_residual = !parallel || rank == 0;
             b200_shadow_linear_args out_proj{};
-            out_proj.x_hi = att_hi_.raw_data(); out_proj.x_lo = att_lo_.raw_data(); out_proj.rows = rows; out_proj.in = D;
-            out_proj.weight = packed.wo; out_proj.out = D; out_proj.epilogue = B200_EPI_RESIDUAL; out_proj.residual = in; out_proj.y = h;
-            out_proj.out_hi = hs_hi_.mutable_data(); out_proj.out_lo = hs_lo_.mutable_data();
-            out_proj.out_norm_weight = ffn_norm->raw_data(); out_proj.out_norm_dtype = code_of(ffn_norm->dtype()); out_proj.sumsq_out = sq_ffn;
+            out_proj.x_hi = att_hi_.raw_data(); out_proj.x_lo = att_lo_.raw_data(); out_proj.rows = rows; out_proj.in = Dl;
+            out_proj.weight = packed.wo; out_proj.out = D; out_proj.y = h;
+            out_proj.epilogue = adds_residual ? B200_EPI_RESIDUAL : B200_EPI_STORE; out_proj.residual = adds_residual ? in : nullptr;
+            if (!parallel) {
+                out_proj.out_hi = hs_hi_.mutable_data(); out_proj.out_lo = hs_lo_.mutable_data();
+                out_proj.out_norm_weight = ffn_norm->raw_data(); out_proj.out_norm_dtype = code_of(ffn_norm->dtype()); out_proj.sumsq_out = sq_ffn;
+            }
             shadow_linear(out_proj, stream, "output projection");
+            if (parallel) rebuild_shadow(ffn_norm, sq_ffn);
             b200_shadow_linear_args gate_up{};
             gate_up.x_hi = hs_hi_.raw_data(); gate_up.x_lo = hs_lo_.raw_data(); gate_up.rows = rows; gate_up.in = D;
-            gate_up.weight = packed.wgu.raw_data(); gate_up.out = 2 * F; gate_up.sumsq_in = sq_ffn; gate_up.parts_in = parts_o; gate_up.eps = eps;
+            gate_up.weight = packed.wgu.raw_data(); gate_up.out = 2 * Fl; gate_up.sumsq_in = sq_ffn; gate_up.parts_in = parts_o; gate_up.eps = eps;
             gate_up.epilogue = B200_EPI_SWIGLU; gate_up.out_hi = act_hi_.mutable_data(); gate_up.out_lo = act_lo_.mutable_data();
             shadow_linear(gate_up, stream, "gate/up projection");
             const Tensor* next_norm = i + 1 < owner_.layer_count() ? owner_.layer(i + 1).attention_norm().weight() : owner_.normalization().weight();
             b200_shadow_linear_args down{};
-            down.x_hi = act_hi_.raw_data(); down.x_lo = act_lo_.raw_data(); down.rows = rows; down.in = F;
-            down.weight = packed.wd; down.out = D; down.epilogue = B200_EPI_RESIDUAL; down.residual = h; down.y = h;
-            down.out_hi = hs_hi_.mutable_data(); down.out_lo = hs_lo_.mutable_data();
-            down.out_norm_weight = next_norm->raw_data(); down.out_norm_dtype = code_of(next_norm->dtype()); down.sumsq_out = sq_attn;
+            down.x_hi = act_hi_.raw_data(); down.x_lo = act_lo_.raw_data(); down.rows = rows; down.in = Fl;
+            down.weight = packed.wd; down.out = D; down.y = h;
+            down.epilogue = adds_residual ? B200_EPI_RESIDUAL : B200_EPI_STORE; down.residual = adds_residual ? h : nullptr;
+            if (!parallel) {
+                down.out_hi = hs_hi_.mutable_data(); down.out_lo = hs_lo_.mutable_data();
+                down.out_norm_weight = next_norm->raw_data(); down.out_norm_dtype = code_of(next_norm->dtype()); down.sumsq_out = sq_attn;
+            }
             shadow_linear(down, stream, "down projection");
+            if (parallel) rebuild_shadow(next_norm, sq_attn);
             parts_attn = parts_down;
         }
         last_parts_ = parts_attn;

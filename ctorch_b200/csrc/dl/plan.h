@@ -47,7 +47,7 @@ public:
 
 private:
     struct Layer {
-        Tensor wqkv, wgu, lora_down;
+        Tensor wqkv, wgu, lora_down, wo_slice, wd_slice;  // slices: tensor-parallel column cuts of o-proj / down
         const void *wo, *wd, *norm1, *norm2, *q_up, *v_up;
         int rank;
         float scale;

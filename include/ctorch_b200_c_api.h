@@ -178,6 +178,17 @@ DL_API dl_status dl_generation_profile_step(dl_generation* generation, double mi
 DL_API dl_status dl_decoder_generate(dl_module* decoder, dl_module* embedding, dl_module* output,
     const dl_tensor* prompt, int64_t steps, dl_decoder_cache* cache, dl_tensor** tokens);
 
+/* KV-head tensor parallelism (one process per GPU).  A group is one NCCL communicator per device: one rank asks for
+ * a 128-byte id, every rank receives it by whatever transport the application has and joins.  A decoder then computes
+ * slice `rank` of `world`: query heads, KV heads and SwiGLU features are split evenly; norms, the residual stream, the
+ * embedding and the logits stay replicated; the partial results of the output projection and of the FFN
+ * down-projection are summed over the group (all-reduce on the library's stream) before the next norm.  Caches created
+ * for such a decoder hold the rank's KV heads only.  bf16 decoders only. */
+DL_API dl_status dl_b200_tp_unique_id(void* id128);
+DL_API dl_status dl_b200_tp_init(dl_device device, int32_t rank, int32_t world, const void* id128);
+DL_API dl_status dl_b200_tp_finalize(dl_device device);
+DL_API dl_status dl_transformer_decoder_set_tensor_parallel(dl_module* decoder, int32_t rank, int32_t world);
+
 /* CUDA-event timing on the library's compute stream of a device (benchmarks must time on the launching
  * stream).  dl_b200_timer_stop waits for the work and returns milliseconds since dl_b200_timer_start. */
 DL_API dl_status dl_b200_timer_start(dl_device device);

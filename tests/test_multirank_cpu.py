@@ -17,6 +17,19 @@ def run_ranks(script_args, port):
     return subprocess.run(cmd, cwd=ROOT, env=env, capture_output=True, text=True, timeout=600)
 
 
+def json_objects(text):
+    """Every top-level JSON object in `text`; two ranks may write to the shared pipe without a newline between them."""
+    decoder, found, at = json.JSONDecoder(), [], text.find("{")
+    while at >= 0:
+        try:
+            value, end = decoder.raw_decode(text, at)
+            found.append(value)
+            at = text.find("{", end)
+        except json.JSONDecodeError:
+            at = text.find("{", at + 1)
+    return found
+
+
 def test_rank_helpers_under_gloo(tmp_path):
     script = tmp_path / "ranks.py"
     script.write_text(textwrap.dedent("""
@@ -35,7 +48,7 @@ def test_rank_helpers_under_gloo(tmp_path):
     """ % ROOT))
     result = run_ranks([str(script)], 29641)
     assert result.returncode == 0, result.stderr[-2000:]
-    lines = [json.loads(l) for l in result.stdout.splitlines() if l.startswith("{")]
+    lines = json_objects(result.stdout)
     assert sorted(l["rank"] for l in lines) == [0, 1]
     assert all(l["slowest"] == 11.0 for l in lines)          # MAX over ranks
     assert lines[0]["sum"] != lines[1]["sum"]                  # independent sequences per rank
@@ -44,7 +57,7 @@ def test_rank_helpers_under_gloo(tmp_path):
 def test_reference_arm_prints_on_rank0_only():
     result = run_ranks(["bench.py", "--impl", "reference", "--workload", "c1", "--gpus", "2", "--steps", "3", "--warmup", "3"], 29642)
     assert result.returncode == 0, result.stderr[-2000:]
-    lines = [json.loads(l) for l in result.stdout.splitlines() if l.startswith("{")]
+    lines = json_objects(result.stdout)
     assert len(lines) == 1
     line = lines[0]
     assert line["impl"] == "reference" and line["n_gpus"] == 2 and line["value"] > 0
