@@ -45,13 +45,16 @@ SplitPlan plan_splits(int64_t rows, int kv_heads, int max_length, int page_size)
     s.pages_total = (max_length + page_size - 1) / page_size;
     if (s.pages_total < 1) s.pages_total = 1;
     const int64_t items = rows * kv_heads;
-    int64_t pps = (items * s.pages_total + 2399) / 2400;
-    if (pps < 1) pps = 1;
-    if (pps > 16) {
-        const int64_t splits16 = (s.pages_total + 15) / 16;
-        pps = items * splits16 <= 32768 ? 16 : s.pages_total;
-    }
-    if (s.pages_total <= 16) pps = s.pages_total;  // short contexts: one CTA per (row, KV head), no merge kernel
+    // Enough CTAs to fill the SMs about three times (the scheduler evens out unequal items), but 8 to 16 pages
+    // (128 to 512 KB of K and V) per CTA: a shorter stream is mostly pipeline ramp.
+    const int64_t fill = 444;
+    const int64_t want_splits = (fill + items - 1) / items;
+    int64_t pps = s.pages_total / want_splits;
+    if (pps < 8) pps = 8;
+    if (pps > 16) pps = 16;
+    if (items * ((s.pages_total + pps - 1) / pps) > 32768) pps = s.pages_total;
+    // short contexts: one CTA per (row, KV head), no merge kernel
+    if (s.pages_total <= 16 || (s.pages_total <= 32 && items >= fill)) pps = s.pages_total;
     if (pps > s.pages_total) pps = s.pages_total;
     s.pages_per_split = static_cast<int>(pps);
     s.num_splits = (s.pages_total + s.pages_per_split - 1) / s.pages_per_split;
@@ -92,11 +95,11 @@ constexpr int kGroupWarps = 4;      // tensor-core pipeline at a time; a warp ow
 constexpr int kFastThreads = (kConsumerWarps + 1) * 32;
 constexpr int kHalfTileBytes = 64 * 128;  // one TMA box: 64 tokens x 64 bf16
 
-template <int HD> struct FastShape {
+template <int HD, int STAGES> struct FastShape {
     static constexpr int halves = HD / 64;
     static constexpr int tile_bytes = halves * kHalfTileBytes;  // K or V page
     static constexpr int stage_bytes = 2 * tile_bytes;
-    static constexpr int stages = HD == 128 ? 6 : 8;  // 192 KB / 128 KB of K and V in flight per CTA
+    static constexpr int stages = STAGES;  // 6 x 32 KB (head_dim 128) or 8 / 6 x 16 KB (head_dim 64) of K and V in flight per CTA
     static constexpr int smem_bytes = stages * stage_bytes + 1024 + 2 * stages * 8;
 };
 
@@ -105,11 +108,18 @@ __device__ __forceinline__ uint32_t tile_offset(int token, int chunk) {
     return static_cast<uint32_t>((chunk >> 3) * kHalfTileBytes + token * 128 + (((chunk & 7) ^ (token & 7)) << 4));
 }
 
-template <int HD>
+// Pages per split for a sequence of `pages` cached pages: the splits the sequence needs at the planned size share its
+// pages evenly (17 pages planned as 16 + 1 become 9 + 8).
+__device__ __forceinline__ int balanced_pages_per_split(int pages, int planned) {
+    const int needed = (pages + planned - 1) / planned;
+    return needed > 0 ? (pages + needed - 1) / needed : planned;
+}
+
+template <int HD, int STAGES>
 __global__ void __launch_bounds__(kFastThreads) attention_mma_kernel(const __grid_constant__ CUtensorMap kmap,
                                                                      const __grid_constant__ CUtensorMap vmap,
                                                                      const AttnParams p) {
-    using S = FastShape<HD>;
+    using S = FastShape<HD, STAGES>;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
     uint64_t* full = reinterpret_cast<uint64_t*>(smem + S::stages * S::stage_bytes);
@@ -124,9 +134,10 @@ __global__ void __launch_bounds__(kFastThreads) attention_mma_kernel(const __gri
     const int row = item / p.kv.kv_heads, kvh = item % p.kv.kv_heads;
     const int sequence = row / p.tokens_per_sequence;
     const int kv_len = p.kv.lengths[sequence] + (p.causal ? row % p.tokens_per_sequence + 1 : 0);
-    const int page_begin = split * p.pages_per_split;
     int page_end = (kv_len + kFastPageSize - 1) / kFastPageSize;
-    if (page_end > page_begin + p.pages_per_split) page_end = page_begin + p.pages_per_split;
+    const int per_split = balanced_pages_per_split(page_end, p.pages_per_split);
+    const int page_begin = split * per_split;
+    if (page_end > page_begin + per_split) page_end = page_begin + per_split;
     if (page_begin >= page_end) { trace_end(trace); return; }  // uniform for the CTA
     const int pages = page_end - page_begin;
     const int group = p.heads / p.kv.kv_heads;
@@ -342,8 +353,9 @@ __global__ void __launch_bounds__(kGenericThreads) attention_generic_kernel(cons
     const int kvh = head / (p.heads / p.kv.kv_heads);
     const int sequence = row / p.tokens_per_sequence;
     const int kv_len = p.kv.lengths[sequence] + (p.causal ? row % p.tokens_per_sequence + 1 : 0);
-    const int begin = split * p.pages_per_split * p.kv.page_size;
-    int end = begin + p.pages_per_split * p.kv.page_size;
+    const int per_split = balanced_pages_per_split((kv_len + p.kv.page_size - 1) / p.kv.page_size, p.pages_per_split);
+    const int begin = split * per_split * p.kv.page_size;
+    int end = begin + per_split * p.kv.page_size;
     if (end > kv_len) end = kv_len;
     if (begin >= end) return;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -415,7 +427,8 @@ __global__ void attention_combine_kernel(const AttnParams p) {
     const int sequence = row / p.tokens_per_sequence;
     const int kv_len = p.kv.lengths[sequence] + (p.causal ? row % p.tokens_per_sequence + 1 : 0);
     const int pages = (kv_len + p.kv.page_size - 1) / p.kv.page_size;
-    int valid = (pages + p.pages_per_split - 1) / p.pages_per_split;
+    const int per_split = balanced_pages_per_split(pages, p.pages_per_split);
+    int valid = (pages + per_split - 1) / per_split;   // splits whose CTA had pages and wrote a partial
     if (valid > p.num_splits) valid = p.num_splits;
     const float* ml = p.part_ml + head_item * p.num_splits * 2;
     float m = -INFINITY;
@@ -430,9 +443,9 @@ __global__ void attention_combine_kernel(const AttnParams p) {
     trace_end(trace);
 }
 
-template <int HD> int launch_fast(const b200_kv_cache* cache, const AttnParams& p, cudaStream_t stream) {
-    using S = FastShape<HD>;
-    auto kernel = attention_mma_kernel<HD>;
+template <int HD, int STAGES> int launch_fast(const b200_kv_cache* cache, const AttnParams& p, cudaStream_t stream) {
+    using S = FastShape<HD, STAGES>;
+    auto kernel = attention_mma_kernel<HD, STAGES>;
     B200_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, S::smem_bytes));
     const dim3 grid(static_cast<unsigned>(p.rows) * p.kv.kv_heads, p.num_splits);
     return cuda_status(launch_dependent(kernel, grid, dim3(kFastThreads), S::smem_bytes, stream, *kv_tensor_map(cache, 0),
@@ -482,7 +495,14 @@ int attention_launch(const float* q, int64_t rows, int32_t tokens_per_sequence, 
     const int group = heads / cache->kv_heads;
     int status;
     if (kv_tensor_map(cache, 0) && group <= 16 && (cache->head_dim == 64 || cache->head_dim == 128)) {
-        status = cache->head_dim == 128 ? launch_fast<128>(cache, p, s) : launch_fast<64>(cache, p, s);
+        // head_dim 64 with more CTAs than SMs: a 96 KB ring lets two CTAs share an SM, so one CTA's pipeline ramp and
+        // drain overlap the other's streaming; with fewer CTAs each keeps the deeper ring to itself.
+        int device = 0;
+        B200_CUDA(cudaGetDevice(&device));
+        const int64_t ctas = static_cast<int64_t>(p.rows) * p.kv.kv_heads * p.num_splits;
+        if (cache->head_dim == 128) status = launch_fast<128, 6>(cache, p, s);
+        else if (ctas > sm_count(device)) status = launch_fast<64, 6>(cache, p, s);
+        else status = launch_fast<64, 8>(cache, p, s);
     } else {
         const dim3 grid(static_cast<unsigned>(rows) * heads, plan.num_splits);
         status = cuda_status(launch_dependent(attention_generic_kernel, grid, dim3(kGenericThreads), sizeof(float) * 4 * cache->head_dim, s, p),

@@ -1,6 +1,7 @@
 // Shared device/host helpers of the sm_100a decoder kernels.
 #pragma once
 
+#include <mutex>
 #include "ctorch_b200_kernels.h"
 
 #include <cuda.h>
@@ -151,6 +152,54 @@ cudaError_t launch_dependent(void (*kernel)(Params...), dim3 grid, dim3 block, s
     config.attrs = &attribute;
     config.numAttrs = 1;
     return cudaLaunchKernelEx(&config, kernel, static_cast<Params>(args)...);
+}
+
+// Same, for a grid made of thread-block clusters of `cluster` CTAs (distributed shared memory between them).
+template <class... Params, class... Args>
+cudaError_t launch_dependent_cluster(void (*kernel)(Params...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, dim3 cluster,
+                                     Args&&... args) {
+    cudaLaunchConfig_t config{};
+    config.gridDim = grid;
+    config.blockDim = block;
+    config.dynamicSmemBytes = smem;
+    config.stream = stream;
+    cudaLaunchAttribute attributes[2]{};
+    attributes[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attributes[0].val.programmaticStreamSerializationAllowed = 1;
+    attributes[1].id = cudaLaunchAttributeClusterDimension;
+    attributes[1].val.clusterDim.x = cluster.x;
+    attributes[1].val.clusterDim.y = cluster.y;
+    attributes[1].val.clusterDim.z = cluster.z;
+    config.attrs = attributes;
+    config.numAttrs = 2;
+    return cudaLaunchKernelEx(&config, kernel, static_cast<Params>(args)...);
+}
+
+// ---- thread-block clusters: hardware barrier over all threads of the cluster, and loads from a peer CTA's shared memory ----
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ uint32_t cluster_cta_rank() {
+    uint32_t rank;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
+    return rank;
+}
+__device__ __forceinline__ float load_peer_shared(uint32_t local_address, uint32_t peer_rank) {
+    uint32_t remote;
+    float value;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_address), "r"(peer_rank));
+    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(value) : "r"(remote) : "memory");
+    return value;
+}
+
+// Number of SMs of a device (cached; 148 when the device cannot be queried).
+inline int sm_count(int device) {
+    static std::mutex mutex;
+    static int counts[64];
+    std::lock_guard<std::mutex> lock(mutex);
+    if (device < 0 || device >= 64) return 148;
+    if (!counts[device] && cudaDeviceGetAttribute(&counts[device], cudaDevAttrMultiProcessorCount, device) != cudaSuccess) counts[device] = 148;
+    return counts[device];
 }
 
 // Host: cuTensorMapEncodeTiled resolved through the runtime so that the library has no link-time dependency on

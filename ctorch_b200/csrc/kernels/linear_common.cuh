@@ -2,6 +2,7 @@
 #pragma once
 
 #include "common.cuh"
+
 #include "kv_cache.cuh"
 
 namespace b200 {
@@ -105,7 +106,7 @@ int launch_linear_stream(const LinearParams& p, int epilogue, cudaStream_t strea
 int linear_stream_parts(int rows, int in, int out);
 // tcgen05 GEMM for many rows (linear_gemm.cu): shadow input only; B200_UNSUPPORTED otherwise.
 int launch_linear_gemm(const LinearParams& p, int epilogue, cudaStream_t stream);
-int linear_gemm_parts(int out);
+int linear_gemm_parts(int rows, int in, int out);
 // Row count from which the dense tensor-core kernel replaces the streaming one.
 constexpr int kGemmRows = 17;
 

@@ -12,6 +12,11 @@
 //               accumulator to registers, one token row per thread; rows are scaled by the split RMSNorm factor and
 //               finished by the shared epilogue (store | residual | SiLU(gate)*up | q|k|v + RoPE + KV append), with
 //               the optional output shadow and its per-row sums of squares.
+// Few tiles (decode batches of 17..256 rows against a narrow projection) leave most SMs idle and the launch far from
+// the HBM rate, so such launches split K over a thread-block cluster of up to 8 CTAs (grid z): every CTA accumulates
+// its K range in its own tensor memory, dumps the f32 partial tile to its shared memory (the operand ring is free by
+// then), and after a cluster barrier each CTA sums one column slice of the tile over all peers (distributed shared
+// memory, fixed order z = 0..S-1, so results do not depend on timing) and runs the epilogue on that slice.
 // Reference arithmetic replaced: src/ops/matmul.cpp:35-67 -> src/kernels/cpu/matmul.h:10-22 for rows = batch * length.
 #include "linear_common.cuh"
 
@@ -77,6 +82,45 @@ __device__ __forceinline__ uint64_t operand_descriptor(uint32_t smem_address) {
 constexpr uint32_t kInstruction = (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(kTileN >> 3) << 17)
                                   | (static_cast<uint32_t>(kTileM >> 4) << 24);
 
+// One finished pair of adjacent features of one token row: shared epilogue, then the optional output shadow (hi + lo of
+// the value times the next norm weight) and the running sum of squares of the new residual stream.
+template <int EPI>
+__device__ __forceinline__ void finish_pair(const LinearParams& p, int row, int feature0, float a, float b, float& squares) {
+    linear_epilogue<EPI>(p, row, feature0, a, b);
+    if constexpr (EPI == B200_EPI_RESIDUAL) {
+        const bool second = feature0 + 1 < p.out;
+        squares += a * a + (second ? b * b : 0.0f);
+        if (p.out_hi) {
+            float wa = 1.0f, wb = 1.0f;
+            if (p.out_norm_weight) {
+                if (p.out_norm_dtype == B200_BF16) {
+                    const __nv_bfloat16* w = static_cast<const __nv_bfloat16*>(p.out_norm_weight) + feature0;
+                    wa = __bfloat162float(w[0]);
+                    wb = second ? __bfloat162float(w[1]) : 0.0f;
+                } else {
+                    const float* w = static_cast<const float*>(p.out_norm_weight) + feature0;
+                    wa = w[0];
+                    wb = second ? w[1] : 0.0f;
+                }
+            }
+            const float va = __fmul_rn(a, wa), vb = __fmul_rn(b, wb);
+            const __nv_bfloat162 hi = __floats2bfloat162_rn(va, vb);
+            const __nv_bfloat162 lo = __floats2bfloat162_rn(va - __low2float(hi), vb - __high2float(hi));
+            const int64_t at = static_cast<int64_t>(row) * p.out + feature0;
+            *reinterpret_cast<__nv_bfloat162*>(p.out_hi + at) = hi;
+            *reinterpret_cast<__nv_bfloat162*>(p.out_lo + at) = lo;
+        }
+    }
+    if constexpr (EPI == B200_EPI_SWIGLU) {
+        if (p.out_hi) {
+            const __nv_bfloat16 hi = __float2bfloat16_rn(a);
+            const int64_t at = static_cast<int64_t>(row) * (p.out >> 1) + (feature0 >> 1);
+            p.out_hi[at] = hi;
+            p.out_lo[at] = __float2bfloat16_rn(a - __bfloat162float(hi));
+        }
+    }
+}
+
 template <int EPI>
 __global__ void __launch_bounds__(kGemmThreads, 1) linear_gemm_kernel(const __grid_constant__ CUtensorMap map_hi,
                                                                       const __grid_constant__ CUtensorMap map_lo,
@@ -91,7 +135,10 @@ __global__ void __launch_bounds__(kGemmThreads, 1) linear_gemm_kernel(const __gr
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int m0 = blockIdx.x * kTileM, n0 = blockIdx.y * kTileN;
-    const int k_blocks = (p.in + kBlockK - 1) / kBlockK;
+    // K split: the cluster spans grid z; CTA z of S takes k blocks [k_begin, k_end), never empty (S <= k blocks).
+    const int split = static_cast<int>(gridDim.z), part = static_cast<int>(blockIdx.z);
+    const int all_blocks = (p.in + kBlockK - 1) / kBlockK;
+    const int k_begin = all_blocks * part / split, k_blocks = all_blocks * (part + 1) / split - k_begin;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kStages; ++s) {
@@ -118,23 +165,24 @@ __global__ void __launch_bounds__(kGemmThreads, 1) linear_gemm_kernel(const __gr
             tma_prefetch_descriptor(&map_hi);
             tma_prefetch_descriptor(&map_lo);
             tma_prefetch_descriptor(&map_w);
-            for (int kb = 0; kb < k_blocks; ++kb) {
-                const int s = kb % kStages;
-                const uint32_t phase = (kb / kStages) & 1;
+            for (int i = 0; i < k_blocks; ++i) {
+                const int s = i % kStages;
+                const uint32_t phase = (i / kStages) & 1;
                 if (!mbar_wait(&empty[s], phase ^ 1)) { atomicExch(gp.status, B200_DEVICE_TIMEOUT); break; }
                 uint8_t* stage = smem + s * kStageBytes;
+                const int k0 = (k_begin + i) * kBlockK;
                 mbar_expect_tx(&full[s], kStageBytes);
-                tma_load_2d(stage, &map_hi, kb * kBlockK, m0, &full[s]);
-                tma_load_2d(stage + kBoxBytes, &map_lo, kb * kBlockK, m0, &full[s]);
-                tma_load_2d(stage + 2 * kBoxBytes, &map_w, kb * kBlockK, n0, &full[s]);
+                tma_load_2d(stage, &map_hi, k0, m0, &full[s]);
+                tma_load_2d(stage + kBoxBytes, &map_lo, k0, m0, &full[s]);
+                tma_load_2d(stage + 2 * kBoxBytes, &map_w, k0, n0, &full[s]);
             }
         }
     } else if (warp == 1) {
         if (lane == 0) {
             bool alive = true;
-            for (int kb = 0; kb < k_blocks && alive; ++kb) {
-                const int s = kb % kStages;
-                const uint32_t phase = (kb / kStages) & 1;
+            for (int i = 0; i < k_blocks && alive; ++i) {
+                const int s = i % kStages;
+                const uint32_t phase = (i / kStages) & 1;
                 if (!mbar_wait(&full[s], phase)) { atomicExch(gp.status, B200_DEVICE_TIMEOUT); alive = false; break; }
                 tc_fence_after_sync();
                 const uint32_t stage = smem_u32(smem + s * kStageBytes);
@@ -143,28 +191,34 @@ __global__ void __launch_bounds__(kGemmThreads, 1) linear_gemm_kernel(const __gr
 #pragma unroll
                 for (int k = 0; k < kBlockK / 16; ++k) {
                     // advancing the start address by 32 bytes selects the next 16 columns inside the swizzled rows
-                    tc_mma_bf16(tmem_base, hi + 2 * k, w + 2 * k, kInstruction, (kb | k) != 0);
+                    tc_mma_bf16(tmem_base, hi + 2 * k, w + 2 * k, kInstruction, (i | k) != 0);
                     tc_mma_bf16(tmem_base, lo + 2 * k, w + 2 * k, kInstruction, 1);
                 }
                 tc_commit(&empty[s]);   // the stage may be refilled once these products have read it
             }
             if (alive) tc_commit(accumulator_ready);
         }
-    } else {
-        // ---- epilogue: warp w may touch TMEM lanes 32 * (w % 4) .. + 31; thread = one token row ----
-        const int quarter = warp & 3;
-        const int row = m0 + quarter * 32 + lane;
-        float scale = 1.0f;
+    }
+
+    // ---- epilogue warps 2-5: warp w may touch TMEM lanes 32 * (w % 4) .. + 31; thread = one token row ----
+    const bool finisher = warp >= 2;
+    const int quarter = warp & 3;
+    const int tile_row = quarter * 32 + lane;
+    const int row = m0 + tile_row;
+    float scale = 1.0f, squares = 0.0f;
+    bool ready = false;
+    if (finisher) {
         if (p.sumsq_in && row < p.rows) {
             float total = 0.0f;
             for (int i = 0; i < p.parts_in; ++i) total += __ldg(p.sumsq_in + static_cast<int64_t>(i) * p.rows + row);
             scale = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(total, static_cast<float>(p.in)), static_cast<float>(p.eps))));
         }
-        const bool ready = mbar_wait(accumulator_ready, 0);
+        ready = mbar_wait(accumulator_ready, 0);
         if (!ready && lane == 0) atomicExch(gp.status, B200_DEVICE_TIMEOUT);
         tc_fence_after_sync();
-        float squares = 0.0f;
-        if (ready) {
+    }
+    if (split == 1) {
+        if (finisher && ready) {
 #pragma unroll 1
             for (int c = 0; c < kTileN / 32; ++c) {
                 uint32_t r[32];
@@ -174,46 +228,49 @@ __global__ void __launch_bounds__(kGemmThreads, 1) linear_gemm_kernel(const __gr
                 for (int j = 0; j < 32; j += 2) {
                     const int feature0 = n0 + c * 32 + j;
                     if (feature0 >= p.out) continue;
-                    float a = __uint_as_float(r[j]) * scale, b = __uint_as_float(r[j + 1]) * scale;
-                    linear_epilogue<EPI>(p, row, feature0, a, b);
-                    if constexpr (EPI == B200_EPI_RESIDUAL) {
-                        const bool second = feature0 + 1 < p.out;
-                        squares += a * a + (second ? b * b : 0.0f);
-                        if (p.out_hi) {
-                            float wa = 1.0f, wb = 1.0f;
-                            if (p.out_norm_weight) {
-                                if (p.out_norm_dtype == B200_BF16) {
-                                    const __nv_bfloat16* w = static_cast<const __nv_bfloat16*>(p.out_norm_weight) + feature0;
-                                    wa = __bfloat162float(w[0]);
-                                    wb = second ? __bfloat162float(w[1]) : 0.0f;
-                                } else {
-                                    const float* w = static_cast<const float*>(p.out_norm_weight) + feature0;
-                                    wa = w[0];
-                                    wb = second ? w[1] : 0.0f;
-                                }
-                            }
-                            const float va = __fmul_rn(a, wa), vb = __fmul_rn(b, wb);
-                            const __nv_bfloat162 hi = __floats2bfloat162_rn(va, vb);
-                            const __nv_bfloat162 lo = __floats2bfloat162_rn(va - __low2float(hi), vb - __high2float(hi));
-                            const int64_t at = static_cast<int64_t>(row) * p.out + feature0;
-                            *reinterpret_cast<__nv_bfloat162*>(p.out_hi + at) = hi;
-                            *reinterpret_cast<__nv_bfloat162*>(p.out_lo + at) = lo;
-                        }
-                    }
-                    if constexpr (EPI == B200_EPI_SWIGLU) {
-                        if (p.out_hi) {
-                            const __nv_bfloat16 hi = __float2bfloat16_rn(a);
-                            const int64_t at = static_cast<int64_t>(row) * (p.out >> 1) + (feature0 >> 1);
-                            p.out_hi[at] = hi;
-                            p.out_lo[at] = __float2bfloat16_rn(a - __bfloat162float(hi));
-                        }
-                    }
+                    finish_pair<EPI>(p, row, feature0, __uint_as_float(r[j]) * scale, __uint_as_float(r[j + 1]) * scale, squares);
                 }
             }
             if constexpr (EPI == B200_EPI_RESIDUAL) {
                 if (p.sumsq_out && row < p.rows) p.sumsq_out[static_cast<int64_t>(blockIdx.y) * p.rows + row] = squares;
             }
         }
+    } else {
+        // Partial tile, transposed [feature column][token row] f32 (64 KB over the first stages of the drained ring):
+        // a warp's lanes are consecutive rows, so its stores and the peers' loads are conflict-free and coalesced.
+        float* partial = reinterpret_cast<float*>(smem);
+        if (finisher && ready) {
+#pragma unroll 1
+            for (int c = 0; c < kTileN / 32; ++c) {
+                uint32_t r[32];
+                tmem_load_32(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + c * 32, r);
+#pragma unroll
+                for (int j = 0; j < 32; ++j) partial[(c * 32 + j) * kTileM + tile_row] = __uint_as_float(r[j]);
+            }
+        }
+        __syncwarp();
+        cluster_sync_all();   // every CTA's partial tile is complete and visible to its peers
+        if (finisher && ready && row < p.rows) {
+            const int width = ((kTileN + split - 1) / split + 1) & ~1;   // even: the epilogues work on feature pairs
+            const int c_begin = part * width, c_end = min(kTileN, c_begin + width);
+            const uint32_t mine = smem_u32(partial) + static_cast<uint32_t>(tile_row) * 4;
+#pragma unroll 1
+            for (int c = c_begin; c < c_end; c += 2) {
+                const int feature0 = n0 + c;
+                if (feature0 >= p.out) break;
+                float a = 0.0f, b = 0.0f;
+                for (int z = 0; z < split; ++z) {
+                    a += load_peer_shared(mine + static_cast<uint32_t>(c * kTileM) * 4, static_cast<uint32_t>(z));
+                    b += load_peer_shared(mine + static_cast<uint32_t>((c + 1) * kTileM) * 4, static_cast<uint32_t>(z));
+                }
+                finish_pair<EPI>(p, row, feature0, a * scale, b * scale, squares);
+            }
+            if constexpr (EPI == B200_EPI_RESIDUAL) {
+                if (p.sumsq_out) p.sumsq_out[(static_cast<int64_t>(blockIdx.y) * split + part) * p.rows + row] = squares;
+            }
+        }
+        __syncwarp();
+        cluster_sync_all();   // no CTA leaves while a peer may still read its shared memory
     }
     tc_fence_before_sync();
     __syncthreads();
@@ -237,16 +294,33 @@ int encode_operand(CUtensorMap* map, const void* base, int rows, int columns) {
     return B200_OK;
 }
 
+// K split of a launch: as many cluster CTAs as keep the grid within one wave of the SMs, at most 8 (the portable
+// cluster size), and at least two K blocks per CTA.
+int choose_split(int rows, int in, int out) {
+    int device = 0, sms = 148;
+    if (cudaGetDevice(&device) == cudaSuccess) sms = sm_count(device);
+    const int tiles = ((rows + kTileM - 1) / kTileM) * ((out + kTileN - 1) / kTileN);
+    const int k_blocks = (in + kBlockK - 1) / kBlockK;
+    int split = sms / (tiles > 0 ? tiles : 1);
+    if (split > 8) split = 8;
+    if (split > k_blocks / 2) split = k_blocks / 2;
+    return split < 1 ? 1 : split;
+}
+
 template <int EPI> int launch_gemm(const CUtensorMap& hi, const CUtensorMap& lo, const CUtensorMap& w, const GemmParams& gp, cudaStream_t stream) {
     auto kernel = linear_gemm_kernel<EPI>;
     B200_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kGemmSmem));
-    const dim3 grid((gp.base.rows + kTileM - 1) / kTileM, (gp.base.out + kTileN - 1) / kTileN);
-    return cuda_status(launch_dependent(kernel, grid, dim3(kGemmThreads), kGemmSmem, stream, hi, lo, w, gp), "linear_gemm_kernel launch");
+    const int split = choose_split(gp.base.rows, gp.base.in, gp.base.out);
+    const dim3 grid((gp.base.rows + kTileM - 1) / kTileM, (gp.base.out + kTileN - 1) / kTileN, split);
+    if (split == 1)
+        return cuda_status(launch_dependent(kernel, grid, dim3(kGemmThreads), kGemmSmem, stream, hi, lo, w, gp), "linear_gemm_kernel launch");
+    return cuda_status(launch_dependent_cluster(kernel, grid, dim3(kGemmThreads), kGemmSmem, stream, dim3(1, 1, split), hi, lo, w, gp),
+                       "linear_gemm_kernel cluster launch");
 }
 
 }  // namespace
 
-int linear_gemm_parts(int out) { return (out + kTileN - 1) / kTileN; }
+int linear_gemm_parts(int rows, int in, int out) { return ((out + kTileN - 1) / kTileN) * choose_split(rows, in, out); }
 
 int launch_linear_gemm(const LinearParams& p, int epilogue, cudaStream_t stream) {
     if (p.weight_dtype != B200_BF16 || !p.x_hi || !p.x_lo || (p.in & 7) || (p.out_hi && (p.out & 1))

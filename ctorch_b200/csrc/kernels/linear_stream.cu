@@ -438,15 +438,6 @@ template <int EPI> int pick_tile(const StreamParams& sp, size_t smem, int ctas, 
     }
 }
 
-int sm_count(int device) {
-    static std::mutex mutex;
-    static int counts[64];
-    std::lock_guard<std::mutex> lock(mutex);
-    if (device < 0 || device >= 64) return 148;
-    if (!counts[device] && cudaDeviceGetAttribute(&counts[device], cudaDevAttrMultiProcessorCount, device) != cudaSuccess) counts[device] = 148;
-    return counts[device];
-}
-
 // Tile size, ring depth and shared-memory size for a weight matrix [out, in]; false when nothing fits.
 bool choose_tiling(int in, int out, int sms, StreamParams& sp, size_t& smem) {
     sp.in_padded = (in + 63) & ~63;
@@ -478,7 +469,7 @@ bool choose_tiling(int in, int out, int sms, StreamParams& sp, size_t& smem) {
 
 int linear_stream_parts(int rows, int in, int out) {
     if ((in & 7) || in <= 0 || out <= 0) return 0;
-    if (rows >= kGemmRows || in > kMaxIn) return linear_gemm_parts(out);
+    if (rows >= kGemmRows || in > kMaxIn) return linear_gemm_parts(rows, in, out);
     int device = 0;
     if (cudaGetDevice(&device) != cudaSuccess) return 0;
     StreamParams sp{};

@@ -393,9 +393,12 @@ def test_shadow_protocol_swiglu_and_attention_output():
 
 
 @pytest.mark.parametrize("rows,inner,out,epilogue", [(40, 768, 1280, 0), (130, 2048, 768, 1), (300, 768, 4096, 2), (17, 4096, 200, 1),
-                                                     (128, 72, 136, 0)])
+                                                     (128, 72, 136, 0), (32, 4096, 1024, 1), (256, 2048, 3072, 2),
+                                                     (1000, 512, 2560, 0)])
 def test_dense_tensor_core_linear(rows, inner, out, epilogue):
-    """More than 16 rows (or a wide input) take the tcgen05 kernel: shadow input, split norm, every epilogue family."""
+    """More than 16 rows (or a wide input) take the tcgen05 kernel: shadow input, split norm, every epilogue family.
+    Launches with few tiles split K over a thread-block cluster (2..8 CTAs, the partial tiles summed through distributed
+    shared memory); the last case has enough tiles to run unsplit."""
     l = B.lib()
     rng = np.random.default_rng(rows + inner + out)
     x = rng.standard_normal((rows, inner), dtype=np.float32) * 2
@@ -410,7 +413,7 @@ def test_dense_tensor_core_linear(rows, inner, out, epilogue):
     xn = oracle.rms_norm(x, W.bf16_to_f32(norm), 1e-5)
     full = oracle.linear(xn, w)
     parts = l.b200_linear_shadow_parts(rows, inner, out)
-    assert parts == (out + 127) // 128
+    assert parts > 0 and parts % ((out + 127) // 128) == 0 and parts // ((out + 127) // 128) <= 8
     cols = out // 2 if epilogue == 2 else out
     y = torch.zeros((rows, cols), dtype=torch.float32, device="cuda")
     ohi = torch.zeros((rows, cols), dtype=torch.bfloat16, device="cuda")
