@@ -46,7 +46,8 @@ class ShadowLinearArgs(C.Structure):
     _fields_ = [("x_hi", C.c_void_p), ("x_lo", C.c_void_p), ("rows", C.c_int64), ("inner", C.c_int64), ("weight", C.c_void_p),
                 ("out", C.c_int64), ("sumsq_in", C.c_void_p), ("parts_in", C.c_int32), ("eps", C.c_double), ("epilogue", C.c_int),
                 ("residual", C.c_void_p), ("qkv", C.POINTER(QkvArgs)), ("y", C.c_void_p), ("out_hi", C.c_void_p),
-                ("out_lo", C.c_void_p), ("out_norm_weight", C.c_void_p), ("out_norm_dtype", C.c_int32), ("sumsq_out", C.c_void_p)]
+                ("out_lo", C.c_void_p), ("out_norm_weight", C.c_void_p), ("out_norm_dtype", C.c_int32), ("sumsq_out", C.c_void_p),
+                ("best_value", C.c_void_p), ("best_index", C.c_void_p)]
 
 
 class B200Error(RuntimeError):
@@ -142,6 +143,7 @@ def _declare(l: C.CDLL) -> None:
         "b200_rotary": (C.c_int, [vp, i64, i64, i64, vp, vp, vp, vp]),
         "b200_permute_0213": (C.c_int, [vp, i64, i64, i64, i64, vp, vp]),
         "b200_token_feedback": (C.c_int, [vp, i64, vp, vp, i64, vp, vp]),
+        "b200_argmax_finish": (C.c_int, [vp, vp, i32, i64, vp, vp, vp, i64, vp, vp]),
         "b200_scaled_add": (C.c_int, [vp, vp, C.c_float, i64, vp]),
         "b200_take_device_status": (C.c_int, [i32, vp, C.POINTER(i32)]),
     }

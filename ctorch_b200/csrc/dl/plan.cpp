@@ -317,6 +317,40 @@ void DecodePlan::logits(const Linear& output, Index rows, float* out, void* stre
     probe(0);
 }
 
+bool DecodePlan::prepare_choice(const Linear& output, Index rows, int device) {
+    const Index V = output.weight().size(0), D = owner_.dimensions();
+    if (!shadows_for(rows) || output.weight().dtype() != DType::bf16 || output.weight().size(1) != D) return false;
+    const Index parts = b200_linear_shadow_parts(rows, D, V);
+    if (parts <= 0) return false;
+    if (!best_value_.defined() || best_value_.numel() < parts * rows || best_value_.device().index != device) {
+        synchronize(Device::cuda(device));
+        const TensorOptions f32{DType::f32, Device::cuda(device)};
+        best_value_ = empty({parts * rows}, f32);
+        best_index_ = empty({parts * rows}, f32);   // int32 payload
+        ++buffer_epoch_;
+    }
+    return true;
+}
+
+void DecodePlan::choose(const Linear& output, Index rows, Index* next, Index* ids, Index* history, Index history_rows, std::int32_t* counter,
+                        void* stream) {
+    const Index V = output.weight().size(0), D = owner_.dimensions();
+    const Index parts = b200_linear_shadow_parts(rows, D, V);
+    if (parts <= 0 || !best_value_.defined() || best_value_.numel() < parts * rows)
+        throw std::logic_error("fused logits + argmax was not prepared for this row count");
+    b200_shadow_linear_args args{};
+    args.x_hi = hs_hi_.raw_data(); args.x_lo = hs_lo_.raw_data(); args.rows = rows; args.in = D;
+    args.weight = output.weight().raw_data(); args.out = V;
+    args.sumsq_in = sq_attn_.data<float>(); args.parts_in = last_parts_; args.eps = owner_.normalization().epsilon();
+    args.epilogue = B200_EPI_ARGMAX;
+    args.best_value = static_cast<float*>(best_value_.mutable_data());
+    args.best_index = static_cast<std::int32_t*>(best_index_.mutable_data());
+    shadow_linear(args, stream, "logits + argmax");
+    runtime::check(b200_argmax_finish(args.best_value, args.best_index, static_cast<std::int32_t>(parts), rows, next, ids, history, history_rows,
+                                      counter, stream), "argmax merge");
+    probe(2);
+}
+
 void DecodePlan::run_layers(const float* x, Index batch, Index length, std::span<KVCache> cache, Index max_length, void* stream,
                             bool shadow_ready) {
     const Index D = owner_.dimensions(), F = owner_.hidden(), rows = batch * length;
@@ -441,6 +475,7 @@ Tensor DecodePlan::decode(const Tensor& input, std::span<KVCache> cache) {
     const int device = input.device().index;
     runtime::set_device(device);
     refresh();
+    user_ = nullptr;
     validate(batch, length, cache, device);
     Tensor result = empty(input.shape(), {DType::f32, input.device()});
     if (rows == 0) return result;
@@ -542,6 +577,8 @@ void Generation::prefill(const Tensor& prompt) {
         }
         synchronize(Device::cuda(device_));  // `part` and the chunk buffers are reused
     }
+    plan.set_user(this);
+    logits_current_ = true;   // the prompt's last position went through the materialised head
     ++generated_;
 }
 
@@ -554,6 +591,11 @@ void Generation::enqueue_step(void* stream, Index max_length) {
     for (auto& layer : *cache_) handles.push_back(layer.handle());
     runtime::check(b200_kv_cache_advance(handles.data(), static_cast<int32_t>(handles.size()), 1, stream), "KV advance");
     probe(2);
+    if (fused_choice_) {
+        plan.choose(*output_, batch_, static_cast<Index*>(next_.mutable_data()), static_cast<Index*>(ids_.mutable_data()),
+                    static_cast<Index*>(history_.mutable_data()), max_steps_, static_cast<int32_t*>(counter_.mutable_data()), stream);
+        return;
+    }
     plan.logits(*output_, batch_, static_cast<float*>(logits_.mutable_data()), stream);
     runtime::check(b200_argmax(logits_.data<float>(), batch_, output_->weight().size(0), static_cast<Index*>(next_.mutable_data()), stream), "argmax");
     runtime::check(b200_token_feedback(next_.data<Index>(), batch_, static_cast<Index*>(ids_.mutable_data()),
@@ -562,13 +604,19 @@ void Generation::enqueue_step(void* stream, Index max_length) {
     probe(2);
 }
 
+void Generation::prepare() {
+    auto& plan = decoder_->plan();
+    plan.reserve(batch_, cache_->front().capacity(), device_);
+    fused_choice_ = plan.prepare_choice(*output_, batch_, device_);
+}
+
 void Generation::capture() {
     auto& plan = decoder_->plan();
     plan.refresh();
     const std::uint64_t version = decoder_->version() + tokens_->version() + output_->version();
     runtime::set_device(device_);
     const Index capacity = cache_->front().capacity();
-    plan.reserve(batch_, capacity, device_);
+    prepare();
     if (graph_ && graph_version_ == version && graph_epoch_ == plan.buffer_epoch()) return;
     if (graph_) { cudaGraphExecDestroy(graph_); graph_ = nullptr; }
     cudaStream_t stream = cuda_stream(device_);
@@ -601,6 +649,10 @@ void Generation::step(Index steps) {
     decoder_->plan().refresh();
     decoder_->plan().validate(batch_, steps, *cache_, device_);  // capacity for all `steps` single-token appends
     capture();
+    if (steps > 0) {
+        decoder_->plan().set_user(this);
+        logits_current_ = !fused_choice_;
+    }
     cudaStream_t stream = cuda_stream(device_);
     for (Index i = 0; i < steps; ++i) runtime::check_cuda(cudaGraphLaunch(graph_, stream), "cudaGraphLaunch");
     for (auto& layer : *cache_) layer.commit(steps);
@@ -635,7 +687,9 @@ Generation::StepProfile Generation::profile_step() {
     auto& plan = decoder_->plan();
     plan.refresh();
     plan.validate(batch_, 1, *cache_, device_);
-    plan.reserve(batch_, cache_->front().capacity(), device_);
+    prepare();
+    plan.set_user(this);
+    logits_current_ = !fused_choice_;
     cudaStream_t stream = cuda_stream(device_);
     runtime::check_cuda(cudaStreamSynchronize(stream), "cudaStreamSynchronize");
     StepProbe trail{stream, {}, {}};
@@ -671,6 +725,15 @@ Tensor Generation::tokens() const {
             static_cast<Index*>(result.mutable_data())[b * generated_ + s] = host.data<Index>()[s * batch_ + b];
     return result;
 }
-Tensor Generation::last_logits() const { return logits_; }
+Tensor Generation::last_logits() {
+    if (logits_current_) return logits_;
+    if (generated_ == 0) throw std::logic_error("nothing has been generated yet");
+    auto& plan = decoder_->plan();
+    if (plan.user() != this) throw std::logic_error("the decoder has run something else since this generation's last step");
+    runtime::set_device(device_);
+    plan.logits(*output_, batch_, static_cast<float*>(logits_.mutable_data()), runtime::stream(device_));
+    logits_current_ = true;
+    return logits_;
+}
 
 }  // namespace dl::nn

@@ -37,6 +37,15 @@ public:
     void embed(const Embedding& tokens, const Index* ids, Index rows, float* x, void* stream);
     // Logits of the last run_layers' rows (decode step: final norm folded into the projection).
     void logits(const Linear& output, Index rows, float* out, void* stream);
+    // Fused logits + greedy choice (no logits in memory): prepare_choice() sizes the per-tile candidate buffers and says
+    // whether the fused path serves this projection and row count; choose() enqueues the projection with the argmax
+    // epilogue and the merge, which also feeds the chosen ids back (ids, history, counter as b200_token_feedback).
+    bool prepare_choice(const Linear& output, Index rows, int device);
+    void choose(const Linear& output, Index rows, Index* next, Index* ids, Index* history, Index history_rows, std::int32_t* counter,
+                void* stream);
+    // Who ran the plan last: the final hidden state in the workspaces belongs to that user (nullptr: Module::decode).
+    void set_user(const void* user) { user_ = user; }
+    const void* user() const { return user_; }
     // Whether a pass over `rows` activation rows runs on the shadow protocol (bf16 model and every projection inside
     // the limits of the kernel that serves that row count).
     bool shadows_for(Index rows) const;
@@ -63,6 +72,8 @@ private:
     bool shadow_ = false;
     int last_parts_ = 0;
     Tensor hs_hi_, hs_lo_, att_hi_, att_lo_, act_hi_, act_lo_, sq_attn_, sq_ffn_;
+    Tensor best_value_, best_index_;   // [tiles][rows] candidates of the fused logits + argmax
+    const void* user_ = nullptr;
 };
 
 // Greedy generation with the token loop resident on the device (the loop of examples/decoder_generate.cpp:20-31).
@@ -80,7 +91,10 @@ public:
     void step_host(const Index* ids_in, Index* ids_out);
     Index generated() const { return generated_; }
     Tensor tokens() const;         // [batch, generated] int64 on the host (synchronises)
-    Tensor last_logits() const;    // [batch, vocab] f32 on the device: logits the latest token was chosen from
+    // [batch, vocab] f32 on the device: logits the latest token was chosen from.  Steps choose their token without
+    // writing logits; they are computed here, on demand, from the final hidden state of the last step, which is only
+    // possible while nothing else has used the decoder since (logic_error otherwise).
+    Tensor last_logits();
     Index launches_per_step() const { return launches_per_step_; }
     // One real step run eagerly with a CUDA event after every launch: milliseconds spent in the skinny-linear
     // launches, in the attention launches and in everything else, and the number of launches.
@@ -89,12 +103,14 @@ public:
 
 private:
     void enqueue_step(void* stream, Index max_length);
+    void prepare();   // workspaces of a single-token step, before anything is enqueued or captured
     void capture();
     std::shared_ptr<TransformerDecoder> decoder_;
     std::shared_ptr<Embedding> tokens_;
     std::shared_ptr<Linear> output_;
     std::vector<KVCache>* cache_;
     Index batch_, max_steps_, generated_ = 0, launches_per_step_ = 0;
+    bool fused_choice_ = false, logits_current_ = false;
     int device_ = 0;
     Tensor ids_, next_, logits_, history_, counter_, x_;
     std::shared_ptr<runtime::Storage> pinned_;

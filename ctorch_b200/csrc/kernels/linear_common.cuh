@@ -34,7 +34,26 @@ struct LinearParams {
     const void* out_norm_weight;       // weight of the RMSNorm that follows, folded into the output shadow
     int out_norm_dtype;
     float* sumsq_out;                  // [tiles][rows] per-tile sums of squares of the (un-weighted) result rows
+    // B200_EPI_ARGMAX: per feature tile and row, the preferred value and its feature index
+    float* best_value;                 // [tiles][rows]
+    int32_t* best_index;               // [tiles][rows]
 };
+
+// (value, index) ordering of the reference's argmax (src/kernels/cpu/reduction.cpp:128-151): a NaN beats every number,
+// and among equals (or among NaNs) the lower index wins.
+struct Candidate { float value; int32_t index; };
+__device__ __forceinline__ bool preferred(const Candidate& a, const Candidate& b) {
+    const bool an = a.value != a.value, bn = b.value != b.value;
+    if (an || bn) return an && (!bn || a.index < b.index);
+    return a.value > b.value || (a.value == b.value && a.index < b.index);
+}
+// The better of the two adjacent features (feature0, feature0 + 1) of one row; feature0 + 1 may lie past `out`.
+__device__ __forceinline__ Candidate pair_candidate(int feature0, float a, float b, int out) {
+    Candidate first{a, feature0};
+    const Candidate second{b, feature0 + 1};
+    if (feature0 + 1 < out && preferred(second, first)) first = second;
+    return first;
+}
 
 // Finishes one pair of adjacent output features (feature0 even) of activation row `row`.
 //   store | residual add (src/nn/decoder.cpp:104-105) | SiLU(gate)*up on interleaved rows (src/nn/decoder.cpp:16) |
@@ -56,6 +75,8 @@ __device__ __forceinline__ void linear_epilogue(const LinearParams& p, int row, 
         // rows 2j (gate_j) and 2j+1 (up_j) of the interleaved weight
         a = __fmul_rn(silu_reference(a), b);
         if (p.y) p.y[static_cast<int64_t>(row) * (p.out >> 1) + (feature0 >> 1)] = a;
+    } else if constexpr (EPI == B200_EPI_ARGMAX) {
+        // nothing is stored: the kernels reduce the pairs of a tile to one candidate per row themselves
     } else {
         const int D = p.heads * p.head_dim, KV = p.kv_heads * p.head_dim;
         const int sequence = row / p.tokens_per_sequence;

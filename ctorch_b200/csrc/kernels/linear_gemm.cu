@@ -206,6 +206,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) linear_gemm_kernel(const __gr
     const int tile_row = quarter * 32 + lane;
     const int row = m0 + tile_row;
     float scale = 1.0f, squares = 0.0f;
+    Candidate best{-INFINITY, INT32_MAX};   // B200_EPI_ARGMAX: this row's preferred feature among the columns seen so far
     bool ready = false;
     if (finisher) {
         if (p.sumsq_in && row < p.rows) {
@@ -228,11 +229,23 @@ __global__ void __launch_bounds__(kGemmThreads, 1) linear_gemm_kernel(const __gr
                 for (int j = 0; j < 32; j += 2) {
                     const int feature0 = n0 + c * 32 + j;
                     if (feature0 >= p.out) continue;
-                    finish_pair<EPI>(p, row, feature0, __uint_as_float(r[j]) * scale, __uint_as_float(r[j + 1]) * scale, squares);
+                    const float a = __uint_as_float(r[j]) * scale, b = __uint_as_float(r[j + 1]) * scale;
+                    if constexpr (EPI == B200_EPI_ARGMAX) {
+                        const Candidate pair = pair_candidate(feature0, a, b, p.out);
+                        if (preferred(pair, best)) best = pair;
+                    } else {
+                        finish_pair<EPI>(p, row, feature0, a, b, squares);
+                    }
                 }
             }
             if constexpr (EPI == B200_EPI_RESIDUAL) {
                 if (p.sumsq_out && row < p.rows) p.sumsq_out[static_cast<int64_t>(blockIdx.y) * p.rows + row] = squares;
+            }
+            if constexpr (EPI == B200_EPI_ARGMAX) {
+                if (row < p.rows) {
+                    p.best_value[static_cast<int64_t>(blockIdx.y) * p.rows + row] = best.value;
+                    p.best_index[static_cast<int64_t>(blockIdx.y) * p.rows + row] = best.index;
+                }
             }
         }
     } else {
@@ -263,10 +276,19 @@ __global__ void __launch_bounds__(kGemmThreads, 1) linear_gemm_kernel(const __gr
                     a += load_peer_shared(mine + static_cast<uint32_t>(c * kTileM) * 4, static_cast<uint32_t>(z));
                     b += load_peer_shared(mine + static_cast<uint32_t>((c + 1) * kTileM) * 4, static_cast<uint32_t>(z));
                 }
-                finish_pair<EPI>(p, row, feature0, a * scale, b * scale, squares);
+                if constexpr (EPI == B200_EPI_ARGMAX) {
+                    const Candidate pair = pair_candidate(feature0, a * scale, b * scale, p.out);
+                    if (preferred(pair, best)) best = pair;
+                } else {
+                    finish_pair<EPI>(p, row, feature0, a * scale, b * scale, squares);
+                }
             }
             if constexpr (EPI == B200_EPI_RESIDUAL) {
                 if (p.sumsq_out) p.sumsq_out[(static_cast<int64_t>(blockIdx.y) * split + part) * p.rows + row] = squares;
+            }
+            if constexpr (EPI == B200_EPI_ARGMAX) {
+                p.best_value[(static_cast<int64_t>(blockIdx.y) * split + part) * p.rows + row] = best.value;
+                p.best_index[(static_cast<int64_t>(blockIdx.y) * split + part) * p.rows + row] = best.index;
             }
         }
         __syncwarp();
@@ -339,6 +361,7 @@ int launch_linear_gemm(const LinearParams& p, int epilogue, cudaStream_t stream)
     case B200_EPI_RESIDUAL: return launch_gemm<B200_EPI_RESIDUAL>(hi, lo, w, gp, stream);
     case B200_EPI_SWIGLU: return launch_gemm<B200_EPI_SWIGLU>(hi, lo, w, gp, stream);
     case B200_EPI_QKV: return launch_gemm<B200_EPI_QKV>(hi, lo, w, gp, stream);
+    case B200_EPI_ARGMAX: return launch_gemm<B200_EPI_ARGMAX>(hi, lo, w, gp, stream);
     }
     return B200_UNSUPPORTED;
 }

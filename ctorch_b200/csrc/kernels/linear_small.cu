@@ -236,6 +236,10 @@ extern "C" int b200_linear(const float* x, int64_t rows, int64_t in, const void*
         set_error("b200_linear: weight dtype %d is not f32 or bf16", weight_dtype);
         return B200_UNSUPPORTED;
     }
+    if (epilogue < B200_EPI_STORE || epilogue > B200_EPI_QKV) {
+        set_error("b200_linear: epilogue %d is not available for f32 activation rows", static_cast<int>(epilogue));
+        return B200_UNSUPPORTED;
+    }
     if (rows == 0) return B200_OK;
     LinearParams p{};
     p.x = x; p.rows = static_cast<int>(rows); p.in = static_cast<int>(in); p.out = static_cast<int>(out);
@@ -268,7 +272,9 @@ extern "C" int b200_linear_shadow(const b200_shadow_linear_args* args, void* str
     }
     if (args->rows == 0) return B200_OK;
     const int epilogue = args->epilogue;
-    if ((epilogue != B200_EPI_SWIGLU && !args->y && epilogue != B200_EPI_QKV) || (epilogue == B200_EPI_RESIDUAL && !args->residual)
+    if (epilogue < B200_EPI_STORE || epilogue > B200_EPI_ARGMAX) { set_error("b200_linear_shadow: unknown epilogue"); return B200_BAD_ARGUMENT; }
+    if ((epilogue != B200_EPI_SWIGLU && !args->y && epilogue != B200_EPI_QKV && epilogue != B200_EPI_ARGMAX)
+        || (epilogue == B200_EPI_ARGMAX && (!args->best_value || !args->best_index)) || (epilogue == B200_EPI_RESIDUAL && !args->residual)
         || (epilogue == B200_EPI_SWIGLU && (args->out & 1)) || (epilogue == B200_EPI_SWIGLU && !args->y && !args->out_hi)
         || (args->out_hi && !args->out_lo) || (args->sumsq_in && args->parts_in <= 0)) {
         set_error("b200_linear_shadow: inconsistent epilogue operands");
@@ -282,6 +288,7 @@ extern "C" int b200_linear_shadow(const b200_shadow_linear_args* args, void* str
     p.sumsq_in = args->sumsq_in; p.parts_in = args->parts_in;
     p.out_hi = static_cast<__nv_bfloat16*>(args->out_hi); p.out_lo = static_cast<__nv_bfloat16*>(args->out_lo);
     p.out_norm_weight = args->out_norm_weight; p.out_norm_dtype = args->out_norm_dtype; p.sumsq_out = args->sumsq_out;
+    p.best_value = args->best_value; p.best_index = args->best_index;
     const int status = fill_qkv(p, epilogue, args->qkv, args->rows, args->out);
     if (status != B200_OK) return status;
     const int launched = launch_linear_stream(p, epilogue, as_stream(stream));

@@ -402,6 +402,19 @@ __global__ void __launch_bounds__(kThreads, 2) linear_stream_kernel(const Stream
                     *reinterpret_cast<__nv_bfloat162*>(p.out_lo + at) = lo;
                 }
             }
+            if constexpr (EPI == B200_EPI_ARGMAX) {
+                // the TF/2 threads of a row are consecutive lanes: butterfly to the row's candidate of this tile
+                Candidate best = live ? pair_candidate(feature0, a, b, p.out) : Candidate{-INFINITY, INT32_MAX};
+#pragma unroll
+                for (int o = 1; o < TF / 2; o <<= 1) {
+                    const Candidate other{__shfl_xor_sync(0xffffffffu, best.value, o), __shfl_xor_sync(0xffffffffu, best.index, o)};
+                    if (preferred(other, best)) best = other;
+                }
+                if (f == 0 && in_tile && row < p.rows) {
+                    p.best_value[static_cast<int64_t>(tile) * p.rows + row] = best.value;
+                    p.best_index[static_cast<int64_t>(tile) * p.rows + row] = best.index;
+                }
+            }
             if constexpr (SHADOW && EPI == B200_EPI_SWIGLU) {
                 if (p.out_hi && live) {
                     const __nv_bfloat16 hi = __float2bfloat16_rn(a);
@@ -502,6 +515,7 @@ int launch_linear_stream(const LinearParams& p, int epilogue, cudaStream_t strea
     case B200_EPI_RESIDUAL: return pick_tile<B200_EPI_RESIDUAL>(sp, smem, ctas, row_tiles, stream);
     case B200_EPI_SWIGLU: return pick_tile<B200_EPI_SWIGLU>(sp, smem, ctas, row_tiles, stream);
     case B200_EPI_QKV: return pick_tile<B200_EPI_QKV>(sp, smem, ctas, row_tiles, stream);
+    case B200_EPI_ARGMAX: return p.x_hi ? pick_tile<B200_EPI_ARGMAX>(sp, smem, ctas, row_tiles, stream) : B200_UNSUPPORTED;
     }
     return B200_UNSUPPORTED;
 }

@@ -1,6 +1,6 @@
 // Small operators of the token loop (embedding gather, stand-alone RMSNorm, argmax, row select) and the host
 // utilities shared by the kernel files (error text, driver entry point lookup, device status word).
-#include "common.cuh"
+#include "linear_common.cuh"
 
 #include <cstring>
 #include <mutex>
@@ -264,6 +264,36 @@ __global__ void token_feedback_kernel(const int64_t* next, int64_t batch, int64_
     if (threadIdx.x == 0) *counter = step + 1;
 }
 
+// Merge of the per-tile candidates of the fused logits + argmax: warp w takes rows w, w + warps, ...; its lanes walk the
+// tiles, a butterfly leaves the row's choice, and lane 0 does the token bookkeeping of token_feedback_kernel.
+__global__ void __launch_bounds__(1024) argmax_finish_kernel(const float* best_value, const int32_t* best_index, int parts, int64_t rows,
+                                                             int64_t* next, int64_t* ids, int64_t* history, int64_t history_rows,
+                                                             int32_t* counter) {
+    grid_dependency_wait();
+    grid_launch_dependents();
+    const int32_t step = *counter;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
+    for (int64_t row = warp; row < rows; row += warps) {
+        Candidate best{-INFINITY, INT32_MAX};
+        for (int t = lane; t < parts; t += 32) {
+            const Candidate other{best_value[static_cast<int64_t>(t) * rows + row], best_index[static_cast<int64_t>(t) * rows + row]};
+            if (preferred(other, best)) best = other;
+        }
+        for (int o = 16; o > 0; o >>= 1) {
+            const Candidate other{__shfl_xor_sync(0xffffffffu, best.value, o), __shfl_xor_sync(0xffffffffu, best.index, o)};
+            if (preferred(other, best)) best = other;
+        }
+        if (lane == 0) {
+            const int64_t token = best.index;
+            next[row] = token;
+            if (ids) ids[row] = token;
+            if (history && step < history_rows) history[static_cast<int64_t>(step) * rows + row] = token;
+        }
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) *counter = step + 1;
+}
+
 unsigned blocks_for(int64_t n) { return static_cast<unsigned>((n + 255) / 256 < 8192 ? (n + 255) / 256 : 8192); }
 
 }  // namespace
@@ -278,6 +308,14 @@ int b200_rotary(const float* x, int64_t outer, int64_t length, int64_t head_dim,
     if (pairs == 0) return B200_OK;
     b200::rotary_kernel<<<b200::blocks_for(pairs), 256, 0, as_stream(stream)>>>(x, pairs, length, head_dim / 2, cosine, sine, out);
     return cuda_status(cudaGetLastError(), "rotary_kernel launch");
+}
+
+int b200_argmax_finish(const float* best_value, const int32_t* best_index, int32_t parts, int64_t rows, int64_t* next, int64_t* ids,
+                       int64_t* history, int64_t history_rows, int32_t* counter, void* stream) {
+    if (!best_value || !best_index || !next || !counter || parts <= 0 || rows <= 0) { set_error("b200_argmax_finish: bad pointer or size"); return B200_BAD_ARGUMENT; }
+    const unsigned threads = rows >= 32 ? 1024 : static_cast<unsigned>(rows) * 32;
+    return cuda_status(launch_dependent(b200::argmax_finish_kernel, dim3(1), dim3(threads), 0, as_stream(stream), best_value, best_index,
+                                        static_cast<int>(parts), rows, next, ids, history, history_rows, counter), "argmax_finish_kernel launch");
 }
 
 int b200_permute_0213(const float* in, int64_t a, int64_t b, int64_t c, int64_t d, float* out, void* stream) {

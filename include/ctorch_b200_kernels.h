@@ -84,8 +84,13 @@ typedef enum b200_epilogue {
     B200_EPI_STORE = 0,     /* y[r,o] = acc                                   (dl::linear, src/ops/matmul.cpp:35-67) */
     B200_EPI_RESIDUAL = 1,  /* y[r,o] = residual[r,o] + acc                   (src/nn/decoder.cpp:104-105) */
     B200_EPI_SWIGLU = 2,    /* weight rows interleaved gate_j, up_j: y[r,j] = silu(gate) * up   (src/nn/decoder.cpp:16) */
-    B200_EPI_QKV = 3        /* fused q|k|v rows: RoPE on q and k, q stored, k and v appended to the KV cache
+    B200_EPI_QKV = 3,       /* fused q|k|v rows: RoPE on q and k, q stored, k and v appended to the KV cache
                                (src/nn/decoder.cpp:80-86) */
+    B200_EPI_ARGMAX = 4     /* shadow linears only: nothing is stored; every feature tile leaves, per row, its best value
+                               and the index of it under the reference's rule (first maximum, first NaN wins:
+                               src/kernels/cpu/reduction.cpp:128-151).  b200_argmax_finish merges the tiles.  This is
+                               logits + greedy choice without materialising the logits
+                               (examples/decoder_generate.cpp:27-30). */
 } b200_epilogue;
 
 /* Extra operands of B200_EPI_QKV. */
@@ -141,12 +146,19 @@ typedef struct b200_shadow_linear_args {
     const void* out_norm_weight;   /* residual epilogue: weight [out] of the norm that follows, folded into the shadow */
     int32_t out_norm_dtype;
     float* sumsq_out;              /* residual epilogue: [b200_linear_shadow_parts(rows, in, out)][rows] */
+    float* best_value;             /* B200_EPI_ARGMAX: [b200_linear_shadow_parts(rows, in, out)][rows] */
+    int32_t* best_index;           /* B200_EPI_ARGMAX: same shape, feature index of best_value */
 } b200_shadow_linear_args;
 /* Up to 16 rows with in <= 2048: streaming kernel (bulk-TMA weight ring, mma.sync).  More rows or a wider input:
  * dense tcgen05 kernel (TMA operand tiles, accumulator in tensor memory).  B200_UNSUPPORTED when in % 8 != 0. */
 B200_API int b200_linear_shadow(const b200_shadow_linear_args* args, void* stream);
 /* Number of row-sum partials a residual-epilogue call with these sizes writes (its feature tiles), 0 if unsupported. */
 B200_API int32_t b200_linear_shadow_parts(int64_t rows, int64_t in, int64_t out);
+/* Second half of the fused logits + greedy choice: merges the `parts` per-tile candidates of every row (same rule), writes
+ * the chosen feature index to next[rows], and does what b200_token_feedback does with it (ids, history, counter; any of
+ * ids / history may be NULL).  One launch of one CTA. */
+B200_API int b200_argmax_finish(const float* best_value, const int32_t* best_index, int32_t parts, int64_t rows, int64_t* next,
+                                int64_t* ids, int64_t* history, int64_t history_rows, int32_t* counter, void* stream);
 /* b200_embedding that also writes the shadow of out * norm_weight and one partial sum of squares per row ([1][rows]). */
 B200_API int b200_embedding_shadow(const void* table, int32_t table_dtype, const int64_t* ids, int64_t rows, int64_t vocab,
                                    int64_t width, const void* norm_weight, int32_t norm_dtype, float* out, void* out_hi,

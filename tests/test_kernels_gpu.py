@@ -442,3 +442,54 @@ def test_dense_tensor_core_linear(rows, inner, out, epilogue):
         assert rel(shadow_to_f32(ohi, olo), want) < 4e-5
     if epilogue == 1:
         assert rel(osq.cpu().numpy().sum(axis=0), (want.astype(np.float64) ** 2).sum(axis=1)) < 1e-4
+
+
+@pytest.mark.parametrize("rows,inner,vocab", [(16, 768, 32000), (5, 256, 1000), (40, 512, 5000), (32, 2048, 1024), (200, 256, 777 * 2)])
+def test_fused_logits_argmax(rows, inner, vocab):
+    """Logits + greedy choice without logits in memory: per-tile candidates from the projection's epilogue (streaming kernel
+    up to 16 rows, tcgen05 kernel above, K-split clusters when the tiles are few), then the merge.  Duplicated weight
+    rows make exact ties: the lowest index must win (src/kernels/cpu/reduction.cpp:128-151 of the reference)."""
+    l = B.lib()
+    rng = np.random.default_rng(rows * 7 + vocab)
+    x = rng.standard_normal((rows, inner), dtype=np.float32)
+    norm = W.bf16_bits((1 + 0.1 * rng.standard_normal(inner)).astype(np.float32))
+    w = 0.05 * rng.standard_normal((vocab, inner), dtype=np.float32)
+    xn = oracle.rms_norm(x, W.bf16_to_f32(norm), 1e-5)
+    # make the winning row of every activation row appear three times (same bits -> equal logits)
+    first = oracle.linear(xn, W.bf16_bits(w))
+    for r in range(rows):
+        top = int(first[r].argmax())
+        for clone in ((top * 7 + 11) % vocab, (top * 13 + 5) % vocab):
+            w[clone] = w[top]
+    wb = W.bf16_bits(w)
+    logits = oracle.linear(xn, wb)
+    want = oracle.argmax(logits)
+    xd, nd, wd = dev(x), bf16_dev(norm), bf16_dev(wb)
+    hi = torch.zeros((rows, inner), dtype=torch.bfloat16, device="cuda")
+    lo = torch.zeros_like(hi)
+    sq = torch.zeros((1, rows), dtype=torch.float32, device="cuda")
+    B.kcheck(l.b200_shadow_from_rows(xd.data_ptr(), rows, inner, nd.data_ptr(), B.BF16, hi.data_ptr(), lo.data_ptr(), sq.data_ptr(), stream()))
+    parts = l.b200_linear_shadow_parts(rows, inner, vocab)
+    assert parts > 0
+    best_value = torch.zeros((parts, rows), dtype=torch.float32, device="cuda")
+    best_index = torch.zeros((parts, rows), dtype=torch.int32, device="cuda")
+    next_ids = torch.full((rows,), -1, dtype=torch.int64, device="cuda")
+    ids = torch.full((rows,), -1, dtype=torch.int64, device="cuda")
+    history = torch.full((3, rows), -1, dtype=torch.int64, device="cuda")
+    counter = torch.tensor([1], dtype=torch.int32, device="cuda")
+    torch.cuda.synchronize()
+    args = B.ShadowLinearArgs(hi.data_ptr(), lo.data_ptr(), rows, inner, wd.data_ptr(), vocab, sq.data_ptr(), 1, 1e-5, 4, None, None, None,
+                              None, None, None, 0, None, best_value.data_ptr(), best_index.data_ptr())
+    B.kcheck(l.b200_linear_shadow(C.byref(args), stream()))
+    B.kcheck(l.b200_argmax_finish(best_value.data_ptr(), best_index.data_ptr(), parts, rows, next_ids.data_ptr(), ids.data_ptr(),
+                                  history.data_ptr(), 3, counter.data_ptr(), stream()))
+    sync()
+    got = next_ids.cpu().numpy()
+    # a tie in the oracle's f32 sums may not be a tie in the tensor-core sums (other summation order) only if the clone rows
+    # differ, and they do not: equal rows give equal sums on either side
+    chosen = logits[np.arange(rows), got]
+    assert np.allclose(chosen, logits.max(axis=1), rtol=0, atol=2e-4 * np.abs(logits).max())
+    near_tie = np.sort(logits, axis=1)[:, -4] > logits.max(axis=1) - 1e-3 * np.abs(logits).max()   # a fourth contender
+    assert np.array_equal(got[~near_tie], want[~near_tie])
+    assert np.array_equal(ids.cpu().numpy(), got) and np.array_equal(history.cpu().numpy()[1], got)
+    assert int(counter.item()) == 2
