@@ -96,6 +96,7 @@ def _declare(l: C.CDLL) -> None:
         "dl_state_release": (None, [vp]), "dl_state_size": (sz, [vp]), "dl_state_name": (C.c_char_p, [vp, sz]),
         "dl_state_tensor": (C.c_int, [vp, sz, pp]),
         "dl_state_create": (C.c_int, [C.POINTER(C.c_char_p), pp, sz, pp]),
+        "dl_state_save": (C.c_int, [C.c_char_p, vp]), "dl_state_load": (C.c_int, [C.c_char_p, pp]),
         "dl_swiglu_create": (C.c_int, [i64, i64, i32, TensorOptions, pp]),
         "dl_lora_linear_create": (C.c_int, [vp, i64, C.c_double, pp]), "dl_lora_linear_merge": (C.c_int, [vp, pp]),
         "dl_rotary_embedding_create": (C.c_int, [i64, i64, C.c_double, TensorOptions, pp]),
@@ -143,6 +144,8 @@ def _declare(l: C.CDLL) -> None:
         "b200_rotary": (C.c_int, [vp, i64, i64, i64, vp, vp, vp, vp]),
         "b200_permute_0213": (C.c_int, [vp, i64, i64, i64, i64, vp, vp]),
         "b200_token_feedback": (C.c_int, [vp, i64, vp, vp, i64, vp, vp]),
+        "b200_sample": (C.c_int, [vp, i64, i64, C.c_double, vp, vp, vp]),
+        "dl_generation_step_sampled": (C.c_int, [vp, C.c_double, vp, vp]),
         "b200_argmax_finish": (C.c_int, [vp, vp, i32, i64, vp, vp, vp, i64, vp, vp]),
         "b200_scaled_add": (C.c_int, [vp, vp, C.c_float, i64, vp]),
         "b200_take_device_status": (C.c_int, [i32, vp, C.POINTER(i32)]),
@@ -286,6 +289,32 @@ class Module:
             lib().dl_state_release(state)
 
 
+def load_archive(path: str) -> dict[str, Tensor]:
+    """Entries of a weight archive (".ct", the reference's dl::io::save layout) as host tensors, in file order."""
+    state = C.c_void_p()
+    check(lib().dl_state_load(os.fspath(path).encode(), C.byref(state)))
+    out = {}
+    try:
+        for i in range(lib().dl_state_size(state)):
+            t = C.c_void_p()
+            check(lib().dl_state_tensor(state, i, C.byref(t)))
+            out[lib().dl_state_name(state, i).decode()] = Tensor(t)
+    finally:
+        lib().dl_state_release(state)
+    return out
+
+
+def save_archive(path: str, named: dict[str, Tensor]) -> None:
+    names = (C.c_char_p * len(named))(*[n.encode() for n in named])
+    handles = (C.c_void_p * len(named))(*[t.h for t in named.values()])
+    state = C.c_void_p()
+    check(lib().dl_state_create(names, handles, len(named), C.byref(state)))
+    try:
+        check(lib().dl_state_save(os.fspath(path).encode(), state))
+    finally:
+        lib().dl_state_release(state)
+
+
 def options(dtype: int = F32, device: Device | None = None) -> TensorOptions:
     return TensorOptions(dtype, device or cpu(), 0)
 
@@ -354,6 +383,14 @@ class DecoderModel:
             check(l.dl_transformer_decoder_set_tensor_parallel(self.decoder.h, tensor_parallel[0], tensor_parallel[1]))
         self.cache = None
         self.new_cache()
+
+    def load_archive_state(self, state: dict[str, Tensor]) -> None:
+        """Weights from an archive of the reference's example model: "tokens.weight" (shared with the output projection
+        when tied, "output.weight" otherwise) and the decoder's own state under "decoder."."""
+        self.decoder.load_state({n[len("decoder."):]: t for n, t in state.items() if n.startswith("decoder.")})
+        self.embedding.load_state({"weight": state["tokens.weight"]})
+        if not self.spec.get("tied", True):
+            self.output.load_state({"weight": state["output.weight"]})
 
     def new_cache(self):
         self.release_cache()
@@ -434,6 +471,12 @@ class Generation:
         ip = C.POINTER(C.c_int64)
         check(lib().dl_generation_step_host(self.h, ids_in.ctypes.data_as(ip) if ids_in is not None else None,
                                             ids_out.ctypes.data_as(ip)))
+
+    def step_sampled(self, temperature: float, uniforms: np.ndarray) -> np.ndarray:
+        u = np.ascontiguousarray(uniforms, dtype=np.float64)
+        out = np.empty(u.shape[0], dtype=np.int64)
+        check(lib().dl_generation_step_sampled(self.h, float(temperature), u.ctypes.data, out.ctypes.data))
+        return out
 
     def tokens(self) -> np.ndarray:
         out = C.c_void_p()

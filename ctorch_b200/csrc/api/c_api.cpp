@@ -231,6 +231,19 @@ dl_status dl_state_create(const char* const* names, const dl_tensor* const* tens
     });
 }
 
+dl_status dl_state_save(const char* path, const dl_state* state) {
+    return invoke([&] {
+        if (!path) throw std::invalid_argument("path is NULL");
+        dl::io::save(path, need(state, "state").value);
+    });
+}
+dl_status dl_state_load(const char* path, dl_state** output) {
+    return make_handle(output, [&] {
+        if (!path) throw std::invalid_argument("path is NULL");
+        return dl::io::load(path);
+    });
+}
+
 // ---- decoder ------------------------------------------------------------------------------------------------
 dl_status dl_swiglu_create(int64_t dimensions, int64_t hidden, int32_t bias, dl_tensor_options options, dl_module** output) {
     return make_handle(output, [&] { return std::make_shared<dl::nn::SwiGLU>(dimensions, hidden, bias != 0, convert(options)); });
@@ -320,6 +333,9 @@ dl_status dl_generation_step(dl_generation* generation, int64_t steps) {
 }
 dl_status dl_generation_step_host(dl_generation* generation, const int64_t* ids_in, int64_t* ids_out) {
     return invoke([&] { need(generation, "generation").value->step_host(ids_in, ids_out); });
+}
+dl_status dl_generation_step_sampled(dl_generation* generation, double temperature, const double* uniforms, int64_t* ids_out) {
+    return invoke([&] { need(generation, "generation").value->step_sampled(temperature, uniforms, ids_out); });
 }
 dl_status dl_generation_tokens(dl_generation* generation, dl_tensor** output) {
     return make_handle(output, [&] { return need(generation, "generation").value->tokens(); });

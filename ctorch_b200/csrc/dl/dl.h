@@ -6,6 +6,7 @@
 
 #include "ctorch_b200_kernels.h"
 
+#include <filesystem>
 #include <cstddef>
 #include <cstdint>
 #include <memory>
@@ -361,4 +362,10 @@ private:
 };
 
 }  // namespace nn
+
+// ---- include/dl/io.h of the reference: weight archives (".ct"), see checkpoint.cpp for the layout --------------
+namespace io {
+void save(const std::filesystem::path& path, std::span<const NamedTensor> state);
+StateDict load(const std::filesystem::path& path);   // tensors in host memory
+}  // namespace io
 }  // namespace dl

@@ -514,7 +514,9 @@ Generation::Generation(std::shared_ptr<TransformerDecoder> decoder, std::shared_
     history_ = zeros({max_steps, batch}, {DType::i64, where});
     counter_ = zeros({1}, {DType::i64, where});  // the kernel uses the first 32 bits
     x_ = empty({batch, decoder_->dimensions()}, {DType::f32, where});
-    pinned_ = std::make_shared<runtime::Storage>(sizeof(Index) * static_cast<std::size_t>(batch) * 2, Device::cpu(), true);
+    uniform_ = zeros({batch}, {DType::f64, where});
+    // pinned staging: ids in, ids out, uniform variates
+    pinned_ = std::make_shared<runtime::Storage>(sizeof(Index) * static_cast<std::size_t>(batch) * 3, Device::cpu(), true);
 }
 Generation::~Generation() {
     try { synchronize(Device::cuda(device_)); } catch (...) {}
@@ -674,6 +676,46 @@ void Generation::step_host(const Index* ids_in, Index* ids_out) {
         if (generated_ == 0) generated_ = 1;  // the caller supplied the first token itself
     }
     step(1);
+    runtime::check_cuda(cudaMemcpyAsync(staging + batch_, next_.raw_data(), sizeof(Index) * static_cast<std::size_t>(batch_),
+                                        cudaMemcpyDeviceToHost, stream), "cudaMemcpyAsync");
+    runtime::check_cuda(cudaStreamSynchronize(stream), "cudaStreamSynchronize");
+    if (ids_out) std::copy(staging + batch_, staging + 2 * batch_, ids_out);
+}
+
+void Generation::step_sampled(double temperature, const double* uniforms, Index* ids_out) {
+    if (!(temperature > 0.0)) throw std::invalid_argument("temperature must be positive");
+    if (!uniforms) throw std::invalid_argument("uniform variates are NULL");
+    if (generated_ == 0) throw std::logic_error("prefill a prompt before stepping");
+    if (generated_ + 1 > max_steps_) throw std::out_of_range("generation step budget exhausted");
+    for (Index b = 0; b < batch_; ++b)
+        if (!(uniforms[b] >= 0.0 && uniforms[b] < 1.0)) throw std::invalid_argument("uniform variates must lie in [0, 1)");
+    runtime::set_device(device_);
+    auto& plan = decoder_->plan();
+    plan.refresh();
+    plan.validate(batch_, 1, *cache_, device_);
+    const Index capacity = cache_->front().capacity();
+    plan.reserve(batch_, capacity, device_);
+    plan.set_user(this);
+    cudaStream_t stream = cuda_stream(device_);
+    auto* staging = static_cast<Index*>(pinned_->data);
+    auto* variates = reinterpret_cast<double*>(staging + 2 * batch_);
+    std::copy(uniforms, uniforms + batch_, variates);
+    runtime::check_cuda(cudaMemcpyAsync(uniform_.mutable_data(), variates, sizeof(double) * static_cast<std::size_t>(batch_),
+                                        cudaMemcpyHostToDevice, stream), "cudaMemcpyAsync");
+    plan.embed(*tokens_, ids_.data<Index>(), batch_, static_cast<float*>(x_.mutable_data()), stream);
+    plan.run_layers(x_.data<float>(), batch_, 1, *cache_, capacity, stream, plan.shadows_for(batch_));
+    std::vector<b200_kv_cache*> handles;
+    for (auto& layer : *cache_) handles.push_back(layer.handle());
+    runtime::check(b200_kv_cache_advance(handles.data(), static_cast<int32_t>(handles.size()), 1, stream), "KV advance");
+    plan.logits(*output_, batch_, static_cast<float*>(logits_.mutable_data()), stream);
+    runtime::check(b200_sample(logits_.data<float>(), batch_, output_->weight().size(0), temperature, uniform_.data<double>(),
+                               static_cast<Index*>(next_.mutable_data()), stream), "sampling");
+    runtime::check(b200_token_feedback(next_.data<Index>(), batch_, static_cast<Index*>(ids_.mutable_data()),
+                                       static_cast<Index*>(history_.mutable_data()), max_steps_,
+                                       static_cast<int32_t*>(counter_.mutable_data()), stream), "token feedback");
+    for (auto& layer : *cache_) layer.commit(1);
+    ++generated_;
+    logits_current_ = true;
     runtime::check_cuda(cudaMemcpyAsync(staging + batch_, next_.raw_data(), sizeof(Index) * static_cast<std::size_t>(batch_),
                                         cudaMemcpyDeviceToHost, stream), "cudaMemcpyAsync");
     runtime::check_cuda(cudaStreamSynchronize(stream), "cudaStreamSynchronize");

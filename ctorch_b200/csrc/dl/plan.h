@@ -89,6 +89,10 @@ public:
     // One step driven from the host: ids_in [batch] host -> H2D, step, D2H -> ids_out [batch] host (the reference's
     // per-token host round trip, examples/decoder_generate.cpp:28-30).  ids_in may be NULL to continue from the device ids.
     void step_host(const Index* ids_in, Index* ids_out);
+    // One token drawn from softmax(logits / temperature) instead of the argmax, host in the loop: uniforms [batch] in
+    // [0, 1) come from the caller's generator (the reference example owns a std::mt19937, examples/text_generate.cpp:29),
+    // the chosen ids go to ids_out [batch] (may be NULL) and feed the next step.
+    void step_sampled(double temperature, const double* uniforms, Index* ids_out);
     Index generated() const { return generated_; }
     Tensor tokens() const;         // [batch, generated] int64 on the host (synchronises)
     // [batch, vocab] f32 on the device: logits the latest token was chosen from.  Steps choose their token without
@@ -112,7 +116,7 @@ private:
     Index batch_, max_steps_, generated_ = 0, launches_per_step_ = 0;
     bool fused_choice_ = false, logits_current_ = false;
     int device_ = 0;
-    Tensor ids_, next_, logits_, history_, counter_, x_;
+    Tensor ids_, next_, logits_, history_, counter_, x_, uniform_;
     std::shared_ptr<runtime::Storage> pinned_;
     cudaGraphExec_t graph_ = nullptr;
     std::uint64_t graph_version_ = ~0ull, graph_epoch_ = ~0ull;

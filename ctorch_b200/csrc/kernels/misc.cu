@@ -294,6 +294,85 @@ __global__ void __launch_bounds__(1024) argmax_finish_kernel(const float* best_v
     if (threadIdx.x == 0) *counter = step + 1;
 }
 
+// One CTA per row.  Thread t owns the contiguous slice [t * chunk, (t + 1) * chunk) of the row, so per-thread f64 sums
+// followed by a scan over the threads give running sums in index order.
+constexpr int kSampleThreads = 1024;
+__global__ void __launch_bounds__(kSampleThreads) sample_kernel(const float* x, int64_t width, float temperature, const double* uniform,
+                                                                int64_t* index) {
+    __shared__ float reduce_f[32];
+    __shared__ double reduce_d[32];
+    __shared__ double prefix[kSampleThreads];
+    __shared__ long long chosen;
+    grid_dependency_wait();
+    grid_launch_dependents();
+    const float* row = x + blockIdx.x * width;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int64_t chunk = (width + kSampleThreads - 1) / kSampleThreads;
+    const int64_t begin = min(width, threadIdx.x * chunk), end = min(width, begin + chunk);
+    // max of x / T
+    float m = -INFINITY;
+    for (int64_t c = begin; c < end; ++c) m = fmaxf(m, __fdiv_rn(row[c], temperature));
+    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    if (lane == 0) reduce_f[warp] = m;
+    __syncthreads();
+    m = reduce_f[lane];
+    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    // sum of exp(v - max): the softmax denominator (f32 terms, f64 sum)
+    double mine = 0.0;
+    for (int64_t c = begin; c < end; ++c) mine += static_cast<double>(expf(__fsub_rn(__fdiv_rn(row[c], temperature), m)));
+    double total = mine;
+    for (int o = 16; o > 0; o >>= 1) total += __shfl_xor_sync(0xffffffffu, total, o);
+    __syncthreads();
+    if (lane == 0) reduce_d[warp] = total;
+    __syncthreads();
+    total = 0.0;
+    for (int w = 0; w < kSampleThreads / 32; ++w) total += reduce_d[w];
+    const float denominator = static_cast<float>(total);
+    // probabilities p = e / denominator (f32), their f64 running sums per thread, scan over threads
+    double slice = 0.0;
+    for (int64_t c = begin; c < end; ++c) slice += static_cast<double>(__fdiv_rn(expf(__fsub_rn(__fdiv_rn(row[c], temperature), m)), denominator));
+    prefix[threadIdx.x] = slice;
+    if (threadIdx.x == 0) chosen = -1;
+    __syncthreads();
+    if (warp == 0) {   // exclusive scan of 1024 slices: each lane scans 32 consecutive entries, then the lanes
+        double run = 0.0;
+        for (int i = 0; i < 32; ++i) {
+            const double v = prefix[lane * 32 + i];
+            prefix[lane * 32 + i] = run;
+            run += v;
+        }
+        double before = run;
+        for (int o = 1; o < 32; o <<= 1) {
+            const double other = __shfl_up_sync(0xffffffffu, before, o);
+            if (lane >= o) before += other;
+        }
+        before -= run;
+        for (int i = 0; i < 32; ++i) prefix[lane * 32 + i] += before;
+        if (lane == 31) reduce_d[0] = before + run;   // sum of all p
+    }
+    __syncthreads();
+    const double target = uniform[blockIdx.x] * reduce_d[0];
+    const double start = prefix[threadIdx.x];
+    if (begin < end && start <= target && target < start + slice) {
+        double run = start;
+        long long found = end - 1;
+        for (int64_t c = begin; c < end; ++c) {
+            run += static_cast<double>(__fdiv_rn(expf(__fsub_rn(__fdiv_rn(row[c], temperature), m)), denominator));
+            if (run > target) { found = c; break; }
+        }
+        chosen = found;   // the slices are disjoint: at most one thread gets here
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        long long result = chosen;
+        if (result < 0) {   // u * total landed on or past the last boundary: the last index with a non-zero probability
+            result = width - 1;
+            while (result > 0 && expf(__fsub_rn(__fdiv_rn(row[result], temperature), m)) == 0.0f) --result;
+        }
+        index[blockIdx.x] = result;
+    }
+}
+
 unsigned blocks_for(int64_t n) { return static_cast<unsigned>((n + 255) / 256 < 8192 ? (n + 255) / 256 : 8192); }
 
 }  // namespace
@@ -316,6 +395,13 @@ int b200_argmax_finish(const float* best_value, const int32_t* best_index, int32
     const unsigned threads = rows >= 32 ? 1024 : static_cast<unsigned>(rows) * 32;
     return cuda_status(launch_dependent(b200::argmax_finish_kernel, dim3(1), dim3(threads), 0, as_stream(stream), best_value, best_index,
                                         static_cast<int>(parts), rows, next, ids, history, history_rows, counter), "argmax_finish_kernel launch");
+}
+
+int b200_sample(const float* x, int64_t rows, int64_t width, double temperature, const double* uniform, int64_t* index, void* stream) {
+    if (!x || !uniform || !index || rows < 0 || width <= 0 || !(temperature > 0.0)) { set_error("b200_sample: bad pointer, size or temperature"); return B200_BAD_ARGUMENT; }
+    if (rows == 0) return B200_OK;
+    return cuda_status(launch_dependent(b200::sample_kernel, dim3(static_cast<unsigned>(rows)), dim3(b200::kSampleThreads), 0, as_stream(stream),
+                                        x, width, static_cast<float>(temperature), uniform, index), "sample_kernel launch");
 }
 
 int b200_permute_0213(const float* in, int64_t a, int64_t b, int64_t c, int64_t d, float* out, void* stream) {

@@ -109,6 +109,10 @@ DL_API void dl_state_release(dl_state* state);
 DL_API size_t dl_state_size(const dl_state* state);
 DL_API const char* dl_state_name(const dl_state* state, size_t index);   /* borrowed from the state */
 DL_API dl_status dl_state_tensor(const dl_state* state, size_t index, dl_tensor** output);
+/* Weight archives (".ct") in the reference's byte layout (include/dl/c_api.h:647-648, src/io/checkpoint.cpp:52-114): files
+ * written by either library load in the other.  Loaded tensors live in host memory; dl_module_load_state moves them. */
+DL_API dl_status dl_state_save(const char* path, const dl_state* state);
+DL_API dl_status dl_state_load(const char* path, dl_state** output);
 DL_API dl_status dl_state_create(const char* const* names, const dl_tensor* const* tensors, size_t count,
     dl_state** output);
 
@@ -165,6 +169,11 @@ DL_API dl_status dl_generation_step(dl_generation* generation, int64_t steps);
  * NULL to continue from the device-resident ids) is copied to the device, one step runs, the chosen ids are
  * copied back into ids_out [batch] (host) and the call waits for them. */
 DL_API dl_status dl_generation_step_host(dl_generation* generation, const int64_t* ids_in, int64_t* ids_out);
+/* One token drawn from softmax(logits / temperature) (the sibling example's loop, examples/text_generate.cpp:37-41): the
+ * caller supplies one uniform variate in [0, 1) per sequence from its own generator; the draw is the inverse of the
+ * running sum in index order, as std::discrete_distribution does.  Host in the loop like dl_generation_step_host.
+ * No counterpart in the reference's C API (its example samples on the host). */
+DL_API dl_status dl_generation_step_sampled(dl_generation* generation, double temperature, const double* uniforms, int64_t* ids_out);
 /* Tokens generated so far, int64 [batch, count] on the host (waits for the device). */
 DL_API dl_status dl_generation_tokens(dl_generation* generation, dl_tensor** output);
 /* Logits [batch, vocab] (f32, device) the latest token was chosen from. */

@@ -216,6 +216,14 @@ B200_API int b200_attention_decode_static(const float* q, int64_t rows, int32_t 
  * first maximum wins, the first NaN wins over everything after it). */
 B200_API int b200_argmax(const float* x, int64_t rows, int64_t width, int64_t* index, void* stream);
 
+/* Temperature sampling of one index per row, the arithmetic of the reference's example loop
+ * (examples/text_generate.cpp:38-39): p = softmax(x / temperature) in f32 (max, exp(v - max), sum, divide:
+ * src/kernels/cpu/reduction.cpp:155-203), then the categorical draw of std::discrete_distribution for a uniform variate
+ * u in [0, 1): the first index whose running sum of p (f64, index order) exceeds u times the total.  `uniform` holds one
+ * u per row in device memory; the caller owns the random stream. */
+B200_API int b200_sample(const float* x, int64_t rows, int64_t width, double temperature, const double* uniform, int64_t* index,
+                         void* stream);
+
 /* Takes every `stride`-th row starting at `first` of a [rows_in, width] f32 matrix (Tensor::select of the last
  * position, examples/decoder_generate.cpp:27). */
 B200_API int b200_select_rows(const float* x, int64_t first, int64_t stride, int64_t rows_out, int64_t width,

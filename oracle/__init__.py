@@ -76,6 +76,7 @@ class CpuLib:
         f("argmax", None if kind == "port" else C.c_int, [fp, C.c_int64, C.c_int64, ip])
         if kind == "port":
             f("rope_tables", None, [C.c_int64, C.c_int64, C.c_double, fp, fp])
+            f("sample", None, [fp, C.c_int64, C.c_int64, C.c_double, C.POINTER(C.c_double), ip])
             f("linear", None, [fp, fp, C.c_int64, C.c_int64, C.c_int64, fp])
             f("rotary", None, [fp] + [C.c_int64] * 4 + [fp, fp, C.c_int64, fp])
             f("lora_linear", None, [fp, fp, fp, fp] + [C.c_int64] * 4 + [C.c_double, fp])
@@ -94,6 +95,10 @@ class CpuLib:
             f("rotary", C.c_int, [fp] + [C.c_int64] * 4 + [C.c_double, C.c_int64, C.c_int64, fp])
             f("lora_linear", C.c_int, [fp, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32] + [C.c_int64] * 4
               + [C.c_double, fp, C.c_void_p])
+            f("sample", C.c_int, [fp, C.c_int64, C.c_int64, C.c_double, C.POINTER(C.c_double), ip])
+            f("save_state", C.c_int, [C.c_void_p, C.c_char_p])
+            f("archive_size", C.c_int64, [C.c_char_p])
+            f("archive_entry", C.c_int, [C.c_char_p, C.c_int64, C.c_char_p, C.c_int64, ip, ip, C.POINTER(C.c_int32), C.c_void_p, C.c_int64])
 
     def _fn(self, name, restype, argtypes):
         fn = getattr(self.lib, self.prefix + name)
@@ -115,6 +120,26 @@ def lib(kind: str = "port") -> CpuLib:
     if kind not in _LIBS:
         _LIBS[kind] = CpuLib(kind)
     return _LIBS[kind]
+
+
+def reference_archive(path: str) -> list[tuple[str, tuple[int, ...], int, bytes]]:
+    """Entries (name, shape, dtype code, element bytes) of a weight archive as the reference's own dl::io::load reads it."""
+    l = lib("ref")
+    count = l.archive_size(path.encode())
+    if count < 0:
+        raise RuntimeError(l.error())
+    entries = []
+    for i in range(count):
+        name = C.create_string_buffer(512)
+        shape = (C.c_int64 * 8)()
+        rank, dtype = C.c_int64(), C.c_int32()
+        l.check(l.archive_entry(path.encode(), i, name, 512, shape, C.byref(rank), C.byref(dtype), None, 0))
+        dims = tuple(shape[d] for d in range(rank.value))
+        size = int(np.prod(dims, dtype=np.int64)) * (4, 8, 8, 1, 2, 2)[dtype.value]
+        data = C.create_string_buffer(max(1, size))
+        l.check(l.archive_entry(path.encode(), i, name, 512, shape, C.byref(rank), C.byref(dtype), data, size))
+        entries.append((name.value.decode(), dims, dtype.value, data.raw[:size]))
+    return entries
 
 
 def make_config(spec: dict) -> Config:
@@ -146,6 +171,10 @@ class CpuDecoder:
         if not self.handle:
             raise RuntimeError(self.l.error())
         self.cache = None
+
+    def save_state(self, path: str) -> None:
+        """Reference only: the model's weights written by the reference's dl::io::save."""
+        self.l.check(self.l.save_state(self.handle, path.encode()))
 
     def close(self):
         if self.cache:
@@ -311,6 +340,19 @@ def argmax(x, kind: str = "port") -> np.ndarray:
     x = np.ascontiguousarray(x, dtype=np.float32)
     index = np.empty(x.shape[:-1], dtype=np.int64)
     status = l.argmax(_ptr(x), x.size // x.shape[-1], x.shape[-1], _ptr(index, C.c_int64))
+    if kind != "port":
+        l.check(status)
+    return index
+
+
+def sample(x, temperature: float, uniforms, kind: str = "port") -> np.ndarray:
+    """One index per row drawn from softmax(x / temperature) with the given uniform variates (multiples of 2**-53 for
+    the reference, whose std::discrete_distribution is fed through a fixed-output generator)."""
+    l = lib(kind)
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    u = np.ascontiguousarray(uniforms, dtype=np.float64)
+    index = np.empty(x.shape[0], dtype=np.int64)
+    status = l.sample(_ptr(x), x.shape[0], x.shape[1], float(temperature), _ptr(u, C.c_double), _ptr(index, C.c_int64))
     if kind != "port":
         l.check(status)
     return index

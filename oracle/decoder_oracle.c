@@ -281,6 +281,44 @@ void oracle_argmax(const float* x, int64_t rows, int64_t width, int64_t* index) 
     }
 }
 
+/* Temperature sampling of the sibling example (examples/text_generate.cpp:38-39): softmax(logits / temperature) with the
+ * f32 softmax of src/kernels/cpu/reduction.cpp:155-203 (max, expf(v - max), running f32 sum in index order, divide), then
+ * the categorical draw of std::discrete_distribution as libstdc++ documents it: probabilities normalised by their sum in
+ * double, running sums with the last forced to one, and the first running sum greater than the uniform variate u
+ * (std::upper_bound).  The caller supplies u in [0, 1), one per row. */
+void oracle_sample(const float* x, int64_t rows, int64_t width, double temperature, const double* uniform, int64_t* index) {
+    float* p = (float*)malloc(sizeof(float) * (size_t)width);
+    const float t = (float)temperature;
+    for (int64_t r = 0; r < rows; ++r) {
+        const float* row = x + r * width;
+        float maximum = -INFINITY;
+        for (int64_t i = 0; i < width; ++i) {
+            const float v = row[i] / t;
+            p[i] = v;
+            maximum = isnan(v) ? v : (maximum < v ? v : maximum);
+        }
+        float total = 0.0f;
+        for (int64_t i = 0; i < width; ++i) {
+            p[i] = expf(p[i] - maximum);
+            total += p[i];
+        }
+        double sum = 0.0;
+        for (int64_t i = 0; i < width; ++i) {
+            p[i] /= total;
+            sum += (double)p[i];
+        }
+        double running = 0.0;
+        int64_t chosen = width - 1;
+        for (int64_t i = 0; i < width; ++i) {
+            running += (double)p[i] / sum;
+            const double boundary = i == width - 1 ? 1.0 : running;
+            if (boundary > uniform[r]) { chosen = i; break; }
+        }
+        index[r] = chosen;
+    }
+    free(p);
+}
+
 /* LoRALinear::forward (src/nn/decoder.cpp:26-28): base(x) + up(down(x)) * f32(alpha/rank). */
 void oracle_lora_linear(const float* x, const float* w, const float* down, const float* up, int64_t rows,
                         int64_t in, int64_t out, int64_t rank, double alpha, float* y) {

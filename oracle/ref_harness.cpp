@@ -13,7 +13,9 @@
 #include <cstdint>
 #include <cstdio>
 #include <cstring>
+#include <cmath>
 #include <memory>
+#include <random>
 #include <string>
 #include <barrier>
 #include <chrono>
@@ -49,6 +51,16 @@ dl::DType dtype_of_code(int32_t code) { return code == 5 ? dl::DType::bf16 : dl:
 dl::Tensor host_tensor(const void* data, dl::Shape shape, dl::DType dtype) {
     return dl::detail::from_host(data, std::move(shape), dtype, false, dl::Device::cpu());
 }
+
+// A "generator" whose every draw makes std::generate_canonical<double, 53> return a chosen u = k / 2^53: with a 64-bit
+// range libstdc++ takes one draw v and returns double(v) / 2^64.
+struct FixedBits {
+    using result_type = std::uint64_t;
+    double u;
+    static constexpr result_type min() { return 0; }
+    static constexpr result_type max() { return ~static_cast<result_type>(0); }
+    result_type operator()() const { return static_cast<result_type>(std::ldexp(u, 53)) << 11; }
+};
 
 struct Model {
     Config cfg;
@@ -363,6 +375,54 @@ int ref_lora_linear(const float* x, const void* w, const void* down, const void*
         if (merged) {
             auto weight = adapter.merged()->weight().contiguous();
             std::memcpy(merged, weight.data<char>(), dl::element_size(dtype) * static_cast<std::size_t>(weight.numel()));
+        }
+    });
+}
+
+// Weight archive written by the reference's own dl::io::save (src/io/checkpoint.cpp:97-104): "tokens.weight" and the
+// decoder's state under "decoder.", the names of examples/decoder_model.h.  ref_archive_entry reads one back through
+// dl::io::load: shape (up to 8 extents), dtype code, and the first `capacity` bytes of the elements.
+int ref_save_state(void* handle, const char* path) {
+    return guarded([&] {
+        auto& model = *static_cast<Model*>(handle);
+        dl::StateDict state;
+        for (auto& [name, tensor] : model.tokens->state_dict()) state.emplace_back("tokens." + name, tensor);
+        for (auto& [name, tensor] : model.decoder->state_dict()) state.emplace_back("decoder." + name, tensor);
+        dl::io::save(path, state);
+    });
+}
+
+int64_t ref_archive_size(const char* path) {
+    int64_t count = -1;
+    guarded([&] { count = static_cast<int64_t>(dl::io::load(path).size()); });
+    return count;
+}
+
+int ref_archive_entry(const char* path, int64_t index, char* name, int64_t name_capacity, int64_t* shape8, int64_t* rank,
+                      int32_t* dtype, void* bytes, int64_t capacity) {
+    return guarded([&] {
+        const auto state = dl::io::load(path);
+        const auto& [entry_name, tensor] = state.at(static_cast<std::size_t>(index));
+        std::snprintf(name, static_cast<std::size_t>(name_capacity), "%s", entry_name.c_str());
+        *rank = tensor.ndim();
+        for (int64_t i = 0; i < tensor.ndim() && i < 8; ++i) shape8[i] = tensor.shape()[static_cast<std::size_t>(i)];
+        *dtype = static_cast<int32_t>(tensor.dtype());
+        const auto dense = tensor.contiguous();
+        const auto total = static_cast<int64_t>(dense.numel()) * static_cast<int64_t>(dl::element_size(dense.dtype()));
+        std::memcpy(bytes, dense.data<char>(), static_cast<std::size_t>(std::min(total, capacity)));
+    });
+}
+
+// The sampling lines of examples/text_generate.cpp:38-39 on the reference library: softmax(logits / temperature), then
+// std::discrete_distribution driven by a generator that yields the caller's uniform variate (a multiple of 2^-53).
+int ref_sample(const float* x, int64_t rows, int64_t width, double temperature, const double* uniform, int64_t* index) {
+    return guarded([&] {
+        dl::NoGradGuard inference;
+        for (int64_t r = 0; r < rows; ++r) {
+            auto logits = host_tensor(x + r * width, {width}, dl::DType::f32);
+            auto probabilities = dl::softmax(logits / temperature, 0).to_vector<float>();
+            FixedBits bits{uniform[r]};
+            index[r] = std::discrete_distribution<int>(probabilities.begin(), probabilities.end())(bits);
         }
     });
 }

@@ -39,3 +39,22 @@ def attention_inputs(case):
 def token_stream(spec, chunks, seed=5):
     rng = np.random.default_rng([seed, sum(chunks)])
     return rng.integers(0, spec["vocab"], size=(spec["batch"], sum(chunks)), dtype=np.int64)
+
+
+def archive_cases():
+    """name -> spec of the decoders whose weights the reference writes to tests/golden/<name>.ct (a few KB each)."""
+    micro = dict(vocab=19, d_model=16, layers=2, heads=4, kv_heads=2, hidden=24, batch=2, prompt=3, steps=2, context=8, tied=True,
+                 eps=1e-5, rope_base=10000.0)
+    return {"micro_f32": dict(micro, dtype="f32"), "micro_bf16": dict(micro, dtype="bf16")}
+
+
+def sampling_case():
+    """(logits [rows, width] f32, temperature, uniforms [rows] as multiples of 2**-53): peaked and flat rows, variates at
+    both ends of the unit interval."""
+    import numpy as np
+    rng = np.random.default_rng(2024)
+    rows, width = 24, 517
+    logits = (rng.standard_normal((rows, width)) * rng.uniform(0.5, 6.0, size=(rows, 1))).astype(np.float32)
+    uniforms = np.floor(rng.uniform(0, 1, rows) * 2.0 ** 53) / 2.0 ** 53
+    uniforms[0], uniforms[1], uniforms[2] = 0.0, 1.0 - 2.0 ** -53, 0.5
+    return logits, 0.8, uniforms

@@ -1,4 +1,4 @@
-"""Regenerates tests/golden/decoder_golden.npz by running the seeded cases of cases.py on the UNMODIFIED
+"""Regenerates tests/golden/decoder_golden.npz and the weight archives tests/golden/*.ct by running the seeded cases of cases.py on the UNMODIFIED
 reference CPU library (oracle/_ref, built by `make -C oracle ref` where the reference tree is present).
 
     python tests/golden/make_golden.py
@@ -16,7 +16,7 @@ sys.path.insert(0, ROOT)
 sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
 
 import oracle  # noqa: E402
-from cases import attention_cases, attention_inputs, decoder_cases, token_stream  # noqa: E402
+from cases import sampling_case, archive_cases, attention_cases, attention_inputs, decoder_cases, token_stream  # noqa: E402
 from ctorch_b200 import workloads as W  # noqa: E402
 
 
@@ -54,6 +54,13 @@ def main():
         out[f"lora/{dt}/y"] = y
         out[f"lora/{dt}/merged"] = merged
         out[f"linear/{dt}"] = oracle.linear(xl, w, kind="ref")
+    logits, temperature, uniforms = sampling_case()
+    out["sample/index"] = oracle.sample(logits, temperature, uniforms, kind="ref")
+    here = os.path.dirname(os.path.abspath(__file__))
+    for name, spec in archive_cases().items():   # weight archives written by the reference's dl::io::save
+        model = oracle.CpuDecoder(spec, W.make_weights(spec, seed=77), kind="ref")
+        model.save_state(os.path.join(here, name + ".ct"))
+        model.close()
     np.savez_compressed(os.path.join(os.path.dirname(os.path.abspath(__file__)), "decoder_golden.npz"), **out)
     print("wrote", len(out), "arrays")
 

@@ -263,3 +263,29 @@ def test_generate_full_context_round_trip_properties():
     assert np.array_equal(gen.tokens(), first)
     assert np.array_equal(out, first[:, -1])
     assert gen.launches_per_step() > 0
+
+
+def test_sampled_steps_follow_the_oracle_draws():
+    """Temperature sampling with the host in the loop: the ids drawn from each step's logits equal the oracle's draw from
+    the same logits and variates, feed the next step, and land in the token history."""
+    spec = W.tiny("f32", batch=3, steps=6)
+    weights = W.make_weights(spec, seed=21, scale=0.3)
+    model = B.DecoderModel(spec, weights)
+    prompt = W.make_prompts(spec, seed=22)
+    gen = B.Generation(model, 3, spec["steps"])
+    gen.prefill(prompt)
+    cpu = oracle.CpuDecoder(spec, weights)
+    cpu.decode_ids(prompt)
+    rng = np.random.default_rng(23)
+    fed = gen.tokens()[:, -1]
+    for step in range(spec["steps"] - 1):
+        uniforms = rng.uniform(0, 1, 3)
+        ids = gen.step_sampled(0.9, uniforms)
+        logits = gen.logits()
+        want_logits = cpu.decode_ids(fed.reshape(3, 1))[:, 0]
+        assert rel(logits, want_logits) < F32_TOL
+        assert np.array_equal(ids, oracle.sample(logits, 0.9, uniforms))
+        fed = ids
+    assert np.array_equal(gen.tokens()[:, -1], fed) and model.cache_length() == spec["prompt"] + spec["steps"] - 1
+    with pytest.raises(B.B200Error, match="temperature"):
+        gen.step_sampled(0.0, np.zeros(3))

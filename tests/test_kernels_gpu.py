@@ -493,3 +493,31 @@ def test_fused_logits_argmax(rows, inner, vocab):
     assert np.array_equal(got[~near_tie], want[~near_tie])
     assert np.array_equal(ids.cpu().numpy(), got) and np.array_equal(history.cpu().numpy()[1], got)
     assert int(counter.item()) == 2
+
+
+@pytest.mark.parametrize("rows,width,temperature", [(16, 32000, 0.8), (3, 517, 1.5), (40, 1000, 0.3)])
+def test_temperature_sampling(rows, width, temperature):
+    """Draws must equal the oracle's (softmax + running-sum inverse) unless the variate lies within 1e-6 of a boundary of
+    the running sums, where the summation order of the two may legitimately disagree."""
+    l = B.lib()
+    rng = np.random.default_rng(rows + width)
+    logits = (rng.standard_normal((rows, width)) * rng.uniform(0.5, 5.0, size=(rows, 1))).astype(np.float32)
+    uniforms = rng.uniform(0, 1, rows)
+    uniforms[0] = 0.0
+    uniforms[-1] = 1.0 - 2.0 ** -53
+    xd = dev(logits)
+    ud = torch.from_numpy(uniforms).cuda()
+    index = torch.full((rows,), -1, dtype=torch.int64, device="cuda")
+    torch.cuda.synchronize()
+    B.kcheck(l.b200_sample(xd.data_ptr(), rows, width, temperature, ud.data_ptr(), index.data_ptr(), stream()))
+    sync()
+    got = index.cpu().numpy()
+    want = oracle.sample(logits, temperature, uniforms)
+    scaled = logits / np.float32(temperature)
+    p = np.exp(scaled - scaled.max(axis=1, keepdims=True)).astype(np.float64)
+    running = np.cumsum(p / p.sum(axis=1, keepdims=True), axis=1)
+    for r in range(rows):
+        if got[r] != want[r]:
+            lo, hi = sorted((got[r], want[r]))
+            assert hi - lo == 1 and abs(running[r, lo] - uniforms[r]) < 1e-6, (r, got[r], want[r])
+    assert (got >= 0).all() and (got < width).all()

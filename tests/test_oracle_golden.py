@@ -9,7 +9,7 @@ import pytest
 sys.path.insert(0, os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden"))
 
 import oracle
-from cases import attention_cases, attention_inputs, decoder_cases, token_stream
+from cases import attention_cases, attention_inputs, decoder_cases, sampling_case, token_stream
 from ctorch_b200 import workloads as W
 
 GOLDEN = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "decoder_golden.npz"))
@@ -97,3 +97,10 @@ def test_cache_errors_and_rollback():
 def test_argmax_rules():
     x = np.array([[1.0, 3.0, 3.0, 2.0], [0.0, np.nan, 5.0, np.nan], [-1.0, -1.0, -1.0, -1.0]], dtype=np.float32)
     assert oracle.argmax(x).tolist() == [1, 1, 0]
+
+
+def test_temperature_sampling_matches_reference_draws():
+    """softmax(logits / T) + std::discrete_distribution of the reference example (examples/text_generate.cpp:38-39), answered
+    by the reference library with a generator that yields the given uniform variates."""
+    logits, temperature, uniforms = sampling_case()
+    assert np.array_equal(oracle.sample(logits, temperature, uniforms), GOLDEN["sample/index"])

@@ -58,3 +58,11 @@ def test_threaded_baseline_matches_serial():
     prompt = W.make_prompts(spec)
     serial, _ = model.generate(prompt, 4)
     assert np.array_equal(model.generate_threads(prompt, 4, 4), serial)
+
+
+def test_sampling_port_equals_reference_on_fresh_inputs():
+    rng = np.random.default_rng(8)
+    logits = (rng.standard_normal((40, 1031)) * rng.uniform(0.2, 8.0, size=(40, 1))).astype(np.float32)
+    uniforms = np.floor(rng.uniform(0, 1, 40) * 2.0 ** 53) / 2.0 ** 53
+    for temperature in (0.5, 1.0, 1.7):
+        assert np.array_equal(oracle.sample(logits, temperature, uniforms), oracle.sample(logits, temperature, uniforms, kind="ref"))
