@@ -42,6 +42,15 @@ def measured_peaks() -> tuple[float, str]:
         return 6650.0, "fallback"
 
 
+def tensor_peak_tflops() -> float:
+    """Measured dense bf16 burst throughput of this pool's B200s (a kernel timed alone), else the stated fallback."""
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as handle:
+            return float(json.load(handle)["bf16_tflops"])
+    except Exception:  # noqa: BLE001
+        return 1590.0
+
+
 class ClockSampler:
     """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
 
@@ -352,21 +361,120 @@ def run_c3(args) -> dict:
     return line if rank == 0 else {}
 
 
+def run_linear(args) -> dict:
+    """One shadow linear in isolation (`--rows R --inner K --out N --epilogue store|residual|swiglu`): the skinny streaming
+    kernel for up to 16 rows, the tcgen05 kernel above.  A step is one launch; the weights rotate through copies that
+    together exceed L2, as they do inside a decode step of a model larger than L2."""
+    import ctypes as C
+
+    import torch
+
+    import ctorch_b200 as B
+    rank, world, local, dist = distributed()
+    rows, inner, out = args.rows, args.inner, args.out
+    epilogue = {"store": 0, "residual": 1, "swiglu": 2}[args.epilogue]
+    l = B.lib()
+    torch.cuda.set_device(local)
+    stream = l.dl_b200_stream(B.cuda(local))
+    generator = torch.Generator(device="cuda").manual_seed(5 + rank)
+    copies = max(2, int(300e6 // (inner * out * 2)) + 1)
+    weights = [(0.05 * torch.randn((out, inner), device="cuda", generator=generator)).to(torch.bfloat16) for _ in range(copies)]
+    x = torch.randn((rows, inner), device="cuda", generator=generator)
+    hi = torch.zeros((rows, inner), dtype=torch.bfloat16, device="cuda")
+    lo = torch.zeros_like(hi)
+    sq = torch.zeros((1, rows), device="cuda")
+    torch.cuda.synchronize()   # torch filled these on its own stream; the library works on another
+    B.kcheck(l.b200_shadow_from_rows(x.data_ptr(), rows, inner, None, 0, hi.data_ptr(), lo.data_ptr(), sq.data_ptr(), stream))
+    columns = out // 2 if epilogue == 2 else out
+    y = torch.zeros((rows, columns), device="cuda")
+    residual = torch.zeros((rows, out), device="cuda")
+    out_hi = torch.zeros((rows, columns), dtype=torch.bfloat16, device="cuda")
+    out_lo = torch.zeros_like(out_hi)
+    parts = l.b200_linear_shadow_parts(rows, inner, out)
+    sums = torch.zeros((max(parts, 1), rows), device="cuda")
+    torch.cuda.synchronize()
+
+    def step(i):
+        a = B.ShadowLinearArgs(hi.data_ptr(), lo.data_ptr(), rows, inner, weights[i % copies].data_ptr(), out, sq.data_ptr(), 1, 1e-5,
+                               epilogue, residual.data_ptr() if epilogue == 1 else None, None, y.data_ptr(),
+                               out_hi.data_ptr() if epilogue else None, out_lo.data_ptr() if epilogue else None, None, 0,
+                               sums.data_ptr() if epilogue == 1 else None, None, None)
+        B.kcheck(l.b200_linear_shadow(C.byref(a), stream))
+
+    # One CUDA graph holds one launch per weight copy (as a decode step holds its launches in a graph: no host work per
+    # launch); a timed step is one launch, so K steps are ceil(K / copies) replays.
+    for i in range(min(args.warmup, copies)):
+        step(i)
+    B.synchronize(local)
+    side = torch.cuda.ExternalStream(stream, device=torch.device("cuda", local))
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, stream=side):
+        for i in range(copies):
+            step(i)
+    replays = (args.steps + copies - 1) // copies
+    launches = replays * copies
+    sampler = ClockSampler(local)
+    sampler.start()
+    with torch.cuda.stream(side):   # replays go to the library's stream, where the timer's events are recorded
+        graph.replay()
+        B.synchronize(local)
+        barrier(dist, local)
+        B.timer_start(local)
+        for _ in range(replays):
+            graph.replay()
+        elapsed = B.timer_stop(local)
+    ms = max_over_ranks(elapsed, dist, local) * args.steps / launches   # scaled to K launches
+    clocks = sampler.stop()
+    status = C.c_int32()
+    B.kcheck(l.b200_take_device_status(local, stream, C.byref(status)))
+    want = x @ weights[copies - 1].float().T * torch.rsqrt((x * x).mean(dim=1, keepdim=True) + 1e-5)
+    if epilogue == 2:
+        want = torch.nn.functional.silu(want[:, 0::2]) * want[:, 1::2]
+    error = float((y - want).abs().max() / want.abs().max())
+    assert status.value == 0 and error < 1e-3, (status.value, error, float(y.abs().max()), float(want.abs().max()))
+    seconds = ms / args.steps / 1000.0
+    weight_bytes = inner * out * 2
+    flops = 2.0 * rows * inner * out
+    peak, peak_kind = measured_peaks()
+    hbm_bound = rows <= 512   # arithmetic intensity rows flop/B against a ridge of ~220: decode batches stream weights
+    tensor_peak = tensor_peak_tflops()
+    roofline = ({"bound": "hbm", "achieved": weight_bytes / seconds / 1e9, "peak": peak, "unit": "GB/s", "peak_kind": peak_kind,
+                 "algorithmic_bytes": weight_bytes}
+                if hbm_bound else
+                {"bound": "tensor", "achieved": flops / seconds / 1e12, "peak": tensor_peak, "unit": "TFLOP/s", "peak_kind": "measured burst",
+                 "algorithmic_flops": flops, "note": "useful flops; the kernel issues twice as many (activation hi + lo planes)"})
+    roofline.update(frac=roofline["achieved"] / roofline["peak"], traffic=None,
+                    kernel="linear_stream_kernel" if rows <= 16 and inner <= 2048 else "linear_gemm_kernel", launch_ms=ms / args.steps)
+    line = {"metric": "linear_rows_per_s", "value": world * rows / seconds, "unit": "rows/s", "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "bf16 weights, f32 activations as bf16 hi+lo, f32 accumulate", "data": "synthetic",
+            "config": {"workload": f"linear microbench rows {rows} in {inner} out {out} {args.epilogue}", "copies": copies,
+                       "l2": "weights rotate through %d copies (%.0f MB) > L2" % (copies, copies * weight_bytes / 1e6), "max_rel_error": error},
+            "clocks": clocks, "gpu_launches": args.steps, "roofline": roofline}
+    if dist is not None:
+        dist.destroy_process_group()
+    return line if rank == 0 else {}
+
+
 def main():
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
     parser.add_argument("--steps", type=int, default=64)
     parser.add_argument("--warmup", type=int, default=8)
     parser.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    parser.add_argument("--workload", default="c2", choices=["c1", "c2", "c3", "c4", "c5"])
+    parser.add_argument("--workload", default="c2", choices=["c1", "c2", "c3", "c4", "c5", "linear"])
+    parser.add_argument("--rows", type=int, default=16, help="linear only")
+    parser.add_argument("--inner", type=int, default=768, help="linear only")
+    parser.add_argument("--out", type=int, default=32000, help="linear only")
+    parser.add_argument("--epilogue", default="store", choices=["store", "residual", "swiglu"], help="linear only")
     parser.add_argument("--cpu-steps", type=int, default=24, help="timed CPU-baseline steps of the default run")
     parser.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     parser.add_argument("--small", action="store_true", help="c3 only: batch 16, contexts up to 8192 (profiler captures)")
     args = parser.parse_args()
     if args.warmup < 3:
         args.warmup = 3
-    if args.workload == "c3":
-        line = run_c3(args)
+    if args.workload in ("c3", "linear"):
+        line = run_c3(args) if args.workload == "c3" else run_linear(args)
         if line:
             print(json.dumps(line))
         return

@@ -184,6 +184,17 @@ __device__ __forceinline__ uint32_t cluster_cta_rank() {
     asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
     return rank;
 }
+__device__ __forceinline__ uint32_t map_peer_shared(uint32_t local_address, uint32_t peer_rank) {
+    uint32_t remote;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_address), "r"(peer_rank));
+    return remote;
+}
+// Not volatile: the cluster barrier orders these loads against the peers' stores, and independent loads should overlap.
+__device__ __forceinline__ float2 load_cluster_float2(uint32_t cluster_address) {
+    float2 value;
+    asm("ld.shared::cluster.v2.f32 {%0, %1}, [%2];" : "=f"(value.x), "=f"(value.y) : "r"(cluster_address));
+    return value;
+}
 __device__ __forceinline__ float load_peer_shared(uint32_t local_address, uint32_t peer_rank) {
     uint32_t remote;
     float value;

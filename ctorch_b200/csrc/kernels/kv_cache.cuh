@@ -16,7 +16,7 @@ struct KvView {
 };
 
 __device__ __forceinline__ int64_t kv_offset(const KvView& kv, int sequence, int position, int head) {
-    const int page = kv.page_table[static_cast<int64_t>(sequence) * kv.pages_per_seq + position / kv.page_size];
+    const int page = __ldg(kv.page_table + static_cast<int64_t>(sequence) * kv.pages_per_seq + position / kv.page_size);
     const int slot = position % kv.page_size;
     return ((static_cast<int64_t>(page) * kv.kv_heads + head) * kv.page_size + slot) * kv.head_dim;
 }

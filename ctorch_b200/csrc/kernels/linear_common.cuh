@@ -80,7 +80,7 @@ __device__ __forceinline__ void linear_epilogue(const LinearParams& p, int row, 
     } else {
         const int D = p.heads * p.head_dim, KV = p.kv_heads * p.head_dim;
         const int sequence = row / p.tokens_per_sequence;
-        const int position = p.kv.lengths[sequence] + row % p.tokens_per_sequence;
+        const int position = __ldg(p.kv.lengths + sequence) + row % p.tokens_per_sequence;
         int region = 0, local = feature0;  // 0 = q, 1 = k, 2 = v
         if (local >= D) { region = 1; local -= D; }
         if (region == 1 && local >= KV) { region = 2; local -= KV; }
@@ -95,8 +95,9 @@ __device__ __forceinline__ void linear_epilogue(const LinearParams& p, int row, 
                                                            : load_as_f32(static_cast<const float*>(up), at);
                 const float ub = p.weight_dtype == B200_BF16 ? load_as_f32(static_cast<const __nv_bfloat16*>(up), at + p.lora_rank)
                                                            : load_as_f32(static_cast<const float*>(up), at + p.lora_rank);
-                da = __fadd_rn(da, __fmul_rn(low[j], ua));
-                db = __fadd_rn(db, __fmul_rn(low[j], ub));
+                const float lj = __ldg(low + j);
+                da = __fadd_rn(da, __fmul_rn(lj, ua));
+                db = __fadd_rn(db, __fmul_rn(lj, ub));
             }
             a = __fadd_rn(a, __fmul_rn(da, p.lora_scale));
             b = __fadd_rn(b, __fmul_rn(db, p.lora_scale));
@@ -104,8 +105,8 @@ __device__ __forceinline__ void linear_epilogue(const LinearParams& p, int row, 
         const int head = local / p.head_dim, d = local % p.head_dim;
         if (region != 2 && position < p.context) {
             // adjacent-pair rotation, each product rounded before the add (src/ops/contraction.cpp:44-49)
-            const float c = p.cosine[static_cast<int64_t>(position) * (p.head_dim >> 1) + (d >> 1)];
-            const float s = p.sine[static_cast<int64_t>(position) * (p.head_dim >> 1) + (d >> 1)];
+            const float c = __ldg(p.cosine + static_cast<int64_t>(position) * (p.head_dim >> 1) + (d >> 1));
+            const float s = __ldg(p.sine + static_cast<int64_t>(position) * (p.head_dim >> 1) + (d >> 1));
             const float even = a, odd = b;
             a = __fsub_rn(__fmul_rn(even, c), __fmul_rn(odd, s));
             b = __fadd_rn(__fmul_rn(even, s), __fmul_rn(odd, c));

@@ -9,14 +9,15 @@
 //               D += x_hi.W and D += x_lo.W for the four K slices of a block, then tcgen05.commit releases the
 //               stage; a last commit publishes the accumulator
 //   warps 2-5   epilogue: tcgen05.ld (32 lanes x 32 columns per instruction) brings each warp's quarter of the
-//               accumulator to registers, one token row per thread; rows are scaled by the split RMSNorm factor and
-//               finished by the shared epilogue (store | residual | SiLU(gate)*up | q|k|v + RoPE + KV append), with
+//               accumulator to registers, one token row per thread, and from there to a row-major tile in shared
+//               memory; the warps then walk the rows with their lanes across the features, so every global access is
+//               coalesced; rows are scaled by the split RMSNorm factor and finished by the shared epilogue (store | residual | SiLU(gate)*up | q|k|v + RoPE + KV append), with
 //               the optional output shadow and its per-row sums of squares.
 // Few tiles (decode batches of 17..256 rows against a narrow projection) leave most SMs idle and the launch far from
 // the HBM rate, so such launches split K over a thread-block cluster of up to 8 CTAs (grid z): every CTA accumulates
-// its K range in its own tensor memory, dumps the f32 partial tile to its shared memory (the operand ring is free by
-// then), and after a cluster barrier each CTA sums one column slice of the tile over all peers (distributed shared
-// memory, fixed order z = 0..S-1, so results do not depend on timing) and runs the epilogue on that slice.
+// its K range in its own tensor memory, copies the f32 partial tile to its shared memory (the operand ring is free by
+// then), and after a cluster barrier each CTA sums a band of rows of the tile over all peers (distributed shared
+// memory, fixed order z = 0..S-1, so results do not depend on timing) and runs the epilogue on that band.
 // Reference arithmetic replaced: src/ops/matmul.cpp:35-67 -> src/kernels/cpu/matmul.h:10-22 for rows = batch * length.
 #include "linear_common.cuh"
 
@@ -24,13 +25,20 @@ namespace b200 {
 namespace {
 
 constexpr int kTileM = 128;   // tokens
-constexpr int kTileN = 128;   // features
+// features per tile: 128 or 256 (template parameter TN).  The wide tile halves the activation bytes a CTA pulls from L2
+// per weight byte, which is what bounds this kernel once the weights stream at HBM rate.
 constexpr int kBlockK = 64;   // bf16 columns per stage: one 128-byte swizzle row
-constexpr int kStages = 4;
-constexpr int kBoxBytes = kTileM * kBlockK * 2;  // 16 KB, same for the three operands
-constexpr int kStageBytes = 3 * kBoxBytes;
+constexpr int kBoxBytes = kTileM * kBlockK * 2;  // 16 KB: one activation plane of a K block
+template <int TN, int STAGES> struct GemmShape {
+    static constexpr int stages = STAGES;
+    static constexpr int weight_bytes = TN * kBlockK * 2;
+    static constexpr int stage_bytes = 2 * kBoxBytes + weight_bytes;   // x_hi, x_lo, W: 48 KB or 64 KB
+    static constexpr int smem = stages * stage_bytes + 1024 + 1024;   // alignment slack; barriers, TMEM slot, 128 row scales
+    // Instruction descriptor: f32 accumulator, bf16 x bf16, both K-major, N = TN, M = 128.
+    static constexpr uint32_t instruction = (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(TN >> 3) << 17)
+                                            | (static_cast<uint32_t>(kTileM >> 4) << 24);
+};
 constexpr int kGemmThreads = 192;
-constexpr int kGemmSmem = kStages * kStageBytes + 1024 + 256;
 
 struct GemmParams {
     LinearParams base;
@@ -78,15 +86,26 @@ __device__ __forceinline__ uint64_t operand_descriptor(uint32_t smem_address) {
     d |= static_cast<uint64_t>(2) << 61;                          // 128-byte swizzle
     return d;
 }
-// Instruction descriptor: f32 accumulator, bf16 x bf16, both K-major, N = 128, M = 128.
-constexpr uint32_t kInstruction = (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(kTileN >> 3) << 17)
-                                  | (static_cast<uint32_t>(kTileM >> 4) << 24);
 
 // One finished pair of adjacent features of one token row: shared epilogue, then the optional output shadow (hi + lo of
 // the value times the next norm weight) and the running sum of squares of the new residual stream.
+// `carried` holds the residual values of the pair (B200_EPI_RESIDUAL only), loaded ahead by the caller.
 template <int EPI>
-__device__ __forceinline__ void finish_pair(const LinearParams& p, int row, int feature0, float a, float b, float& squares) {
-    linear_epilogue<EPI>(p, row, feature0, a, b);
+__device__ __forceinline__ void finish_pair(const LinearParams& p, int row, int feature0, float a, float b, float2 carried, float& squares) {
+    if constexpr (EPI == B200_EPI_RESIDUAL) {
+        const bool second = feature0 + 1 < p.out;
+        const int64_t at = static_cast<int64_t>(row) * p.out + feature0;
+        a = __fadd_rn(carried.x, a);
+        b = second ? __fadd_rn(carried.y, b) : 0.0f;
+        if ((p.out & 1) == 0) {
+            *reinterpret_cast<float2*>(p.y + at) = make_float2(a, b);
+        } else {
+            p.y[at] = a;
+            if (second) p.y[at + 1] = b;
+        }
+    } else {
+        linear_epilogue<EPI>(p, row, feature0, a, b);
+    }
     if constexpr (EPI == B200_EPI_RESIDUAL) {
         const bool second = feature0 + 1 < p.out;
         squares += a * a + (second ? b * b : 0.0f);
@@ -121,10 +140,13 @@ __device__ __forceinline__ void finish_pair(const LinearParams& p, int row, int 
     }
 }
 
-template <int EPI>
-__global__ void __launch_bounds__(kGemmThreads, 1) linear_gemm_kernel(const __grid_constant__ CUtensorMap map_hi,
+template <int EPI, int TN, int STAGES>
+__global__ void __launch_bounds__(kGemmThreads, STAGES == 2 && TN == 128 ? 2 : 1) linear_gemm_kernel(const __grid_constant__ CUtensorMap map_hi,
                                                                       const __grid_constant__ CUtensorMap map_lo,
                                                                       const __grid_constant__ CUtensorMap map_w, const GemmParams gp) {
+    using S = GemmShape<TN, STAGES>;
+    constexpr int kStages = S::stages, kStageBytes = S::stage_bytes, kTileN = TN;
+    constexpr uint32_t kInstruction = S::instruction;
     const LinearParams& p = gp.base;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
@@ -200,97 +222,141 @@ __global__ void __launch_bounds__(kGemmThreads, 1) linear_gemm_kernel(const __gr
         }
     }
 
-    // ---- epilogue warps 2-5: warp w may touch TMEM lanes 32 * (w % 4) .. + 31; thread = one token row ----
+    // ---- epilogue, warps 2-5 ----
+    // (1) Each warp may touch TMEM lanes 32 * (warp % 4) .. + 31: thread = one token row copies its accumulators to a
+    //     row-major f32 tile in shared memory (the drained operand ring; rows padded by 4 floats so that the 16-byte
+    //     stores of a quarter warp hit distinct banks).
+    // (2) With a K split, a cluster barrier publishes every CTA's partial tile.
+    // (3) The rows of the tile are divided over the cluster's CTAs and over the four warps; a warp finishes one row
+    //     at a time with its lanes across the feature pairs, so the sums over the peers' tiles (distributed shared
+    //     memory, fixed order) and every global access of the epilogue (residual, result, shadows, cache) are
+    //     coalesced.  Per-row reductions (sum of squares, argmax candidate) are butterflies.
+    constexpr int kTileStride = kTileN + 4;
+    float* tile = reinterpret_cast<float*>(smem);
+    float* row_scale = reinterpret_cast<float*>(smem + kStages * kStageBytes + 512);   // 128 floats behind the barriers
     const bool finisher = warp >= 2;
     const int quarter = warp & 3;
-    const int tile_row = quarter * 32 + lane;
-    const int row = m0 + tile_row;
-    float scale = 1.0f, squares = 0.0f;
-    Candidate best{-INFINITY, INT32_MAX};   // B200_EPI_ARGMAX: this row's preferred feature among the columns seen so far
     bool ready = false;
     if (finisher) {
+        const int tile_row = quarter * 32 + lane;
+        const int row = m0 + tile_row;
+        float scale = 1.0f;
         if (p.sumsq_in && row < p.rows) {
             float total = 0.0f;
             for (int i = 0; i < p.parts_in; ++i) total += __ldg(p.sumsq_in + static_cast<int64_t>(i) * p.rows + row);
             scale = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(total, static_cast<float>(p.in)), static_cast<float>(p.eps))));
         }
+        row_scale[tile_row] = scale;
         ready = mbar_wait(accumulator_ready, 0);
         if (!ready && lane == 0) atomicExch(gp.status, B200_DEVICE_TIMEOUT);
         tc_fence_after_sync();
-    }
-    if (split == 1) {
-        if (finisher && ready) {
+        if (ready) {
 #pragma unroll 1
             for (int c = 0; c < kTileN / 32; ++c) {
                 uint32_t r[32];
                 tmem_load_32(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + c * 32, r);
-                if (row >= p.rows) continue;
+                float4* out4 = reinterpret_cast<float4*>(tile + tile_row * kTileStride + c * 32);
 #pragma unroll
-                for (int j = 0; j < 32; j += 2) {
-                    const int feature0 = n0 + c * 32 + j;
-                    if (feature0 >= p.out) continue;
-                    const float a = __uint_as_float(r[j]) * scale, b = __uint_as_float(r[j + 1]) * scale;
+                for (int j = 0; j < 8; ++j)
+                    out4[j] = make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]), __uint_as_float(r[4 * j + 2]),
+                                          __uint_as_float(r[4 * j + 3]));
+            }
+        }
+        asm volatile("bar.sync 2, 128;" ::: "memory");   // the four epilogue warps: the whole tile is in shared memory
+    }
+    if (split > 1) {
+        __syncwarp();
+        cluster_sync_all();   // every CTA's partial tile is complete and visible to its peers
+    }
+    if (finisher) {
+        const int rows_each = (kTileM + split - 1) / split;
+        const int first = part * rows_each, last = min(kTileM, first + rows_each);
+        uint32_t peer_tile[8];
+        peer_tile[0] = smem_u32(tile);
+        if (split > 1) {
+#pragma unroll
+            for (int z = 0; z < 8; ++z) peer_tile[z] = z < split ? map_peer_shared(smem_u32(tile), static_cast<uint32_t>(z)) : 0u;
+        }
+        // A warp takes kBatch consecutive rows per iteration: first every value the rows need is requested (accumulators
+        // from shared memory or from the peers, residual pairs from global memory), then the rows are finished, so the
+        // memory round trips of the rows overlap instead of queueing behind each other.
+        constexpr int kBatch = 4, kPasses = kTileN / 64;
+        for (int base = first + quarter * kBatch; base < last; base += 4 * kBatch) {
+            if (m0 + base >= p.rows) break;   // rows grow with base
+            float2 value[kBatch][kPasses], carried[kBatch][kPasses];
+#pragma unroll
+            for (int r = 0; r < kBatch; ++r) {
+                const int tile_row = base + r, row = m0 + tile_row;
+                const bool live_row = tile_row < last && row < p.rows;
+#pragma unroll
+                for (int pass = 0; pass < kPasses; ++pass) {
+                    const int c = pass * 64 + lane * 2;
+                    const int feature0 = n0 + c;
+                    value[r][pass] = make_float2(0.0f, 0.0f);
+                    carried[r][pass] = make_float2(0.0f, 0.0f);
+                    if (!live_row) continue;
+                    if (split == 1) {
+                        value[r][pass] = *reinterpret_cast<const float2*>(tile + tile_row * kTileStride + c);
+                    } else {
+                        const uint32_t offset = static_cast<uint32_t>(tile_row * kTileStride + c) * 4;
+                        float2 v[8];
+#pragma unroll
+                        for (int z = 0; z < 8; ++z) v[z] = z < split ? load_cluster_float2(peer_tile[z] + offset) : make_float2(0.0f, 0.0f);
+                        float2 sum = v[0];
+#pragma unroll
+                        for (int z = 1; z < 8; ++z) { sum.x += v[z].x; sum.y += v[z].y; }
+                        value[r][pass] = sum;
+                    }
+                    if constexpr (EPI == B200_EPI_RESIDUAL) {
+                        if (feature0 < p.out) {
+                            const float* source = p.residual + static_cast<int64_t>(row) * p.out + feature0;
+                            if ((p.out & 1) == 0) carried[r][pass] = *reinterpret_cast<const float2*>(source);
+                            else carried[r][pass] = make_float2(source[0], feature0 + 1 < p.out ? source[1] : 0.0f);
+                        }
+                    }
+                }
+            }
+#pragma unroll
+            for (int r = 0; r < kBatch; ++r) {
+                const int tile_row = base + r, row = m0 + tile_row;
+                if (tile_row >= last || row >= p.rows) break;
+                const float scale = row_scale[tile_row];
+                float squares = 0.0f;
+                Candidate best{-INFINITY, INT32_MAX};
+#pragma unroll
+                for (int pass = 0; pass < kPasses; ++pass) {
+                    const int feature0 = n0 + pass * 64 + lane * 2;
+                    if (!ready || feature0 >= p.out) continue;
+                    const float a = value[r][pass].x * scale, b = value[r][pass].y * scale;
                     if constexpr (EPI == B200_EPI_ARGMAX) {
                         const Candidate pair = pair_candidate(feature0, a, b, p.out);
                         if (preferred(pair, best)) best = pair;
                     } else {
-                        finish_pair<EPI>(p, row, feature0, a, b, squares);
+                        finish_pair<EPI>(p, row, feature0, a, b, carried[r][pass], squares);
+                    }
+                }
+                if constexpr (EPI == B200_EPI_RESIDUAL) {
+                    if (p.sumsq_out) {
+#pragma unroll
+                        for (int o = 16; o > 0; o >>= 1) squares += __shfl_xor_sync(0xffffffffu, squares, o);
+                        if (lane == 0) p.sumsq_out[static_cast<int64_t>(blockIdx.y) * p.rows + row] = squares;
+                    }
+                }
+                if constexpr (EPI == B200_EPI_ARGMAX) {
+#pragma unroll
+                    for (int o = 16; o > 0; o >>= 1) {
+                        const Candidate other{__shfl_xor_sync(0xffffffffu, best.value, o), __shfl_xor_sync(0xffffffffu, best.index, o)};
+                        if (preferred(other, best)) best = other;
+                    }
+                    if (lane == 0) {
+                        p.best_value[static_cast<int64_t>(blockIdx.y) * p.rows + row] = best.value;
+                        p.best_index[static_cast<int64_t>(blockIdx.y) * p.rows + row] = best.index;
                     }
                 }
             }
-            if constexpr (EPI == B200_EPI_RESIDUAL) {
-                if (p.sumsq_out && row < p.rows) p.sumsq_out[static_cast<int64_t>(blockIdx.y) * p.rows + row] = squares;
-            }
-            if constexpr (EPI == B200_EPI_ARGMAX) {
-                if (row < p.rows) {
-                    p.best_value[static_cast<int64_t>(blockIdx.y) * p.rows + row] = best.value;
-                    p.best_index[static_cast<int64_t>(blockIdx.y) * p.rows + row] = best.index;
-                }
-            }
         }
-    } else {
-        // Partial tile, transposed [feature column][token row] f32 (64 KB over the first stages of the drained ring):
-        // a warp's lanes are consecutive rows, so its stores and the peers' loads are conflict-free and coalesced.
-        float* partial = reinterpret_cast<float*>(smem);
-        if (finisher && ready) {
-#pragma unroll 1
-            for (int c = 0; c < kTileN / 32; ++c) {
-                uint32_t r[32];
-                tmem_load_32(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + c * 32, r);
-#pragma unroll
-                for (int j = 0; j < 32; ++j) partial[(c * 32 + j) * kTileM + tile_row] = __uint_as_float(r[j]);
-            }
-        }
-        __syncwarp();
-        cluster_sync_all();   // every CTA's partial tile is complete and visible to its peers
-        if (finisher && ready && row < p.rows) {
-            const int width = ((kTileN + split - 1) / split + 1) & ~1;   // even: the epilogues work on feature pairs
-            const int c_begin = part * width, c_end = min(kTileN, c_begin + width);
-            const uint32_t mine = smem_u32(partial) + static_cast<uint32_t>(tile_row) * 4;
-#pragma unroll 1
-            for (int c = c_begin; c < c_end; c += 2) {
-                const int feature0 = n0 + c;
-                if (feature0 >= p.out) break;
-                float a = 0.0f, b = 0.0f;
-                for (int z = 0; z < split; ++z) {
-                    a += load_peer_shared(mine + static_cast<uint32_t>(c * kTileM) * 4, static_cast<uint32_t>(z));
-                    b += load_peer_shared(mine + static_cast<uint32_t>((c + 1) * kTileM) * 4, static_cast<uint32_t>(z));
-                }
-                if constexpr (EPI == B200_EPI_ARGMAX) {
-                    const Candidate pair = pair_candidate(feature0, a * scale, b * scale, p.out);
-                    if (preferred(pair, best)) best = pair;
-                } else {
-                    finish_pair<EPI>(p, row, feature0, a * scale, b * scale, squares);
-                }
-            }
-            if constexpr (EPI == B200_EPI_RESIDUAL) {
-                if (p.sumsq_out) p.sumsq_out[(static_cast<int64_t>(blockIdx.y) * split + part) * p.rows + row] = squares;
-            }
-            if constexpr (EPI == B200_EPI_ARGMAX) {
-                p.best_value[(static_cast<int64_t>(blockIdx.y) * split + part) * p.rows + row] = best.value;
-                p.best_index[(static_cast<int64_t>(blockIdx.y) * split + part) * p.rows + row] = best.index;
-            }
-        }
+    }
+    if (split > 1) {
         __syncwarp();
         cluster_sync_all();   // no CTA leaves while a peer may still read its shared memory
     }
@@ -302,12 +368,12 @@ __global__ void __launch_bounds__(kGemmThreads, 1) linear_gemm_kernel(const __gr
     }
 }
 
-int encode_operand(CUtensorMap* map, const void* base, int rows, int columns) {
+int encode_operand(CUtensorMap* map, const void* base, int rows, int columns, int box_rows) {
     encode_tiled_fn encode = tensor_map_encoder();
     if (!encode) { set_error("cuTensorMapEncodeTiled is not available from this driver"); return B200_NO_DEVICE; }
     const cuuint64_t dims[2] = {static_cast<cuuint64_t>(columns), static_cast<cuuint64_t>(rows)};
     const cuuint64_t strides[1] = {static_cast<cuuint64_t>(columns) * 2};
-    const cuuint32_t box[2] = {kBlockK, kTileM};
+    const cuuint32_t box[2] = {kBlockK, static_cast<cuuint32_t>(box_rows)};
     const cuuint32_t element_strides[2] = {1, 1};
     const CUresult result = encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box,
                                    element_strides, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
@@ -316,33 +382,66 @@ int encode_operand(CUtensorMap* map, const void* base, int rows, int columns) {
     return B200_OK;
 }
 
-// K split of a launch: as many cluster CTAs as keep the grid within one wave of the SMs, at most 8 (the portable
-// cluster size), and at least two K blocks per CTA.
+// Tile width of a launch: 128 features; 256 only for very wide matrices (vocabulary projections), where the tiles still
+// fill the SMs several times over and the wide tile halves the activation bytes pulled per weight byte.
+int choose_tile_features(int rows, int out) {
+    int device = 0, sms = 148;
+    if (cudaGetDevice(&device) == cudaSuccess) sms = sm_count(device);
+    const int row_tiles = (rows + kTileM - 1) / kTileM;
+    return row_tiles * ((out + 255) / 256) >= 2 * sms ? 256 : 128;
+}
+
+// Ring depth for the 128-wide tile: two stages (96 KB) let two CTAs share an SM, so one tile's epilogue and pipeline ramp
+// overlap the other's products; up to 64 rows the activation boxes are mostly zero fill and a CTA alone with a deep ring
+// streams weights faster.
+int choose_stages(int rows) { return rows > 64 ? 2 : 4; }
+
+// K split of a launch: cluster CTAs (grid z) while the grid stays within one wave of the SMs, at most 4 (larger clusters
+// of CTAs this big place badly), and at least two K blocks per CTA.
 int choose_split(int rows, int in, int out) {
     int device = 0, sms = 148;
     if (cudaGetDevice(&device) == cudaSuccess) sms = sm_count(device);
-    const int tiles = ((rows + kTileM - 1) / kTileM) * ((out + kTileN - 1) / kTileN);
+    const int tn = choose_tile_features(rows, out);
+    const int tiles = ((rows + kTileM - 1) / kTileM) * ((out + tn - 1) / tn);
     const int k_blocks = (in + kBlockK - 1) / kBlockK;
     int split = sms / (tiles > 0 ? tiles : 1);
-    if (split > 8) split = 8;
+    if (split > 4) split = 4;
     if (split > k_blocks / 2) split = k_blocks / 2;
     return split < 1 ? 1 : split;
 }
 
-template <int EPI> int launch_gemm(const CUtensorMap& hi, const CUtensorMap& lo, const CUtensorMap& w, const GemmParams& gp, cudaStream_t stream) {
-    auto kernel = linear_gemm_kernel<EPI>;
-    B200_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kGemmSmem));
+template <int EPI, int TN, int STAGES>
+int launch_gemm(const CUtensorMap& hi, const CUtensorMap& lo, const CUtensorMap& w, const GemmParams& gp, cudaStream_t stream) {
+    using S = GemmShape<TN, STAGES>;
+    auto kernel = linear_gemm_kernel<EPI, TN, STAGES>;
+    B200_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, S::smem));
     const int split = choose_split(gp.base.rows, gp.base.in, gp.base.out);
-    const dim3 grid((gp.base.rows + kTileM - 1) / kTileM, (gp.base.out + kTileN - 1) / kTileN, split);
+    const dim3 grid((gp.base.rows + kTileM - 1) / kTileM, (gp.base.out + TN - 1) / TN, split);
     if (split == 1)
-        return cuda_status(launch_dependent(kernel, grid, dim3(kGemmThreads), kGemmSmem, stream, hi, lo, w, gp), "linear_gemm_kernel launch");
-    return cuda_status(launch_dependent_cluster(kernel, grid, dim3(kGemmThreads), kGemmSmem, stream, dim3(1, 1, split), hi, lo, w, gp),
+        return cuda_status(launch_dependent(kernel, grid, dim3(kGemmThreads), S::smem, stream, hi, lo, w, gp), "linear_gemm_kernel launch");
+    return cuda_status(launch_dependent_cluster(kernel, grid, dim3(kGemmThreads), S::smem, stream, dim3(1, 1, split), hi, lo, w, gp),
                        "linear_gemm_kernel cluster launch");
+}
+
+template <int TN, int STAGES>
+int launch_epilogue(int epilogue, const CUtensorMap& hi, const CUtensorMap& lo, const CUtensorMap& w, const GemmParams& gp, cudaStream_t stream) {
+    switch (epilogue) {
+    case B200_EPI_STORE: return launch_gemm<B200_EPI_STORE, TN, STAGES>(hi, lo, w, gp, stream);
+    case B200_EPI_RESIDUAL: return launch_gemm<B200_EPI_RESIDUAL, TN, STAGES>(hi, lo, w, gp, stream);
+    case B200_EPI_SWIGLU: return launch_gemm<B200_EPI_SWIGLU, TN, STAGES>(hi, lo, w, gp, stream);
+    case B200_EPI_QKV: return launch_gemm<B200_EPI_QKV, TN, STAGES>(hi, lo, w, gp, stream);
+    case B200_EPI_ARGMAX: return launch_gemm<B200_EPI_ARGMAX, TN, STAGES>(hi, lo, w, gp, stream);
+    }
+    return B200_UNSUPPORTED;
 }
 
 }  // namespace
 
-int linear_gemm_parts(int rows, int in, int out) { return ((out + kTileN - 1) / kTileN) * choose_split(rows, in, out); }
+int linear_gemm_parts(int rows, int in, int out) {
+    (void)in;
+    const int tn = choose_tile_features(rows, out);
+    return (out + tn - 1) / tn;   // one partial per feature tile: a row of a tile is finished by one CTA of the cluster
+}
 
 int launch_linear_gemm(const LinearParams& p, int epilogue, cudaStream_t stream) {
     if (p.weight_dtype != B200_BF16 || !p.x_hi || !p.x_lo || (p.in & 7) || (p.out_hi && (p.out & 1))
@@ -352,18 +451,14 @@ int launch_linear_gemm(const LinearParams& p, int epilogue, cudaStream_t stream)
     B200_CUDA(cudaGetDevice(&device));
     GemmParams gp{p, device_status_word(device)};
     alignas(64) CUtensorMap hi, lo, w;
-    int status = encode_operand(&hi, p.x_hi, p.rows, p.in);
-    if (status == B200_OK) status = encode_operand(&lo, p.x_lo, p.rows, p.in);
-    if (status == B200_OK) status = encode_operand(&w, p.weight, p.out, p.in);
+    const int tn = choose_tile_features(p.rows, p.out);
+    int status = encode_operand(&hi, p.x_hi, p.rows, p.in, kTileM);
+    if (status == B200_OK) status = encode_operand(&lo, p.x_lo, p.rows, p.in, kTileM);
+    if (status == B200_OK) status = encode_operand(&w, p.weight, p.out, p.in, tn);
     if (status != B200_OK) return status;
-    switch (epilogue) {
-    case B200_EPI_STORE: return launch_gemm<B200_EPI_STORE>(hi, lo, w, gp, stream);
-    case B200_EPI_RESIDUAL: return launch_gemm<B200_EPI_RESIDUAL>(hi, lo, w, gp, stream);
-    case B200_EPI_SWIGLU: return launch_gemm<B200_EPI_SWIGLU>(hi, lo, w, gp, stream);
-    case B200_EPI_QKV: return launch_gemm<B200_EPI_QKV>(hi, lo, w, gp, stream);
-    case B200_EPI_ARGMAX: return launch_gemm<B200_EPI_ARGMAX>(hi, lo, w, gp, stream);
-    }
-    return B200_UNSUPPORTED;
+    const int stages = choose_stages(p.rows);
+    if (tn == 256) return launch_epilogue<256, 3>(epilogue, hi, lo, w, gp, stream);
+    return stages == 2 ? launch_epilogue<128, 2>(epilogue, hi, lo, w, gp, stream) : launch_epilogue<128, 4>(epilogue, hi, lo, w, gp, stream);
 }
 
 }  // namespace b200

@@ -413,7 +413,7 @@ def test_dense_tensor_core_linear(rows, inner, out, epilogue):
     xn = oracle.rms_norm(x, W.bf16_to_f32(norm), 1e-5)
     full = oracle.linear(xn, w)
     parts = l.b200_linear_shadow_parts(rows, inner, out)
-    assert parts > 0 and parts % ((out + 127) // 128) == 0 and parts // ((out + 127) // 128) <= 8
+    assert parts in ((out + 127) // 128, (out + 255) // 256)   # one partial per feature tile of the dense kernel
     cols = out // 2 if epilogue == 2 else out
     y = torch.zeros((rows, cols), dtype=torch.float32, device="cuda")
     ohi = torch.zeros((rows, cols), dtype=torch.bfloat16, device="cuda")
