@@ -146,6 +146,7 @@ def _declare(l: C.CDLL) -> None:
         "b200_token_feedback": (C.c_int, [vp, i64, vp, vp, i64, vp, vp]),
         "b200_sample": (C.c_int, [vp, i64, i64, C.c_double, vp, vp, vp]),
         "dl_generation_step_sampled": (C.c_int, [vp, C.c_double, vp, vp]),
+        "b200_linear_argmax_parts": (i32, [i64, i64, i64]),
         "b200_argmax_finish": (C.c_int, [vp, vp, i32, i64, vp, vp, vp, i64, vp, vp]),
         "b200_scaled_add": (C.c_int, [vp, vp, C.c_float, i64, vp]),
         "b200_take_device_status": (C.c_int, [i32, vp, C.POINTER(i32)]),

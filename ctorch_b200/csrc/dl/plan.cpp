@@ -320,7 +320,7 @@ void DecodePlan::logits(const Linear& output, Index rows, float* out, void* stre
 bool DecodePlan::prepare_choice(const Linear& output, Index rows, int device) {
     const Index V = output.weight().size(0), D = owner_.dimensions();
     if (!shadows_for(rows) || output.weight().dtype() != DType::bf16 || output.weight().size(1) != D) return false;
-    const Index parts = b200_linear_shadow_parts(rows, D, V);
+    const Index parts = b200_linear_argmax_parts(rows, D, V);
     if (parts <= 0) return false;
     if (!best_value_.defined() || best_value_.numel() < parts * rows || best_value_.device().index != device) {
         synchronize(Device::cuda(device));
@@ -335,7 +335,7 @@ bool DecodePlan::prepare_choice(const Linear& output, Index rows, int device) {
 void DecodePlan::choose(const Linear& output, Index rows, Index* next, Index* ids, Index* history, Index history_rows, std::int32_t* counter,
                         void* stream) {
     const Index V = output.weight().size(0), D = owner_.dimensions();
-    const Index parts = b200_linear_shadow_parts(rows, D, V);
+    const Index parts = b200_linear_argmax_parts(rows, D, V);
     if (parts <= 0 || !best_value_.defined() || best_value_.numel() < parts * rows)
         throw std::logic_error("fused logits + argmax was not prepared for this row count");
     b200_shadow_linear_args args{};

@@ -126,6 +126,8 @@ __device__ __forceinline__ void linear_epilogue(const LinearParams& p, int row, 
 int launch_linear_stream(const LinearParams& p, int epilogue, cudaStream_t stream);
 // Number of per-row sum-of-squares partials a residual-epilogue shadow call with these sizes writes (0: unsupported).
 int linear_stream_parts(int rows, int in, int out);
+// Number of per-row candidate slices the argmax epilogue of a shadow call with these sizes writes (0: unsupported).
+int linear_argmax_parts(int rows, int in, int out);
 // tcgen05 GEMM for many rows (linear_gemm.cu): shadow input only; B200_UNSUPPORTED otherwise.
 int launch_linear_gemm(const LinearParams& p, int epilogue, cudaStream_t stream);
 int linear_gemm_parts(int rows, int in, int out);

@@ -300,3 +300,8 @@ extern "C" int32_t b200_linear_shadow_parts(int64_t rows, int64_t in, int64_t ou
     if (rows <= 0 || in <= 0 || out <= 0 || rows > INT32_MAX || in > INT32_MAX || out > INT32_MAX) return 0;
     return b200::linear_stream_parts(static_cast<int>(rows), static_cast<int>(in), static_cast<int>(out));
 }
+
+extern "C" int32_t b200_linear_argmax_parts(int64_t rows, int64_t in, int64_t out) {
+    if (rows <= 0 || in <= 0 || out <= 0 || rows > INT32_MAX || in > INT32_MAX || out > INT32_MAX) return 0;
+    return b200::linear_argmax_parts(static_cast<int>(rows), static_cast<int>(in), static_cast<int>(out));
+}

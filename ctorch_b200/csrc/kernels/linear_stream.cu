@@ -280,6 +280,11 @@ __global__ void __launch_bounds__(kThreads, 2) linear_stream_kernel(const Stream
     const uint32_t a_hi = smem_u32(x_hi) + a_lane, a_lo = smem_u32(x_lo) + a_lane;
     const int ksteps = (p.in + 15) >> 4;
 
+    // B200_EPI_ARGMAX: the row candidates this thread has seen over the CTA's tiles (one per pass of the finishing loop)
+    Candidate running[TF > 32 ? 2 : 1];
+#pragma unroll
+    for (int i = 0; i < (TF > 32 ? 2 : 1); ++i) running[i] = Candidate{-INFINITY, INT32_MAX};
+
     bool alive = true;
     for (int t = 0; t < my_tiles && alive; ++t) {
         const int tile = blockIdx.x + t * gridDim.x;
@@ -347,6 +352,7 @@ __global__ void __launch_bounds__(kThreads, 2) linear_stream_kernel(const Stream
         consumer_barrier();
         if (t == 0) B200_MARK(5);
         // items of one row are TF/2 consecutive threads of a warp: thread i finishes the feature pair (r, f)
+#pragma unroll
         for (int base = 0; base < kRows * (TF / 2); base += kConsumers * 32) {
             const int i = base + threadIdx.x;
             const int r = i / (TF / 2), f = (i - r * (TF / 2)) * 2;
@@ -410,10 +416,7 @@ __global__ void __launch_bounds__(kThreads, 2) linear_stream_kernel(const Stream
                     const Candidate other{__shfl_xor_sync(0xffffffffu, best.value, o), __shfl_xor_sync(0xffffffffu, best.index, o)};
                     if (preferred(other, best)) best = other;
                 }
-                if (f == 0 && in_tile && row < p.rows) {
-                    p.best_value[static_cast<int64_t>(tile) * p.rows + row] = best.value;
-                    p.best_index[static_cast<int64_t>(tile) * p.rows + row] = best.index;
-                }
+                if (preferred(best, running[base / (kConsumers * 32)])) running[base / (kConsumers * 32)] = best;
             }
             if constexpr (SHADOW && EPI == B200_EPI_SWIGLU) {
                 if (p.out_hi && live) {
@@ -426,6 +429,18 @@ __global__ void __launch_bounds__(kThreads, 2) linear_stream_kernel(const Stream
         }
         consumer_barrier();
         if (t == 0) B200_MARK(6);
+    }
+    if constexpr (EPI == B200_EPI_ARGMAX) {
+        // one candidate per row and CTA: thread (row r, first pair) holds the best of the CTA's tiles
+#pragma unroll
+        for (int base = 0; base < kRows * (TF / 2); base += kConsumers * 32) {
+            const int i = base + threadIdx.x;
+            const int r = i / (TF / 2), f = i - r * (TF / 2);
+            if (alive && f == 0 && i < kRows * (TF / 2) && row0 + r < p.rows) {
+                p.best_value[static_cast<int64_t>(blockIdx.x) * p.rows + row0 + r] = running[base / (kConsumers * 32)].value;
+                p.best_index[static_cast<int64_t>(blockIdx.x) * p.rows + row0 + r] = running[base / (kConsumers * 32)].index;
+            }
+        }
     }
     B200_MARK(7);
     trace_end(trace);
@@ -488,6 +503,17 @@ int linear_stream_parts(int rows, int in, int out) {
     StreamParams sp{};
     size_t smem = 0;
     return choose_tiling(in, out, sm_count(device), sp, smem) ? sp.tiles : 0;
+}
+
+int linear_argmax_parts(int rows, int in, int out) {
+    if ((in & 7) || in <= 0 || out <= 0) return 0;
+    if (rows >= kGemmRows || in > kMaxIn) return linear_gemm_parts(rows, in, out);
+    int device = 0;
+    if (cudaGetDevice(&device) != cudaSuccess) return 0;
+    StreamParams sp{};
+    size_t smem = 0;
+    if (!choose_tiling(in, out, sm_count(device), sp, smem)) return 0;
+    return sp.tiles < sm_count(device) ? sp.tiles : sm_count(device);   // one candidate slice per CTA
 }
 
 int launch_linear_stream(const LinearParams& p, int epilogue, cudaStream_t stream) {

@@ -275,9 +275,17 @@ __global__ void __launch_bounds__(1024) argmax_finish_kernel(const float* best_v
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
     for (int64_t row = warp; row < rows; row += warps) {
         Candidate best{-INFINITY, INT32_MAX};
-        for (int t = lane; t < parts; t += 32) {
-            const Candidate other{best_value[static_cast<int64_t>(t) * rows + row], best_index[static_cast<int64_t>(t) * rows + row]};
-            if (preferred(other, best)) best = other;
+        for (int t0 = 0; t0 < parts; t0 += 32 * 8) {   // eight independent loads per lane in flight
+            Candidate batch[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                const int t = t0 + u * 32 + lane;
+                batch[u] = t < parts ? Candidate{__ldg(best_value + static_cast<int64_t>(t) * rows + row), __ldg(best_index + static_cast<int64_t>(t) * rows + row)}
+                                     : Candidate{-INFINITY, INT32_MAX};
+            }
+#pragma unroll
+            for (int u = 0; u < 8; ++u)
+                if (preferred(batch[u], best)) best = batch[u];
         }
         for (int o = 16; o > 0; o >>= 1) {
             const Candidate other{__shfl_xor_sync(0xffffffffu, best.value, o), __shfl_xor_sync(0xffffffffu, best.index, o)};

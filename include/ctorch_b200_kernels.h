@@ -146,7 +146,7 @@ typedef struct b200_shadow_linear_args {
     const void* out_norm_weight;   /* residual epilogue: weight [out] of the norm that follows, folded into the shadow */
     int32_t out_norm_dtype;
     float* sumsq_out;              /* residual epilogue: [b200_linear_shadow_parts(rows, in, out)][rows] */
-    float* best_value;             /* B200_EPI_ARGMAX: [b200_linear_shadow_parts(rows, in, out)][rows] */
+    float* best_value;             /* B200_EPI_ARGMAX: [b200_linear_argmax_parts(rows, in, out)][rows] */
     int32_t* best_index;           /* B200_EPI_ARGMAX: same shape, feature index of best_value */
 } b200_shadow_linear_args;
 /* Up to 16 rows with in <= 2048: streaming kernel (bulk-TMA weight ring, mma.sync).  More rows or a wider input:
@@ -154,6 +154,9 @@ typedef struct b200_shadow_linear_args {
 B200_API int b200_linear_shadow(const b200_shadow_linear_args* args, void* stream);
 /* Number of row-sum partials a residual-epilogue call with these sizes writes (its feature tiles), 0 if unsupported. */
 B200_API int32_t b200_linear_shadow_parts(int64_t rows, int64_t in, int64_t out);
+/* Number of candidate slices a B200_EPI_ARGMAX call with these sizes writes (one per CTA of the streaming kernel, one per
+ * feature tile of the dense kernel), 0 if unsupported. */
+B200_API int32_t b200_linear_argmax_parts(int64_t rows, int64_t in, int64_t out);
 /* Second half of the fused logits + greedy choice: merges the `parts` per-tile candidates of every row (same rule), writes
  * the chosen feature index to next[rows], and does what b200_token_feedback does with it (ids, history, counter; any of
  * ids / history may be NULL).  One launch of one CTA. */

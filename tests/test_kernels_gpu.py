@@ -469,7 +469,7 @@ def test_fused_logits_argmax(rows, inner, vocab):
     lo = torch.zeros_like(hi)
     sq = torch.zeros((1, rows), dtype=torch.float32, device="cuda")
     B.kcheck(l.b200_shadow_from_rows(xd.data_ptr(), rows, inner, nd.data_ptr(), B.BF16, hi.data_ptr(), lo.data_ptr(), sq.data_ptr(), stream()))
-    parts = l.b200_linear_shadow_parts(rows, inner, vocab)
+    parts = l.b200_linear_argmax_parts(rows, inner, vocab)
     assert parts > 0
     best_value = torch.zeros((parts, rows), dtype=torch.float32, device="cuda")
     best_index = torch.zeros((parts, rows), dtype=torch.int32, device="cuda")
