@@ -117,7 +117,8 @@ def _declare(l: C.CDLL) -> None:
         "dl_decoder_generate": (C.c_int, [vp, vp, vp, vp, i64, vp, pp]),
         "dl_generation_profile_step": (C.c_int, [vp, C.POINTER(C.c_double)]),
         "dl_b200_tp_unique_id": (C.c_int, [vp]), "dl_b200_tp_init": (C.c_int, [Device, i32, i32, vp]),
-        "dl_b200_tp_finalize": (C.c_int, [Device]), "dl_transformer_decoder_set_tensor_parallel": (C.c_int, [vp, i32, i32]),
+        "dl_b200_tp_finalize": (C.c_int, [Device]),
+        "dl_b200_tp_symmetric_handle": (C.c_int, [Device, sz, vp]), "dl_b200_tp_symmetric_open": (C.c_int, [Device, vp, i32]), "dl_transformer_decoder_set_tensor_parallel": (C.c_int, [vp, i32, i32]),
         "dl_b200_timer_start": (C.c_int, [Device]), "dl_b200_timer_stop": (C.c_int, [Device, C.POINTER(C.c_double)]),
         "dl_b200_stream": (vp, [Device]),
         # kernel-level ABI
@@ -147,6 +148,8 @@ def _declare(l: C.CDLL) -> None:
         "b200_sample": (C.c_int, [vp, i64, i64, C.c_double, vp, vp, vp]),
         "dl_generation_step_sampled": (C.c_int, [vp, C.c_double, vp, vp]),
         "b200_linear_argmax_parts": (i32, [i64, i64, i64]),
+        "b200_tp_region_bytes": (sz, [sz]), "b200_tp_slot": (vp, [vp, sz, i32]),
+        "b200_tp_reduce_shadow": (C.c_int, [pp, i32, i32, i32, sz, i64, i64, vp, i32, vp, vp, vp, vp, vp]),
         "b200_argmax_finish": (C.c_int, [vp, vp, i32, i64, vp, vp, vp, i64, vp, vp]),
         "b200_scaled_add": (C.c_int, [vp, vp, C.c_float, i64, vp]),
         "b200_take_device_status": (C.c_int, [i32, vp, C.POINTER(i32)]),
@@ -512,8 +515,10 @@ def timer_stop(device: int = 0) -> float:
     return ms.value
 
 
-def tensor_parallel_init(rank: int, world: int, device: int) -> None:
-    """Joins the tensor-parallel group of `world` ranks; the NCCL id travels over torch.distributed (any backend)."""
+def tensor_parallel_init(rank: int, world: int, device: int, peer_slot_bytes: int = 8 << 20) -> None:
+    """Joins the tensor-parallel group of `world` ranks; the NCCL id travels over torch.distributed (any backend).
+    `peer_slot_bytes` > 0 also maps the ranks' symmetric memory (CUDA IPC handles gathered the same way) so that steps of
+    up to that many bytes of residual rows sum over NVLink peer memory instead of calling NCCL."""
     import torch
     import torch.distributed as dist
     ident = (C.c_char * 128)()
@@ -525,6 +530,16 @@ def tensor_parallel_init(rank: int, world: int, device: int) -> None:
     dist.broadcast(payload, src=0)
     raw = bytes(payload.cpu().tolist())
     check(lib().dl_b200_tp_init(cuda(device), rank, world, raw))
+    if peer_slot_bytes > 0 and world <= 8:
+        handle = (C.c_char * 64)()
+        check(lib().dl_b200_tp_symmetric_handle(cuda(device), peer_slot_bytes, handle))
+        mine = torch.tensor(list(handle.raw), dtype=torch.uint8)
+        if dist.get_backend() == "nccl":
+            mine = mine.cuda(device)
+        table = [torch.empty_like(mine) for _ in range(world)]
+        dist.all_gather(table, mine)
+        check(lib().dl_b200_tp_symmetric_open(cuda(device), bytes(torch.cat(table).cpu().tolist()), world))
+        dist.barrier()   # every rank has mapped every region before the first step
 
 
 def tensor_parallel_finalize(device: int) -> None:

@@ -20,6 +20,12 @@ void tp_finalize(int device);
 int tp_world(int device);
 int tp_rank(int device);
 void tp_all_reduce(int device, float* data, std::size_t count);
+void tp_symmetric_handle(int device, std::size_t slot_bytes, void* handle64);
+void tp_symmetric_open(int device, const void* handles, int world);
+bool tp_symmetric_ready(int device, std::size_t bytes);   // mapped on all ranks and a slot holds `bytes`
+float* tp_partial_slot(int device, int slot);              // this rank's partial rows, slot 0 or 1
+void tp_reduce_shadow(int device, int slot, std::int64_t rows, std::int64_t width, const void* norm_weight, int norm_dtype, float* out,
+                      void* out_hi, void* out_lo, float* sumsq_out);
 }  // namespace runtime
 
 namespace internal {

@@ -371,7 +371,16 @@ void DecodePlan::run_layers(const float* x, Index batch, Index length, std::span
         const int parts_down = parallel ? 1 : b200_linear_shadow_parts(rows, F, D);
         auto* sq_attn = static_cast<float*>(sq_attn_.mutable_data());
         auto* sq_ffn = static_cast<float*>(sq_ffn_.mutable_data());
-        auto rebuild_shadow = [&](const Tensor* norm, float* sums) {
+        // With symmetric memory mapped (and the rows fitting a slot) the projections write their partial rows into this
+        // rank's slot and one kernel sums the ranks' slots over NVLink and rebuilds the shadow; otherwise NCCL.
+        const bool peer_sum = parallel && runtime::tp_symmetric_ready(device, static_cast<std::size_t>(rows * D) * sizeof(float));
+        auto rebuild_shadow = [&](const Tensor* norm, float* sums, int slot) {
+            if (peer_sum) {
+                runtime::tp_reduce_shadow(device, slot, rows, D, norm->raw_data(), code_of(norm->dtype()), h, hs_hi_.mutable_data(),
+                                          hs_lo_.mutable_data(), sums);
+                probe(2);
+                return;
+            }
             runtime::tp_all_reduce(device, h, static_cast<std::size_t>(rows * D));
             probe(2);
             runtime::check(b200_shadow_from_rows(h, rows, D, norm->raw_data(), code_of(norm->dtype()), hs_hi_.mutable_data(),
@@ -418,14 +427,14 @@ void DecodePlan::run_layers(const float* x, Index batch, Index length, std::span
             const bool adds_residual = !parallel || rank == 0;
             b200_shadow_linear_args out_proj{};
             out_proj.x_hi = att_hi_.raw_data(); out_proj.x_lo = att_lo_.raw_data(); out_proj.rows = rows; out_proj.in = Dl;
-            out_proj.weight = packed.wo; out_proj.out = D; out_proj.y = h;
+            out_proj.weight = packed.wo; out_proj.out = D; out_proj.y = peer_sum ? runtime::tp_partial_slot(device, 0) : h;
             out_proj.epilogue = adds_residual ? B200_EPI_RESIDUAL : B200_EPI_STORE; out_proj.residual = adds_residual ? in : nullptr;
             if (!parallel) {
                 out_proj.out_hi = hs_hi_.mutable_data(); out_proj.out_lo = hs_lo_.mutable_data();
                 out_proj.out_norm_weight = ffn_norm->raw_data(); out_proj.out_norm_dtype = code_of(ffn_norm->dtype()); out_proj.sumsq_out = sq_ffn;
             }
             shadow_linear(out_proj, stream, "output projection");
-            if (parallel) rebuild_shadow(ffn_norm, sq_ffn);
+            if (parallel) rebuild_shadow(ffn_norm, sq_ffn, 0);
             b200_shadow_linear_args gate_up{};
             gate_up.x_hi = hs_hi_.raw_data(); gate_up.x_lo = hs_lo_.raw_data(); gate_up.rows = rows; gate_up.in = D;
             gate_up.weight = packed.wgu.raw_data(); gate_up.out = 2 * Fl; gate_up.sumsq_in = sq_ffn; gate_up.parts_in = parts_o; gate_up.eps = eps;
@@ -434,14 +443,14 @@ void DecodePlan::run_layers(const float* x, Index batch, Index length, std::span
             const Tensor* next_norm = i + 1 < owner_.layer_count() ? owner_.layer(i + 1).attention_norm().weight() : owner_.normalization().weight();
             b200_shadow_linear_args down{};
             down.x_hi = act_hi_.raw_data(); down.x_lo = act_lo_.raw_data(); down.rows = rows; down.in = Fl;
-            down.weight = packed.wd; down.out = D; down.y = h;
+            down.weight = packed.wd; down.out = D; down.y = peer_sum ? runtime::tp_partial_slot(device, 1) : h;
             down.epilogue = adds_residual ? B200_EPI_RESIDUAL : B200_EPI_STORE; down.residual = adds_residual ? h : nullptr;
             if (!parallel) {
                 down.out_hi = hs_hi_.mutable_data(); down.out_lo = hs_lo_.mutable_data();
                 down.out_norm_weight = next_norm->raw_data(); down.out_norm_dtype = code_of(next_norm->dtype()); down.sumsq_out = sq_attn;
             }
             shadow_linear(down, stream, "down projection");
-            if (parallel) rebuild_shadow(next_norm, sq_attn);
+            if (parallel) rebuild_shadow(next_norm, sq_attn, 1);
             parts_attn = parts_down;
         }
         last_parts_ = parts_attn;

@@ -4,6 +4,8 @@
 // projection and after the FFN down-projection, enqueued on the library's compute stream (capturable in a graph).
 #include "dl/internal.h"
 
+#include "ctorch_b200_kernels.h"
+
 #include <cuda_runtime.h>
 #include <dlfcn.h>
 
@@ -52,8 +54,19 @@ void check_nccl(int result, const char* what) {
 }
 
 std::mutex group_mutex;
-struct Group { Comm comm = nullptr; int rank = 0, world = 1; };
+// `region`: this rank's symmetric memory (control words + two slots of partial rows) and every rank's mapping of it.
+struct Group {
+    Comm comm = nullptr;
+    int rank = 0, world = 1;
+    void* regions[16] = {};
+    std::size_t slot_bytes = 0;
+    bool mapped = false;
+};
 Group groups[64];
+
+void check_runtime(cudaError_t status, const char* what) {
+    if (status != cudaSuccess) throw std::runtime_error(std::string("CUDA: ") + what + ": " + cudaGetErrorString(status));
+}
 
 }  // namespace
 
@@ -74,7 +87,10 @@ void tp_init(int device, int rank, int world, const void* id128) {
     std::memcpy(id.bytes, id128, sizeof id.bytes);
     Comm comm = nullptr;
     check_nccl(nccl().comm_init_rank(&comm, world, id, rank), "ncclCommInitRank");
-    groups[device] = Group{comm, rank, world};
+    groups[device] = Group{};
+    groups[device].comm = comm;
+    groups[device].rank = rank;
+    groups[device].world = world;
 }
 
 void tp_finalize(int device) {
@@ -82,8 +98,81 @@ void tp_finalize(int device) {
     if (device < 0 || device >= 64 || !groups[device].comm) return;
     set_device(device);
     cudaStreamSynchronize(static_cast<cudaStream_t>(stream(device)));
-    nccl().comm_destroy(groups[device].comm);
-    groups[device] = Group{};
+    Group& group = groups[device];
+    for (int r = 0; r < group.world && r < 16; ++r) {
+        if (!group.regions[r]) continue;
+        if (r == group.rank) cudaFree(group.regions[r]);
+        else cudaIpcCloseMemHandle(group.regions[r]);
+    }
+    nccl().comm_destroy(group.comm);
+    group = Group{};
+}
+
+// Symmetric memory for the one-shot sum over peer memory (kernels/tp_reduce.cu).  Each rank allocates its region, hands
+// the 64-byte CUDA IPC handle to the application, which gathers the handles of all ranks (any transport) and gives the
+// table back; only then is the peer path used.  Without the table the plan keeps the NCCL all-reduce.
+void tp_symmetric_handle(int device, std::size_t slot_bytes, void* handle64) {
+    std::lock_guard<std::mutex> lock(group_mutex);
+    if (device < 0 || device >= 64 || !groups[device].comm) throw std::logic_error("tensor-parallel group is not initialised on this device");
+    Group& group = groups[device];
+    if (group.world > 8) throw std::invalid_argument("the peer-memory sum serves at most 8 ranks");
+    if (group.regions[group.rank]) throw std::logic_error("symmetric memory was already allocated on this device");
+    if (!handle64 || slot_bytes == 0 || (slot_bytes & 255)) throw std::invalid_argument("slot size must be a positive multiple of 256 bytes");
+    set_device(device);
+    void* region = nullptr;
+    const std::size_t bytes = b200_tp_region_bytes(slot_bytes);
+    check_runtime(cudaMalloc(&region, bytes), "cudaMalloc(symmetric region)");
+    check_runtime(cudaMemset(region, 0, bytes), "cudaMemset(symmetric region)");
+    check_runtime(cudaDeviceSynchronize(), "cudaDeviceSynchronize");
+    cudaIpcMemHandle_t handle;
+    const cudaError_t status = cudaIpcGetMemHandle(&handle, region);
+    if (status != cudaSuccess) {
+        cudaFree(region);
+        check_runtime(status, "cudaIpcGetMemHandle");
+    }
+    static_assert(sizeof handle == 64, "CUDA IPC handles are 64 bytes");
+    std::memcpy(handle64, &handle, sizeof handle);
+    group.regions[group.rank] = region;
+    group.slot_bytes = slot_bytes;
+}
+
+void tp_symmetric_open(int device, const void* handles, int world) {
+    std::lock_guard<std::mutex> lock(group_mutex);
+    if (device < 0 || device >= 64 || !groups[device].comm) throw std::logic_error("tensor-parallel group is not initialised on this device");
+    Group& group = groups[device];
+    if (!handles || world != group.world || !group.regions[group.rank]) throw std::invalid_argument("handle table does not match the group");
+    set_device(device);
+    for (int r = 0; r < world; ++r) {
+        if (r == group.rank || group.regions[r]) continue;
+        cudaIpcMemHandle_t handle;
+        std::memcpy(&handle, static_cast<const char*>(handles) + 64 * static_cast<std::size_t>(r), sizeof handle);
+        void* mapped = nullptr;
+        check_runtime(cudaIpcOpenMemHandle(&mapped, handle, cudaIpcMemLazyEnablePeerAccess), "cudaIpcOpenMemHandle");
+        group.regions[r] = mapped;
+    }
+    group.mapped = true;
+}
+
+bool tp_symmetric_ready(int device, std::size_t bytes) {
+    std::lock_guard<std::mutex> lock(group_mutex);
+    return device >= 0 && device < 64 && groups[device].mapped && bytes <= groups[device].slot_bytes;
+}
+
+float* tp_partial_slot(int device, int slot) {
+    std::lock_guard<std::mutex> lock(group_mutex);
+    const Group& group = groups[device];
+    return static_cast<float*>(b200_tp_slot(group.regions[group.rank], group.slot_bytes, slot));
+}
+
+void tp_reduce_shadow(int device, int slot, std::int64_t rows, std::int64_t width, const void* norm_weight, int norm_dtype, float* out,
+                      void* out_hi, void* out_lo, float* sumsq_out) {
+    Group group;
+    {
+        std::lock_guard<std::mutex> lock(group_mutex);
+        group = groups[device];
+    }
+    check(b200_tp_reduce_shadow(group.regions, group.rank, group.world, slot, group.slot_bytes, rows, width, norm_weight, norm_dtype, out,
+                                out_hi, out_lo, sumsq_out, stream(device)), "peer-memory sum");
 }
 
 int tp_world(int device) {

@@ -196,6 +196,14 @@ DL_API dl_status dl_decoder_generate(dl_module* decoder, dl_module* embedding, d
 DL_API dl_status dl_b200_tp_unique_id(void* id128);
 DL_API dl_status dl_b200_tp_init(dl_device device, int32_t rank, int32_t world, const void* id128);
 DL_API dl_status dl_b200_tp_finalize(dl_device device);
+/* Optional second step: memory that the ranks read from each other over NVLink, so that the two sums per layer run as one
+ * kernel that also rebuilds the next norm's input (no NCCL call on the token path).  Every rank asks for its 64-byte handle
+ * (the library allocates 4 KiB + 2 * slot_bytes; a slot must hold rows * dimensions * 4 bytes of the largest step that
+ * should take this path), the application gathers the handles of all ranks in rank order and passes the table to every
+ * rank.  Steps whose rows do not fit a slot keep the NCCL all-reduce.  All ranks must be past their last step (a barrier of
+ * the application) before any of them calls dl_b200_tp_finalize. */
+DL_API dl_status dl_b200_tp_symmetric_handle(dl_device device, size_t slot_bytes, void* handle64);
+DL_API dl_status dl_b200_tp_symmetric_open(dl_device device, const void* handles, int32_t world);
 DL_API dl_status dl_transformer_decoder_set_tensor_parallel(dl_module* decoder, int32_t rank, int32_t world);
 
 /* CUDA-event timing on the library's compute stream of a device (benchmarks must time on the launching

@@ -253,6 +253,20 @@ B200_API int b200_scaled_add(float* y, const float* x, float scale, int64_t coun
  * Returns the word and clears it (synchronises the stream). 0 = healthy. */
 B200_API int b200_take_device_status(int32_t device, void* stream, int32_t* status);
 
+/* ---- tensor-parallel sum over NVLink peer memory (no reference counterpart: the reference has no tensor parallelism) ----
+ * Every rank owns a region of b200_tp_region_bytes(slot_bytes) bytes of its own device memory (zero-filled, cudaMalloc'ed,
+ * mapped by every rank of the group, e.g. through CUDA IPC): control words and two slots of partial rows; b200_tp_slot
+ * gives the address of a slot inside a region.  b200_tp_reduce_shadow, called by every rank at the same point of its
+ * stream with regions[r] = rank r's region as mapped here, publishes "my slot is written", waits (bounded; on expiry the
+ * device status word reads B200_DEVICE_TIMEOUT) for all ranks, and writes out[rows, width] = sum over ranks in rank order of
+ * their slot rows, the shadow planes of out * norm_weight and the per-row sums of squares ([1][rows]).  The caller's
+ * projection writes its partial rows into its own slot beforehand, alternating slots 0 and 1 from call to call. */
+B200_API size_t b200_tp_region_bytes(size_t slot_bytes);
+B200_API void* b200_tp_slot(void* region, size_t slot_bytes, int32_t slot);
+B200_API int b200_tp_reduce_shadow(void* const* regions, int32_t rank, int32_t world, int32_t slot, size_t slot_bytes, int64_t rows,
+                                   int64_t width, const void* norm_weight, int32_t norm_dtype, float* out, void* out_hi, void* out_lo,
+                                   float* sumsq_out, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

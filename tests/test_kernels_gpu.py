@@ -521,3 +521,84 @@ def test_temperature_sampling(rows, width, temperature):
             lo, hi = sorted((got[r], want[r]))
             assert hi - lo == 1 and abs(running[r, lo] - uniforms[r]) < 1e-6, (r, got[r], want[r])
     assert (got >= 0).all() and (got < width).all()
+
+
+def _tp_regions(world, slot_bytes):
+    l = B.lib()
+    size = l.b200_tp_region_bytes(slot_bytes)
+    regions = [torch.zeros((size,), dtype=torch.uint8, device="cuda") for _ in range(world)]
+    table = (C.c_void_p * world)(*[r.data_ptr() for r in regions])
+    return regions, table
+
+
+def _slot_view(region, slot_bytes, slot, rows, width):
+    return region[4096 + slot * slot_bytes: 4096 + slot * slot_bytes + rows * width * 4].view(torch.float32).view(rows, width)
+
+
+def test_peer_memory_sum_one_gpu():
+    """The tensor-parallel sum kernel on one GPU: as a group of one, and as rank 0 of two with the other rank's arrival and
+    partial rows put in place by the host beforehand (two kernels that wait on one another never share a GPU)."""
+    l = B.lib()
+    rows, width, slot_bytes = 5, 512, 16384
+    rng = np.random.default_rng(12)
+    norm = W.bf16_bits((1 + 0.1 * rng.standard_normal(width)).astype(np.float32))
+    nd = bf16_dev(norm)
+    out = torch.zeros((rows, width), device="cuda")
+    hi = torch.zeros((rows, width), dtype=torch.bfloat16, device="cuda")
+    lo = torch.zeros_like(hi)
+    sums = torch.zeros((1, rows), device="cuda")
+    for world in (1, 2):
+        regions, table = _tp_regions(world, slot_bytes)
+        for call, slot in ((1, 0), (2, 1), (3, 0)):
+            parts = [rng.standard_normal((rows, width), dtype=np.float32) for _ in range(world)]
+            for r in range(world):
+                _slot_view(regions[r], slot_bytes, slot, rows, width).copy_(torch.from_numpy(parts[r]))
+            if world == 2:   # rank 1 "arrived" for this call
+                regions[0][4:8].view(torch.int32)[0] = call
+            torch.cuda.synchronize()
+            B.kcheck(l.b200_tp_reduce_shadow(table, 0, world, slot, slot_bytes, rows, width, nd.data_ptr(), B.BF16, out.data_ptr(),
+                                             hi.data_ptr(), lo.data_ptr(), sums.data_ptr(), stream()))
+            sync()
+            status = C.c_int32()
+            B.kcheck(l.b200_take_device_status(0, stream(), C.byref(status)))
+            assert status.value == 0
+            want = parts[0] if world == 1 else parts[0] + parts[1]
+            assert np.array_equal(out.cpu().numpy(), want)
+            assert rel(shadow_to_f32(hi, lo), want * W.bf16_to_f32(norm)) < 2e-5
+            assert rel(sums.cpu().numpy()[0], (want.astype(np.float64) ** 2).sum(axis=1)) < 1e-5
+            control = regions[0][:256].view(torch.int32).cpu().numpy()
+            assert control[0] == call and control[32] == call and control[33] == 0      # arrive[0], calls, ticket
+            if world == 2:
+                assert regions[1][:4].view(torch.int32).item() == call                  # the signal sent to the peer
+
+
+def test_peer_memory_sum_gives_up_when_a_rank_never_arrives():
+    """A flag that nothing sets: the wait ends after its limit, the status word reports it, the context stays usable, and a
+    later call does not wait again while the status is set."""
+    import time
+    l = B.lib()
+    rows, width, slot_bytes = 2, 256, 4096
+    regions, table = _tp_regions(2, slot_bytes)
+    out = torch.zeros((rows, width), device="cuda")
+    hi = torch.zeros((rows, width), dtype=torch.bfloat16, device="cuda")
+    lo = torch.zeros_like(hi)
+    sums = torch.zeros((1, rows), device="cuda")
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    B.kcheck(l.b200_tp_reduce_shadow(table, 0, 2, 0, slot_bytes, rows, width, None, 0, out.data_ptr(), hi.data_ptr(), lo.data_ptr(),
+                                     sums.data_ptr(), stream()))
+    sync()
+    waited = time.perf_counter() - t0
+    assert 1.5 < waited < 10.0
+    t0 = time.perf_counter()
+    B.kcheck(l.b200_tp_reduce_shadow(table, 0, 2, 1, slot_bytes, rows, width, None, 0, out.data_ptr(), hi.data_ptr(), lo.data_ptr(),
+                                     sums.data_ptr(), stream()))
+    sync()
+    assert time.perf_counter() - t0 < 1.0
+    status = C.c_int32()
+    B.kcheck(l.b200_take_device_status(0, stream(), C.byref(status)))
+    assert status.value != 0
+    B.kcheck(l.b200_take_device_status(0, stream(), C.byref(status)))
+    assert status.value == 0
+    x = torch.ones((4,), device="cuda") * 2
+    assert float(x.sum()) == 8.0

@@ -26,7 +26,8 @@ def rel(a, b):
 def main():
     rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
     dist.init_process_group("gloo")
-    B.tensor_parallel_init(rank, world, local)
+    # 64 KiB slots: single-token steps (rows * 512 * 4 bytes <= 64 KiB) sum over NVLink peer memory, prefill chunks keep NCCL
+    B.tensor_parallel_init(rank, world, local, peer_slot_bytes=64 << 10)
     report = {"rank": rank, "cases": []}
     for batch, adapters in ((4, True), (32, False)):     # streaming kernel with adapters; tensor-core kernel without
         spec = dict(vocab=1024, d_model=512, layers=3, heads=8, kv_heads=4, hidden=1024, dtype="bf16", batch=batch, prompt=40,
