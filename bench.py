@@ -180,7 +180,8 @@ def run_b200(args, spec, weights) -> dict:
     sliced = args.workload == "c5" and world > 1
     if sliced:
         B.tensor_parallel_init(rank, world, local)
-    model = B.DecoderModel(spec, weights, lora=W.make_lora(spec), device=local, tensor_parallel=(rank, world) if sliced else None)
+    model = B.DecoderModel(spec, weights, lora=W.make_lora(spec), device=local, tensor_parallel=(rank, world) if sliced else None,
+                           activation_dtype=args.activations if spec["dtype"] == "bf16" else None)
     gen = B.Generation(model, batch, total_steps + 1)
     prompt = W.make_prompts(spec, seed=99 if sliced else 99 + rank)
     sampler = ClockSampler(local)
@@ -241,7 +242,8 @@ def run_b200(args, spec, weights) -> dict:
     line = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": device_ms / args.steps, "higher_is_better": True, "scaling": "strong" if sliced or divided else "weak", "vs_baseline": None,
-        "dtype": "bf16 weights and KV, f32 accumulate and activations" if spec["dtype"] == "bf16" else "f32",
+        "dtype": ("bf16 weights and KV, f32 accumulate and activations" if args.activations == "f32" else
+                  "bf16 weights and KV, f32 accumulate, bf16 activations in passes over more than 16 rows") if spec["dtype"] == "bf16" else "f32",
         "data": "synthetic",
         "config": {"workload": args.workload, "batch_per_gpu": batch, "prompt": prompt_len, "mean_context": mean_context,
                    "layers": spec["layers"], "d_model": spec["d_model"], "vocab": spec["vocab"], "parallelism": f"tp{world} (heads, KV heads and SwiGLU features sliced; 2 all-reduces per layer)" if sliced else f"replicas x{world}",
@@ -463,6 +465,8 @@ def main():
     parser.add_argument("--warmup", type=int, default=8)
     parser.add_argument("--impl", default="b200", choices=["b200", "reference"])
     parser.add_argument("--workload", default="c2", choices=["c1", "c2", "c3", "c4", "c5", "linear"])
+    parser.add_argument("--activations", default="f32", choices=["f32", "bf16"],
+                        help="bf16 decoders: precision of the activations between kernels in passes over more than 16 rows")
     parser.add_argument("--rows", type=int, default=16, help="linear only")
     parser.add_argument("--inner", type=int, default=768, help="linear only")
     parser.add_argument("--out", type=int, default=32000, help="linear only")

@@ -108,6 +108,7 @@ def _declare(l: C.CDLL) -> None:
         "dl_decoder_cache_length": (C.c_int, [vp, C.POINTER(i64)]),
         "dl_transformer_decoder_decode": (C.c_int, [vp, vp, vp, pp]),
         "dl_transformer_decoder_set_cache_dtype": (C.c_int, [vp, C.c_int]),
+        "dl_transformer_decoder_set_activation_dtype": (C.c_int, [vp, C.c_int]),
         "dl_transformer_decoder_set_adapters": (C.c_int, [vp, i64, vp, vp]),
         "dl_generation_create": (C.c_int, [vp, vp, vp, vp, i64, i64, pp]), "dl_generation_release": (None, [vp]),
         "dl_generation_prefill": (C.c_int, [vp, vp]), "dl_generation_step": (C.c_int, [vp, i64]),
@@ -328,7 +329,8 @@ class DecoderModel:
     through the C ABI from the canonical ordered tensor list (see ctorch_b200.workloads.tensor_shapes)."""
 
     def __init__(self, spec: dict, tensors: list[np.ndarray], lora: list[np.ndarray] | None = None, device: int = 0,
-                 cache_dtype: str | None = None, tensor_parallel: tuple[int, int] | None = None):
+                 cache_dtype: str | None = None, tensor_parallel: tuple[int, int] | None = None,
+                 activation_dtype: str | None = None):
         l = lib()
         self.spec = spec
         self.dev = cuda(device)
@@ -353,6 +355,8 @@ class DecoderModel:
             state[name] = Tensor.from_numpy(array, dtype=code)
         self.decoder.load_state(state)
         self.decoder.to(self.dev)
+        if activation_dtype is not None:
+            check(l.dl_transformer_decoder_set_activation_dtype(self.decoder.h, BF16 if activation_dtype == "bf16" else F32))
         if cache_dtype is not None:
             check(l.dl_transformer_decoder_set_cache_dtype(self.decoder.h, BF16 if cache_dtype == "bf16" else F32))
         table = Tensor.from_numpy(tensors[0], device=self.dev, dtype=code)

@@ -302,6 +302,9 @@ dl_status dl_transformer_decoder_decode(dl_module* decoder, const dl_tensor* inp
 }
 
 // ---- new entry points ---------------------------------------------------------------------------------------
+dl_status dl_transformer_decoder_set_activation_dtype(dl_module* decoder, dl_dtype dtype) {
+    return invoke([&] { as<dl::nn::TransformerDecoder>(decoder, "TransformerDecoder").set_activation_dtype(static_cast<dl::DType>(dtype)); });
+}
 dl_status dl_transformer_decoder_set_cache_dtype(dl_module* decoder, dl_dtype dtype) {
     return invoke([&] {
         if (dtype != DL_F32 && dtype != DL_BF16) throw std::invalid_argument("cache dtype must be f32 or bf16");

@@ -342,6 +342,10 @@ public:
     DType dtype() const { return dtype_; }
     TransformerDecoderLayer& layer(Index i) const { return *layers_[static_cast<std::size_t>(i)]; }
     const RMSNorm& normalization() const { return *normalization_; }
+    // f32 (default): activations between the kernels keep ~16 mantissa bits (bf16 hi + lo planes).  bf16: passes over more
+    // than 16 rows (prefill, large decode batches) feed the tensor cores the hi plane only.
+    void set_activation_dtype(DType dtype);
+    DType activation_dtype() const { return activation_dtype_; }
     void set_cache_dtype(DType dtype) { cache_dtype_ = dtype; }  // storage dtype of caches made by make_cache()
     // KV-head tensor parallelism: this object computes the slice `rank` of `world` (query heads, KV heads and SwiGLU
     // features are split evenly; norms, residual stream, embedding and logits stay replicated) and sums the partial
@@ -354,7 +358,7 @@ public:
 
 private:
     Index dimensions_, heads_, kv_heads_, hidden_, context_;
-    DType dtype_, cache_dtype_;
+    DType dtype_, cache_dtype_, activation_dtype_ = DType::f32;
     int tp_rank_ = 0, tp_world_ = 1;
     std::vector<std::shared_ptr<TransformerDecoderLayer>> layers_;
     std::shared_ptr<RMSNorm> normalization_;

@@ -363,6 +363,12 @@ TransformerDecoder::TransformerDecoder(Index layers, Index dimensions, Index hea
 }
 TransformerDecoder::~TransformerDecoder() = default;
 
+void TransformerDecoder::set_activation_dtype(DType dtype) {
+    if (dtype != DType::f32 && dtype != DType::bf16) throw std::invalid_argument("activation dtype must be f32 or bf16");
+    if (dtype == DType::bf16 && dtype_ != DType::bf16) throw std::invalid_argument("bf16 activations need a bf16 decoder");
+    activation_dtype_ = dtype;
+}
+
 void TransformerDecoder::set_tensor_parallel(int rank, int world) {
     if (world < 1 || rank < 0 || rank >= world) throw std::invalid_argument("tensor-parallel rank must lie in [0, world)");
     const Index hd = dimensions_ / heads_;

@@ -304,7 +304,8 @@ void DecodePlan::logits(const Linear& output, Index rows, float* out, void* stre
     const Index V = output.weight().size(0), D = owner_.dimensions();
     if (shadows_for(rows) && output.weight().dtype() == DType::bf16 && b200_linear_shadow_parts(rows, D, V) > 0) {
         b200_shadow_linear_args args{};
-        args.x_hi = hs_hi_.raw_data(); args.x_lo = hs_lo_.raw_data(); args.rows = rows; args.in = D;
+        args.x_hi = hs_hi_.raw_data(); args.rows = rows; args.in = D;
+        args.x_lo = owner_.activation_dtype() == DType::bf16 && rows >= 17 ? nullptr : hs_lo_.raw_data();
         args.weight = output.weight().raw_data(); args.out = V;
         args.sumsq_in = sq_attn_.data<float>(); args.parts_in = last_parts_; args.eps = owner_.normalization().epsilon();
         args.epilogue = B200_EPI_STORE; args.y = out;
@@ -339,7 +340,8 @@ void DecodePlan::choose(const Linear& output, Index rows, Index* next, Index* id
     if (parts <= 0 || !best_value_.defined() || best_value_.numel() < parts * rows)
         throw std::logic_error("fused logits + argmax was not prepared for this row count");
     b200_shadow_linear_args args{};
-    args.x_hi = hs_hi_.raw_data(); args.x_lo = hs_lo_.raw_data(); args.rows = rows; args.in = D;
+    args.x_hi = hs_hi_.raw_data(); args.rows = rows; args.in = D;
+    args.x_lo = owner_.activation_dtype() == DType::bf16 && rows >= 17 ? nullptr : hs_lo_.raw_data();
     args.weight = output.weight().raw_data(); args.out = V;
     args.sumsq_in = sq_attn_.data<float>(); args.parts_in = last_parts_; args.eps = owner_.normalization().epsilon();
     args.epilogue = B200_EPI_ARGMAX;
@@ -371,6 +373,9 @@ void DecodePlan::run_layers(const float* x, Index batch, Index length, std::span
         const int parts_down = parallel ? 1 : b200_linear_shadow_parts(rows, F, D);
         auto* sq_attn = static_cast<float*>(sq_attn_.mutable_data());
         auto* sq_ffn = static_cast<float*>(sq_ffn_.mutable_data());
+        // bf16 activations: the dense kernel (more than 16 rows) is given the hi plane only
+        const bool single_plane = owner_.activation_dtype() == DType::bf16 && rows >= 17;
+        auto lo_plane = [&](const Tensor& plane) -> const void* { return single_plane ? nullptr : plane.raw_data(); };
         // With symmetric memory mapped (and the rows fitting a slot) the projections write their partial rows into this
         // rank's slot and one kernel sums the ranks' slots over NVLink and rebuilds the shadow; otherwise NCCL.
         const bool peer_sum = parallel && runtime::tp_symmetric_ready(device, static_cast<std::size_t>(rows * D) * sizeof(float));
@@ -407,7 +412,7 @@ void DecodePlan::run_layers(const float* x, Index batch, Index length, std::span
             qkv.context = static_cast<int32_t>(a.rotary().cosine().size(0));
             qkv.cache = kv; qkv.q_out = static_cast<float*>(q_.mutable_data());
             b200_shadow_linear_args base{};
-            base.x_hi = hs_hi_.raw_data(); base.x_lo = hs_lo_.raw_data(); base.rows = rows; base.in = D;
+            base.x_hi = hs_hi_.raw_data(); base.x_lo = lo_plane(hs_lo_); base.rows = rows; base.in = D;
             base.sumsq_in = sq_attn; base.parts_in = parts_attn; base.eps = eps;
             if (packed.rank > 0) {
                 b200_shadow_linear_args low = base;
@@ -426,7 +431,7 @@ void DecodePlan::run_layers(const float* x, Index batch, Index length, std::span
             const Tensor* ffn_norm = layer.feedforward_norm().weight();
             const bool adds_residual = !parallel || rank == 0;
             b200_shadow_linear_args out_proj{};
-            out_proj.x_hi = att_hi_.raw_data(); out_proj.x_lo = att_lo_.raw_data(); out_proj.rows = rows; out_proj.in = Dl;
+            out_proj.x_hi = att_hi_.raw_data(); out_proj.x_lo = lo_plane(att_lo_); out_proj.rows = rows; out_proj.in = Dl;
             out_proj.weight = packed.wo; out_proj.out = D; out_proj.y = peer_sum ? runtime::tp_partial_slot(device, 0) : h;
             out_proj.epilogue = adds_residual ? B200_EPI_RESIDUAL : B200_EPI_STORE; out_proj.residual = adds_residual ? in : nullptr;
             if (!parallel) {
@@ -436,13 +441,13 @@ void DecodePlan::run_layers(const float* x, Index batch, Index length, std::span
             shadow_linear(out_proj, stream, "output projection");
             if (parallel) rebuild_shadow(ffn_norm, sq_ffn, 0);
             b200_shadow_linear_args gate_up{};
-            gate_up.x_hi = hs_hi_.raw_data(); gate_up.x_lo = hs_lo_.raw_data(); gate_up.rows = rows; gate_up.in = D;
+            gate_up.x_hi = hs_hi_.raw_data(); gate_up.x_lo = lo_plane(hs_lo_); gate_up.rows = rows; gate_up.in = D;
             gate_up.weight = packed.wgu.raw_data(); gate_up.out = 2 * Fl; gate_up.sumsq_in = sq_ffn; gate_up.parts_in = parts_o; gate_up.eps = eps;
             gate_up.epilogue = B200_EPI_SWIGLU; gate_up.out_hi = act_hi_.mutable_data(); gate_up.out_lo = act_lo_.mutable_data();
             shadow_linear(gate_up, stream, "gate/up projection");
             const Tensor* next_norm = i + 1 < owner_.layer_count() ? owner_.layer(i + 1).attention_norm().weight() : owner_.normalization().weight();
             b200_shadow_linear_args down{};
-            down.x_hi = act_hi_.raw_data(); down.x_lo = act_lo_.raw_data(); down.rows = rows; down.in = Fl;
+            down.x_hi = act_hi_.raw_data(); down.x_lo = lo_plane(act_lo_); down.rows = rows; down.in = Fl;
             down.weight = packed.wd; down.out = D; down.y = peer_sum ? runtime::tp_partial_slot(device, 1) : h;
             down.epilogue = adds_residual ? B200_EPI_RESIDUAL : B200_EPI_STORE; down.residual = adds_residual ? h : nullptr;
             if (!parallel) {

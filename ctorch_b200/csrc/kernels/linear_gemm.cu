@@ -161,6 +161,7 @@ __global__ void __launch_bounds__(kGemmThreads, STAGES == 2 && TN == 128 ? 2 : 1
     const int split = static_cast<int>(gridDim.z), part = static_cast<int>(blockIdx.z);
     const int all_blocks = (p.in + kBlockK - 1) / kBlockK;
     const int k_begin = all_blocks * part / split, k_blocks = all_blocks * (part + 1) / split - k_begin;
+    const bool has_lo = p.x_lo != nullptr;   // without the lo plane the activations count as bf16 (half the operand bytes and products)
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kStages; ++s) {
@@ -193,9 +194,9 @@ __global__ void __launch_bounds__(kGemmThreads, STAGES == 2 && TN == 128 ? 2 : 1
                 if (!mbar_wait(&empty[s], phase ^ 1)) { atomicExch(gp.status, B200_DEVICE_TIMEOUT); break; }
                 uint8_t* stage = smem + s * kStageBytes;
                 const int k0 = (k_begin + i) * kBlockK;
-                mbar_expect_tx(&full[s], kStageBytes);
+                mbar_expect_tx(&full[s], has_lo ? kStageBytes : kStageBytes - kBoxBytes);
                 tma_load_2d(stage, &map_hi, k0, m0, &full[s]);
-                tma_load_2d(stage + kBoxBytes, &map_lo, k0, m0, &full[s]);
+                if (has_lo) tma_load_2d(stage + kBoxBytes, &map_lo, k0, m0, &full[s]);
                 tma_load_2d(stage + 2 * kBoxBytes, &map_w, k0, n0, &full[s]);
             }
         }
@@ -214,7 +215,7 @@ __global__ void __launch_bounds__(kGemmThreads, STAGES == 2 && TN == 128 ? 2 : 1
                 for (int k = 0; k < kBlockK / 16; ++k) {
                     // advancing the start address by 32 bytes selects the next 16 columns inside the swizzled rows
                     tc_mma_bf16(tmem_base, hi + 2 * k, w + 2 * k, kInstruction, (i | k) != 0);
-                    tc_mma_bf16(tmem_base, lo + 2 * k, w + 2 * k, kInstruction, 1);
+                    if (has_lo) tc_mma_bf16(tmem_base, lo + 2 * k, w + 2 * k, kInstruction, 1);
                 }
                 tc_commit(&empty[s]);   // the stage may be refilled once these products have read it
             }
@@ -444,7 +445,7 @@ int linear_gemm_parts(int rows, int in, int out) {
 }
 
 int launch_linear_gemm(const LinearParams& p, int epilogue, cudaStream_t stream) {
-    if (p.weight_dtype != B200_BF16 || !p.x_hi || !p.x_lo || (p.in & 7) || (p.out_hi && (p.out & 1))
+    if (p.weight_dtype != B200_BF16 || !p.x_hi || (p.in & 7) || (p.out_hi && (p.out & 1))
         || ((reinterpret_cast<uintptr_t>(p.weight) | reinterpret_cast<uintptr_t>(p.x_hi) | reinterpret_cast<uintptr_t>(p.x_lo)) & 15))
         return B200_UNSUPPORTED;
     int device = 0;
@@ -453,7 +454,7 @@ int launch_linear_gemm(const LinearParams& p, int epilogue, cudaStream_t stream)
     alignas(64) CUtensorMap hi, lo, w;
     const int tn = choose_tile_features(p.rows, p.out);
     int status = encode_operand(&hi, p.x_hi, p.rows, p.in, kTileM);
-    if (status == B200_OK) status = encode_operand(&lo, p.x_lo, p.rows, p.in, kTileM);
+    if (status == B200_OK) status = encode_operand(&lo, p.x_lo ? p.x_lo : p.x_hi, p.rows, p.in, kTileM);
     if (status == B200_OK) status = encode_operand(&w, p.weight, p.out, p.in, tn);
     if (status != B200_OK) return status;
     const int stages = choose_stages(p.rows);

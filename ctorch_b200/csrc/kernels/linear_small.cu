@@ -265,7 +265,7 @@ extern "C" int b200_linear(const float* x, int64_t rows, int64_t in, const void*
 
 extern "C" int b200_linear_shadow(const b200_shadow_linear_args* args, void* stream) {
     using namespace b200;
-    if (!args || !args->x_hi || !args->x_lo || !args->weight || args->rows < 0 || args->in <= 0 || args->out <= 0
+    if (!args || !args->x_hi || !args->weight || args->rows < 0 || args->in <= 0 || args->out <= 0
         || args->rows > INT32_MAX || args->in > INT32_MAX || args->out > INT32_MAX) {
         set_error("b200_linear_shadow: bad pointer or size");
         return B200_BAD_ARGUMENT;

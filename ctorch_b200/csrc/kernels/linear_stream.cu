@@ -518,6 +518,7 @@ int linear_argmax_parts(int rows, int in, int out) {
 
 int launch_linear_stream(const LinearParams& p, int epilogue, cudaStream_t stream) {
     if (p.x_hi && (p.rows >= kGemmRows || p.in > kMaxIn)) return launch_linear_gemm(p, epilogue, stream);
+    if (p.x_hi && !p.x_lo) return B200_UNSUPPORTED;   // the streaming kernel always multiplies both planes
     if (p.weight_dtype != B200_BF16 || p.in > kMaxIn || (p.in & 7) || (reinterpret_cast<uintptr_t>(p.weight) & 15))
         return B200_UNSUPPORTED;
     if (p.x_hi ? ((reinterpret_cast<uintptr_t>(p.x_hi) | reinterpret_cast<uintptr_t>(p.x_lo)) & 15) || !p.x_lo

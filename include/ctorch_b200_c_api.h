@@ -147,6 +147,11 @@ DL_API dl_status dl_transformer_decoder_decode(dl_module* decoder, const dl_tens
 /* Storage dtype of caches created afterwards by dl_decoder_cache_create for this decoder: DL_F32 or DL_BF16.
  * Default: DL_BF16 for bf16 decoders, DL_F32 for f32 decoders (the reference always caches f32). */
 DL_API dl_status dl_transformer_decoder_set_cache_dtype(dl_module* decoder, dl_dtype dtype);
+/* Precision of the activations handed from kernel to kernel in a bf16 decoder.  DL_F32 (default): f32-equivalent (two bf16
+ * planes), as the reference keeps activations in f32 (src/ops/matmul.cpp:43).  DL_BF16: passes over more than 16 rows
+ * (prefill, large decode batches) use one bf16 plane - about half the tensor-core work, logits still within the 2e-2 bf16
+ * tolerance.  Single-token steps of up to 16 sequences are unaffected. */
+DL_API dl_status dl_transformer_decoder_set_activation_dtype(dl_module* decoder, dl_dtype dtype);
 /* Installs adapters (from dl_lora_linear_create) on the query and value projections of one layer; both NULL
  * removes them.  The reference can only host merged weights inside its decoder (include/dl/decoder.h:75). */
 DL_API dl_status dl_transformer_decoder_set_adapters(dl_module* decoder, int64_t layer, const dl_module* query,

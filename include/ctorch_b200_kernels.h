@@ -130,7 +130,8 @@ B200_API int b200_linear(const float* x, int64_t rows, int64_t in, const void* w
  * 1/sqrt(sum/width + eps).  The f32 arithmetic differs from the reference's f64 norm by rounding only. */
 typedef struct b200_shadow_linear_args {
     const void* x_hi;              /* bf16 [rows, in] */
-    const void* x_lo;
+    const void* x_lo;              /* may be NULL for calls the dense kernel serves (more than 16 rows or in > 2048): the
+                                      activations then count as bf16 - half the operand traffic and tensor-core work */
     int64_t rows, in;
     const void* weight;            /* bf16 [out, in] */
     int64_t out;

@@ -289,3 +289,24 @@ def test_sampled_steps_follow_the_oracle_draws():
     assert np.array_equal(gen.tokens()[:, -1], fed) and model.cache_length() == spec["prompt"] + spec["steps"] - 1
     with pytest.raises(B.B200Error, match="temperature"):
         gen.step_sampled(0.0, np.zeros(3))
+
+
+def test_bf16_activation_option_stays_within_the_bf16_tolerance():
+    """dl_transformer_decoder_set_activation_dtype(DL_BF16): prefill (more than 16 rows) runs on one activation plane; logits
+    stay within the bf16 budget of the oracle, single-token steps of a small batch are unchanged bit for bit."""
+    spec = dict(W.CONFIGS["c2"], layers=2, batch=4, prompt=40, steps=3)
+    spec["context"] = 64
+    weights = W.make_weights(spec, seed=17)
+    prompt = W.make_prompts(spec, seed=18)
+    cpu = oracle.CpuDecoder(spec, weights)
+    want = cpu.decode_ids(prompt)
+    full = B.DecoderModel(spec, weights)
+    half = B.DecoderModel(spec, weights, activation_dtype="bf16")
+    got_full, got_half = full.decode_ids(prompt), half.decode_ids(prompt)
+    assert rel(got_full, want) < BF16_TOL and rel(got_half, want) < BF16_TOL
+    assert not np.array_equal(got_full, got_half)           # the option really changes the arithmetic of the dense passes
+    step = prompt[:, :1]
+    half.truncate(0), full.truncate(0)
+    assert np.array_equal(full.decode_ids(step), half.decode_ids(step))   # 4 rows: streaming kernel, both planes
+    with pytest.raises(B.B200Error, match="bf16"):
+        B.DecoderModel(W.tiny("f32"), W.make_weights(W.tiny("f32")), activation_dtype="bf16")

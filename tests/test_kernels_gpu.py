@@ -602,3 +602,31 @@ def test_peer_memory_sum_gives_up_when_a_rank_never_arrives():
     assert status.value == 0
     x = torch.ones((4,), device="cuda") * 2
     assert float(x.sum()) == 8.0
+
+
+@pytest.mark.parametrize("rows,inner,out", [(40, 768, 1280), (256, 2048, 3072), (32, 4096, 1024)])
+def test_dense_linear_with_single_plane_activations(rows, inner, out):
+    """x_lo = NULL: the dense kernel multiplies the hi plane only, i.e. activations rounded to bf16.  The result must equal
+    the oracle's linear of the ROUNDED activations to f32 accuracy, and the unrounded one within bf16 resolution."""
+    l = B.lib()
+    rng = np.random.default_rng(rows + out)
+    x = rng.standard_normal((rows, inner), dtype=np.float32)
+    w = W.bf16_bits(0.05 * rng.standard_normal((out, inner), dtype=np.float32))
+    xd, wd = dev(x), bf16_dev(w)
+    hi = torch.zeros((rows, inner), dtype=torch.bfloat16, device="cuda")
+    lo = torch.zeros_like(hi)
+    sq = torch.zeros((1, rows), dtype=torch.float32, device="cuda")
+    y = torch.zeros((rows, out), dtype=torch.float32, device="cuda")
+    torch.cuda.synchronize()
+    B.kcheck(l.b200_shadow_from_rows(xd.data_ptr(), rows, inner, None, 0, hi.data_ptr(), lo.data_ptr(), sq.data_ptr(), stream()))
+    args = B.ShadowLinearArgs(hi.data_ptr(), None, rows, inner, wd.data_ptr(), out, None, 0, 0.0, 0, None, None, y.data_ptr(),
+                              None, None, None, 0, None, None, None)
+    B.kcheck(l.b200_linear_shadow(C.byref(args), stream()))
+    sync()
+    rounded = W.bf16_to_f32(W.bf16_bits(x))
+    assert rel(y.cpu().numpy(), oracle.linear(rounded, w)) < 3e-5
+    assert rel(y.cpu().numpy(), oracle.linear(x, w)) < 1e-2
+    # up to 16 rows the streaming kernel serves the call and needs both planes
+    args = B.ShadowLinearArgs(hi.data_ptr(), None, 8, 768, wd.data_ptr(), 64, None, 0, 0.0, 0, None, None, y.data_ptr(),
+                              None, None, None, 0, None, None, None)
+    assert l.b200_linear_shadow(C.byref(args), stream()) != 0
