@@ -89,6 +89,26 @@ __device__ __forceinline__ void linear_epilogue(const LinearParams& p, int row, 
             const float* low = p.low + static_cast<int64_t>(row) * 2 * p.lora_rank + (region == 2 ? p.lora_rank : 0);
             const void* up = region == 0 ? p.q_up : p.v_up;
             float da = 0.0f, db = 0.0f;
+            if (p.weight_dtype == B200_BF16 && (p.lora_rank & 7) == 0) {
+                // 16-byte loads: eight up-projection weights of each feature and eight low-rank activations per step; the
+                // products are added in the same order as the scalar loop below (j ascending)
+                const uint4* ua = reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(up) + static_cast<int64_t>(local) * p.lora_rank);
+                const uint4* ub = ua + (p.lora_rank >> 3);
+                const float4* lv = reinterpret_cast<const float4*>(low);
+                for (int j = 0; j < (p.lora_rank >> 3); ++j) {
+                    const uint4 wa = __ldg(ua + j), wb = __ldg(ub + j);
+                    const float4 l0 = __ldg(lv + 2 * j), l1 = __ldg(lv + 2 * j + 1);
+                    const float l[8] = {l0.x, l0.y, l0.z, l0.w, l1.x, l1.y, l1.z, l1.w};
+                    const uint32_t pa[4] = {wa.x, wa.y, wa.z, wa.w}, pb[4] = {wb.x, wb.y, wb.z, wb.w};
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        da = __fadd_rn(da, __fmul_rn(l[2 * i], __uint_as_float(pa[i] << 16)));
+                        db = __fadd_rn(db, __fmul_rn(l[2 * i], __uint_as_float(pb[i] << 16)));
+                        da = __fadd_rn(da, __fmul_rn(l[2 * i + 1], __uint_as_float(pa[i] & 0xffff0000u)));
+                        db = __fadd_rn(db, __fmul_rn(l[2 * i + 1], __uint_as_float(pb[i] & 0xffff0000u)));
+                    }
+                }
+            } else
             for (int j = 0; j < p.lora_rank; ++j) {
                 const int64_t at = static_cast<int64_t>(local) * p.lora_rank + j;
                 const float ua = p.weight_dtype == B200_BF16 ? load_as_f32(static_cast<const __nv_bfloat16*>(up), at)

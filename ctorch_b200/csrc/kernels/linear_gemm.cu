@@ -235,6 +235,7 @@ __global__ void __launch_bounds__(kGemmThreads, STAGES == 2 && TN == 128 ? 2 : 1
     constexpr int kTileStride = kTileN + 4;
     float* tile = reinterpret_cast<float*>(smem);
     float* row_scale = reinterpret_cast<float*>(smem + kStages * kStageBytes + 512);   // 128 floats behind the barriers
+    volatile int* tile_ready = reinterpret_cast<volatile int*>(smem + kStages * kStageBytes + 256);   // one flag per epilogue warp
     const bool finisher = warp >= 2;
     const int quarter = warp & 3;
     bool ready = false;
@@ -263,15 +264,18 @@ __global__ void __launch_bounds__(kGemmThreads, STAGES == 2 && TN == 128 ? 2 : 1
                                           __uint_as_float(r[4 * j + 3]));
             }
         }
-        asm volatile("bar.sync 2, 128;" ::: "memory");   // the four epilogue warps: the whole tile is in shared memory
+        if (lane == 0) tile_ready[quarter] = ready ? 1 : 0;
     }
-    if (split > 1) {
-        __syncwarp();
-        cluster_sync_all();   // every CTA's partial tile is complete and visible to its peers
-    }
-    if (finisher) {
-        const int rows_each = (kTileM + split - 1) / split;
-        const int first = part * rows_each, last = min(kTileM, first + rows_each);
+    __syncwarp();
+    if (split > 1) cluster_sync_all();   // every CTA's partial tile is complete and visible to its peers
+    else __syncthreads();                // the whole tile is in shared memory
+    {
+        // All six warps finish rows (the producer and the issuing warp are idle by now).  Only rows that exist are divided
+        // over the cluster's CTAs: a decode batch of 32 rows keeps every CTA of the cluster busy.
+        ready = tile_ready[0] && tile_ready[1] && tile_ready[2] && tile_ready[3];
+        const int rows_here = min(kTileM, p.rows - m0);
+        const int rows_each = (rows_here + split - 1) / split;
+        const int first = part * rows_each, last = min(rows_here, first + rows_each);
         uint32_t peer_tile[8];
         peer_tile[0] = smem_u32(tile);
         if (split > 1) {
@@ -282,8 +286,7 @@ __global__ void __launch_bounds__(kGemmThreads, STAGES == 2 && TN == 128 ? 2 : 1
         // from shared memory or from the peers, residual pairs from global memory), then the rows are finished, so the
         // memory round trips of the rows overlap instead of queueing behind each other.
         constexpr int kBatch = 4, kPasses = kTileN / 64;
-        for (int base = first + quarter * kBatch; base < last; base += 4 * kBatch) {
-            if (m0 + base >= p.rows) break;   // rows grow with base
+        for (int base = first + warp * kBatch; base < last; base += (kGemmThreads / 32) * kBatch) {
             float2 value[kBatch][kPasses], carried[kBatch][kPasses];
 #pragma unroll
             for (int r = 0; r < kBatch; ++r) {

@@ -155,9 +155,11 @@ def test_state_dict_names_follow_the_reference():
     assert np.array_equal(state["layer1.attention.rotary.sine"].numpy(), sin)
 
 
-@pytest.mark.parametrize("dtype", ["f32", "bf16"])
-def test_adapters_match_oracle(dtype):
-    spec = W.tiny(dtype, lora_rank=4, lora_alpha=8.0, d_model=64, heads=4, kv_heads=2)
+@pytest.mark.parametrize("dtype,rank", [("f32", 4), ("bf16", 4), ("bf16", 16)])
+def test_adapters_match_oracle(dtype, rank):
+    """rank 4 takes the scalar adapter loop of the projection epilogue, rank 16 (bf16) the 16-byte vector loads; prefill
+    chunks of more than 16 rows run on the tcgen05 kernel, the single-token chunks on the streaming kernel."""
+    spec = W.tiny(dtype, lora_rank=rank, lora_alpha=2.0 * rank, d_model=64, heads=4, kv_heads=2, batch=4 if rank == 16 else 2)
     weights, lora = W.make_weights(spec, seed=21, scale=0.08), W.make_lora(spec)
     model = B.DecoderModel(spec, weights, lora=lora)
     port = oracle.CpuDecoder(spec, weights, lora=lora)
