@@ -52,15 +52,52 @@ def tensor_peak_tflops() -> float:
 
 
 class ClockSampler:
-    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    """SM clock and throttle reasons of one GPU while the timed region runs: NVML read from a thread every few
+    milliseconds (the timed loops last tens of milliseconds), nvidia-smi as a fall-back.  Read-only."""
 
     QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    REASON_BITS = {0x8: "hw_slowdown", 0x40: "hw_thermal_slowdown", 0x20: "sw_thermal_slowdown", 0x4: "sw_power_cap"}
 
     def __init__(self, index: int):
         self.index, self.rows, self.process = index, [], None
+        self.samples, self.thread, self.running, self.nvml, self.first = [], None, False, None, 0
+
+    def mark(self):
+        """The timed region starts here: earlier NVML samples (set-up, warm-up) are left out of the summary."""
+        self.first = len(self.samples)
+
+    def _visible_index(self) -> int:
+        """Index of the CUDA device among the GPUs NVML sees (CUDA_VISIBLE_DEVICES may renumber them)."""
+        visible = os.environ.get("CUDA_VISIBLE_DEVICES", "")
+        entries = [e for e in visible.split(",") if e.strip()]
+        if entries and self.index < len(entries) and entries[self.index].strip().isdigit():
+            return int(entries[self.index])
+        return self.index
 
     def start(self):
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            handle = pynvml.nvmlDeviceGetHandleByIndex(self._visible_index())
+            maximum = float(pynvml.nvmlDeviceGetMaxClockInfo(handle, pynvml.NVML_CLOCK_SM))
+            self.nvml, self.running = pynvml, True
+
+            def poll():
+                while self.running:
+                    try:
+                        clock = float(pynvml.nvmlDeviceGetClockInfo(handle, pynvml.NVML_CLOCK_SM))
+                        reasons = int(pynvml.nvmlDeviceGetCurrentClocksThrottleReasons(handle))
+                        self.samples.append((clock, maximum, reasons))
+                    except Exception:  # noqa: BLE001
+                        break
+                    time.sleep(0.002)
+
+            self.thread = threading.Thread(target=poll, daemon=True)
+            self.thread.start()
+            return
+        except Exception:  # noqa: BLE001
+            self.nvml = None
         try:
             self.process = subprocess.Popen(["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.QUERY}",
                                              "--format=csv,noheader,nounits", "-lms", "100"], stdout=subprocess.PIPE,
@@ -74,13 +111,25 @@ class ClockSampler:
             self.rows.append([cell.strip() for cell in line.split(",")])
 
     def stop(self) -> dict:
+        clocks, maxima, reasons = [], [], set()
+        if self.nvml is not None:
+            self.running = False
+            if self.thread:
+                self.thread.join(timeout=2)
+            for clock, maximum, bits in self.samples[self.first:] or self.samples[-1:]:
+                clocks.append(clock)
+                maxima.append(maximum)
+                reasons.update(name for bit, name in self.REASON_BITS.items() if bits & bit)
+            try:
+                self.nvml.nvmlShutdown()
+            except Exception:  # noqa: BLE001
+                pass
         if self.process:
             self.process.terminate()
             try:
                 self.process.wait(timeout=5)
             except subprocess.TimeoutExpired:
                 self.process.kill()
-        clocks, maxima, reasons = [], [], set()
         for row in self.rows:
             try:
                 clocks.append(float(row[0]))
@@ -195,6 +244,7 @@ def run_b200(args, spec, weights) -> dict:
     B.synchronize(local)
     start_length = model.cache_length()
     barrier(dist, local)
+    sampler.mark()
     B.timer_start(local)
     gen.step(args.steps)
     device_ms = B.timer_stop(local)

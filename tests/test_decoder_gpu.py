@@ -312,3 +312,25 @@ def test_bf16_activation_option_stays_within_the_bf16_tolerance():
     assert np.array_equal(full.decode_ids(step), half.decode_ids(step))   # 4 rows: streaming kernel, both planes
     with pytest.raises(B.B200Error, match="bf16"):
         B.DecoderModel(W.tiny("f32"), W.make_weights(W.tiny("f32")), activation_dtype="bf16")
+
+
+@pytest.mark.parametrize("name,overrides", [
+    ("c4", dict(layers=2, batch=17, prompt=6, steps=3)),                       # 1B shape at full width, 17 rows: tcgen05 decode
+    ("c5", dict(layers=1, batch=18, prompt=5, steps=2, vocab=4096)),           # 8B shape at full width with adapters, small vocabulary
+])
+def test_full_width_large_configurations_match_oracle(name, overrides):
+    """BASELINE configurations 4 and 5 at their full layer width (d 2048 / 4096, 32 query / 8 KV heads, SwiGLU 8192 / 14336,
+    rank-16 adapters on configuration 5) with few layers and short prompts, so that the CPU oracle finishes in seconds:
+    prefill and single-token steps of more than 16 sequences (the tcgen05 path with K-split clusters) within the bf16 budget."""
+    spec = dict(W.CONFIGS[name], **overrides)
+    spec["context"] = spec["prompt"] + spec["steps"] + 2
+    weights = W.make_weights(spec, seed=31)
+    lora = W.make_lora(spec, seed=32)
+    prompt = W.make_prompts(spec, seed=33)
+    model = B.DecoderModel(spec, weights, lora=lora)
+    cpu = oracle.CpuDecoder(spec, weights, lora=lora)
+    assert rel(model.decode_ids(prompt), cpu.decode_ids(prompt)) < BF16_TOL
+    for step in range(spec["steps"]):
+        ids = prompt[:, step:step + 1]
+        assert rel(model.decode_ids(ids), cpu.decode_ids(ids)) < BF16_TOL, step
+    assert model.cache_length() == spec["prompt"] + spec["steps"]
