@@ -4,6 +4,9 @@
 // together, so every K/V byte is read once per item.  The key range of an item is cut into splits of
 // `pages_per_split` pages (grid.y); each CTA produces a partial (max, sum, accumulator) triple per head in the
 // caller's scratch buffer and a second small kernel merges the splits.  The work is KV streaming (HBM-bound).
+// Chunks of several positions per sequence (prefill) put 16 / G consecutive positions into one item of the fast path:
+// the 16 fragment rows of the tensor-core products are positions x heads, each row with its own causal key count,
+// so the K/V bytes of a sequence are streamed 16 / G times less often than with one item per position.
 //
 // Fast path (bf16 pools, 64-token pages, head_dim 64 or 128): a producer warp stages K and V pages with
 // non-multicast TMA (cp.async.bulk.tensor, 128-byte swizzle) through a ring of shared-memory stages guarded by
@@ -28,6 +31,7 @@ namespace {
 struct AttnParams {
     const float* q;    // [rows, heads, head_dim]
     int rows, tokens_per_sequence, heads, causal;
+    int positions_per_item;   // tensor-core kernel: consecutive positions of one sequence that share a CTA (1 in decode)
     KvView kv;
     int pages_per_split, num_splits;
     float* part_o;     // [rows*heads, num_splits, head_dim]
@@ -130,10 +134,18 @@ __global__ void __launch_bounds__(kFastThreads) attention_mma_kernel(const __gri
     grid_dependency_wait();   // q, the cache and the lengths come from the preceding kernels
     trace_mark(trace, 1);
     grid_launch_dependents();
+    // An item is (sequence, block of consecutive positions, KV head).  The 16 fragment rows of a warp hold the block's
+    // positions times the head group: row r = position r / group, query head r % group.  Decode: one position, rows =
+    // the group.  Prefill: 16 / group positions share every K/V byte the CTA streams.
     const int item = blockIdx.x, split = blockIdx.y;
-    const int row = item / p.kv.kv_heads, kvh = item % p.kv.kv_heads;
-    const int sequence = row / p.tokens_per_sequence;
-    const int kv_len = p.kv.lengths[sequence] + (p.causal ? row % p.tokens_per_sequence + 1 : 0);
+    const int kvh = item % p.kv.kv_heads, block = item / p.kv.kv_heads;
+    const int blocks_per_sequence = (p.tokens_per_sequence + p.positions_per_item - 1) / p.positions_per_item;
+    const int sequence = block / blocks_per_sequence;
+    const int t_first = (block - sequence * blocks_per_sequence) * p.positions_per_item;
+    const int t_count = min(p.positions_per_item, p.tokens_per_sequence - t_first);
+    const int row = sequence * p.tokens_per_sequence + t_first;   // first activation row of the item
+    const int base_len = p.kv.lengths[sequence];
+    const int kv_len = base_len + (p.causal ? t_first + t_count : 0);   // keys the item's last position sees
     int page_end = (kv_len + kFastPageSize - 1) / kFastPageSize;
     const int per_split = balanced_pages_per_split(page_end, p.pages_per_split);
     const int page_begin = split * per_split;
@@ -188,10 +200,14 @@ __global__ void __launch_bounds__(kFastThreads) attention_mma_kernel(const __gri
         // ---- consumers ----
         const int g = lane >> 2, t = lane & 3;
         uint32_t qa[HD / 16][4];
+        // this thread's two fragment rows: position and head inside the item, and the keys each may see
+        const int pos0 = g / group, pos1 = (g + 8) / group;
+        const bool v0 = g < group * t_count, v1 = g + 8 < group * t_count;
+        const int limit0 = v0 ? base_len + (p.causal ? t_first + pos0 + 1 : 0) : 0;
+        const int limit1 = v1 ? base_len + (p.causal ? t_first + pos1 + 1 : 0) : 0;
         {
-            const float* q0 = p.q + (static_cast<int64_t>(row) * p.heads + kvh * group + g) * HD;
-            const float* q1 = q0 + 8 * HD;
-            const bool v0 = g < group, v1 = g + 8 < group;
+            const float* q0 = p.q + (static_cast<int64_t>(row + pos0) * p.heads + kvh * group + (g - pos0 * group)) * HD;
+            const float* q1 = p.q + (static_cast<int64_t>(row + pos1) * p.heads + kvh * group + (g + 8 - pos1 * group)) * HD;
 #pragma unroll
             for (int kk = 0; kk < HD / 16; ++kk) {
                 const int c = kk * 16 + 2 * t;
@@ -236,7 +252,7 @@ __global__ void __launch_bounds__(kFastThreads) attention_mma_kernel(const __gri
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
                     const int token = token_base + n * 8 + (e & 1);
-                    const float v = token < kv_len ? sc[n][e] * p.scale : -INFINITY;
+                    const float v = token < ((e >> 1) ? limit1 : limit0) ? sc[n][e] * p.scale : -INFINITY;
                     sc[n][e] = v;
                     mx[e >> 1] = fmaxf(mx[e >> 1], v);
                 }
@@ -296,7 +312,7 @@ __global__ void __launch_bounds__(kFastThreads) attention_mma_kernel(const __gri
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
             const int r = g + 8 * h;
-            if (r < group) {
+            if (r < group * t_count) {
                 float* dst = merge_o + (warp * 16 + r) * HD + 2 * t;
 #pragma unroll
                 for (int j = 0; j < HD / 8; ++j) {
@@ -311,7 +327,7 @@ __global__ void __launch_bounds__(kFastThreads) attention_mma_kernel(const __gri
         }
     }
     __syncthreads();
-    for (int i = threadIdx.x; i < group * HD; i += kFastThreads) {
+    for (int i = threadIdx.x; i < group * t_count * HD; i += kFastThreads) {
         const int r = i / HD, d = i - r * HD;
         float m = -INFINITY;
 #pragma unroll
@@ -324,7 +340,8 @@ __global__ void __launch_bounds__(kFastThreads) attention_mma_kernel(const __gri
             acc += weight * merge_o[(w * 16 + r) * HD + d];
             l += weight * merge_ml[(w * 16 + r) * 2 + 1];
         }
-        const int64_t head_item = static_cast<int64_t>(row) * p.heads + kvh * group + r;
+        const int position = r / group;
+        const int64_t head_item = static_cast<int64_t>(row + position) * p.heads + kvh * group + (r - position * group);
         if (p.num_splits == 1) {
             store_result(p, head_item * HD + d, acc / l);
         } else {
@@ -447,7 +464,8 @@ template <int HD, int STAGES> int launch_fast(const b200_kv_cache* cache, const 
     using S = FastShape<HD, STAGES>;
     auto kernel = attention_mma_kernel<HD, STAGES>;
     B200_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, S::smem_bytes));
-    const dim3 grid(static_cast<unsigned>(p.rows) * p.kv.kv_heads, p.num_splits);
+    const int blocks_per_sequence = (p.tokens_per_sequence + p.positions_per_item - 1) / p.positions_per_item;
+    const dim3 grid(static_cast<unsigned>(p.rows / p.tokens_per_sequence) * blocks_per_sequence * p.kv.kv_heads, p.num_splits);
     return cuda_status(launch_dependent(kernel, grid, dim3(kFastThreads), S::smem_bytes, stream, *kv_tensor_map(cache, 0),
                                         *kv_tensor_map(cache, 1), p), "attention_mma_kernel launch");
 }
@@ -476,7 +494,16 @@ int attention_launch(const float* q, int64_t rows, int32_t tokens_per_sequence, 
     }
     if (cache->head_dim > 32 * kMaxDimsPerLane) { set_error("b200_attention_decode: head_dim above 256 is not supported"); return B200_UNSUPPORTED; }
     if (max_length > cache->capacity) max_length = cache->capacity;
-    const SplitPlan plan = plan_splits(rows, cache->kv_heads, max_length, cache->page_size);
+    const int group = heads / cache->kv_heads;
+    const bool fast = kv_tensor_map(cache, 0) && group <= 16 && (cache->head_dim == 64 || cache->head_dim == 128);
+    // Chunks of several positions (prefill) on the tensor-core kernel: 16 / group consecutive positions share a CTA and one
+    // CTA walks all pages of its item (the split sizes of the merge kernel are per row, the items' are per block).
+    const int positions = fast && tokens_per_sequence > 1 ? (16 / group > 0 ? 16 / group : 1) : 1;
+    SplitPlan plan = plan_splits(rows, cache->kv_heads, max_length, cache->page_size);
+    if (positions > 1) {
+        plan.pages_per_split = plan.pages_total;
+        plan.num_splits = 1;
+    }
     const size_t need = b200_attention_scratch_bytes(rows, heads, cache->kv_heads, cache->head_dim, max_length, cache->page_size);
     if (plan.num_splits > 1 && (!scratch || scratch_bytes < need)) {
         set_error("b200_attention_decode: scratch of %zu bytes needed, %zu given", need, scratch_bytes);
@@ -484,6 +511,7 @@ int attention_launch(const float* q, int64_t rows, int32_t tokens_per_sequence, 
     }
     AttnParams p{};
     p.q = q; p.rows = static_cast<int>(rows); p.tokens_per_sequence = tokens_per_sequence; p.heads = heads; p.causal = causal;
+    p.positions_per_item = positions;
     p.kv = kv_view(cache);
     p.pages_per_split = plan.pages_per_split; p.num_splits = plan.num_splits;
     p.part_o = static_cast<float*>(scratch);
@@ -492,14 +520,14 @@ int attention_launch(const float* q, int64_t rows, int32_t tokens_per_sequence, 
     p.scale = static_cast<float>(1.0 / std::sqrt(static_cast<double>(cache->head_dim)));
     p.status = device_status_word(cache->device);
     cudaStream_t s = as_stream(stream);
-    const int group = heads / cache->kv_heads;
     int status;
-    if (kv_tensor_map(cache, 0) && group <= 16 && (cache->head_dim == 64 || cache->head_dim == 128)) {
+    if (fast) {
         // head_dim 64 with more CTAs than SMs: a 96 KB ring lets two CTAs share an SM, so one CTA's pipeline ramp and
         // drain overlap the other's streaming; with fewer CTAs each keeps the deeper ring to itself.
         int device = 0;
         B200_CUDA(cudaGetDevice(&device));
-        const int64_t ctas = static_cast<int64_t>(p.rows) * p.kv.kv_heads * p.num_splits;
+        const int64_t ctas = (static_cast<int64_t>(p.rows) / tokens_per_sequence) * ((tokens_per_sequence + positions - 1) / positions)
+                             * p.kv.kv_heads * p.num_splits;
         if (cache->head_dim == 128) status = launch_fast<128, 6>(cache, p, s);
         else if (ctas > sm_count(device)) status = launch_fast<64, 6>(cache, p, s);
         else status = launch_fast<64, 8>(cache, p, s);
