@@ -140,6 +140,92 @@ __device__ __forceinline__ void finish_pair(const LinearParams& p, int row, int 
     }
 }
 
+// Finishes the rows [first, last) of a tile held row-major in shared memory (`tile`, or the sum over the cluster's
+// `split` partial tiles `peer_tile[z]`).  Warp `worker` of `workers` takes kBatch consecutive rows per iteration: first
+// every value the rows need is requested (accumulators from shared memory or from the peers, residual pairs from global
+// memory), then the rows are finished, so the memory round trips of the rows overlap instead of queueing behind each
+// other.  Lanes run across the feature pairs: every global access is coalesced; per-row reductions are butterflies.
+template <int EPI, int kTileN>
+__device__ __forceinline__ void finish_rows(const LinearParams& p, const float* tile, const uint32_t (&peer_tile)[8], int split,
+                                            const float* row_scale, int m0, int n0, int feature_tile, int first, int last, int worker,
+                                            int workers, int lane, bool ready) {
+    constexpr int kTileStride = kTileN + 4;
+        constexpr int kBatch = 4, kPasses = kTileN / 64;
+        for (int base = first + worker * kBatch; base < last; base += workers * kBatch) {
+            float2 value[kBatch][kPasses], carried[kBatch][kPasses];
+#pragma unroll
+            for (int r = 0; r < kBatch; ++r) {
+                const int tile_row = base + r, row = m0 + tile_row;
+                const bool live_row = tile_row < last && row < p.rows;
+#pragma unroll
+                for (int pass = 0; pass < kPasses; ++pass) {
+                    const int c = pass * 64 + lane * 2;
+                    const int feature0 = n0 + c;
+                    value[r][pass] = make_float2(0.0f, 0.0f);
+                    carried[r][pass] = make_float2(0.0f, 0.0f);
+                    if (!live_row) continue;
+                    if (split == 1) {
+                        value[r][pass] = *reinterpret_cast<const float2*>(tile + tile_row * kTileStride + c);
+                    } else {
+                        const uint32_t offset = static_cast<uint32_t>(tile_row * kTileStride + c) * 4;
+                        float2 v[8];
+#pragma unroll
+                        for (int z = 0; z < 8; ++z) v[z] = z < split ? load_cluster_float2(peer_tile[z] + offset) : make_float2(0.0f, 0.0f);
+                        float2 sum = v[0];
+#pragma unroll
+                        for (int z = 1; z < 8; ++z) { sum.x += v[z].x; sum.y += v[z].y; }
+                        value[r][pass] = sum;
+                    }
+                    if constexpr (EPI == B200_EPI_RESIDUAL) {
+                        if (feature0 < p.out) {
+                            const float* source = p.residual + static_cast<int64_t>(row) * p.out + feature0;
+                            if ((p.out & 1) == 0) carried[r][pass] = *reinterpret_cast<const float2*>(source);
+                            else carried[r][pass] = make_float2(source[0], feature0 + 1 < p.out ? source[1] : 0.0f);
+                        }
+                    }
+                }
+            }
+#pragma unroll
+            for (int r = 0; r < kBatch; ++r) {
+                const int tile_row = base + r, row = m0 + tile_row;
+                if (tile_row >= last || row >= p.rows) break;
+                const float scale = row_scale[tile_row];
+                float squares = 0.0f;
+                Candidate best{-INFINITY, INT32_MAX};
+#pragma unroll
+                for (int pass = 0; pass < kPasses; ++pass) {
+                    const int feature0 = n0 + pass * 64 + lane * 2;
+                    if (!ready || feature0 >= p.out) continue;
+                    const float a = value[r][pass].x * scale, b = value[r][pass].y * scale;
+                    if constexpr (EPI == B200_EPI_ARGMAX) {
+                        const Candidate pair = pair_candidate(feature0, a, b, p.out);
+                        if (preferred(pair, best)) best = pair;
+                    } else {
+                        finish_pair<EPI>(p, row, feature0, a, b, carried[r][pass], squares);
+                    }
+                }
+                if constexpr (EPI == B200_EPI_RESIDUAL) {
+                    if (p.sumsq_out) {
+#pragma unroll
+                        for (int o = 16; o > 0; o >>= 1) squares += __shfl_xor_sync(0xffffffffu, squares, o);
+                        if (lane == 0) p.sumsq_out[static_cast<int64_t>(feature_tile) * p.rows + row] = squares;
+                    }
+                }
+                if constexpr (EPI == B200_EPI_ARGMAX) {
+#pragma unroll
+                    for (int o = 16; o > 0; o >>= 1) {
+                        const Candidate other{__shfl_xor_sync(0xffffffffu, best.value, o), __shfl_xor_sync(0xffffffffu, best.index, o)};
+                        if (preferred(other, best)) best = other;
+                    }
+                    if (lane == 0) {
+                        p.best_value[static_cast<int64_t>(feature_tile) * p.rows + row] = best.value;
+                        p.best_index[static_cast<int64_t>(feature_tile) * p.rows + row] = best.index;
+                    }
+                }
+            }
+        }
+    }
+
 template <int EPI, int TN, int STAGES>
 __global__ void __launch_bounds__(kGemmThreads, STAGES == 2 && TN == 128 ? 2 : 1) linear_gemm_kernel(const __grid_constant__ CUtensorMap map_hi,
                                                                       const __grid_constant__ CUtensorMap map_lo,
@@ -282,83 +368,7 @@ __global__ void __launch_bounds__(kGemmThreads, STAGES == 2 && TN == 128 ? 2 : 1
 #pragma unroll
             for (int z = 0; z < 8; ++z) peer_tile[z] = z < split ? map_peer_shared(smem_u32(tile), static_cast<uint32_t>(z)) : 0u;
         }
-        // A warp takes kBatch consecutive rows per iteration: first every value the rows need is requested (accumulators
-        // from shared memory or from the peers, residual pairs from global memory), then the rows are finished, so the
-        // memory round trips of the rows overlap instead of queueing behind each other.
-        constexpr int kBatch = 4, kPasses = kTileN / 64;
-        for (int base = first + warp * kBatch; base < last; base += (kGemmThreads / 32) * kBatch) {
-            float2 value[kBatch][kPasses], carried[kBatch][kPasses];
-#pragma unroll
-            for (int r = 0; r < kBatch; ++r) {
-                const int tile_row = base + r, row = m0 + tile_row;
-                const bool live_row = tile_row < last && row < p.rows;
-#pragma unroll
-                for (int pass = 0; pass < kPasses; ++pass) {
-                    const int c = pass * 64 + lane * 2;
-                    const int feature0 = n0 + c;
-                    value[r][pass] = make_float2(0.0f, 0.0f);
-                    carried[r][pass] = make_float2(0.0f, 0.0f);
-                    if (!live_row) continue;
-                    if (split == 1) {
-                        value[r][pass] = *reinterpret_cast<const float2*>(tile + tile_row * kTileStride + c);
-                    } else {
-                        const uint32_t offset = static_cast<uint32_t>(tile_row * kTileStride + c) * 4;
-                        float2 v[8];
-#pragma unroll
-                        for (int z = 0; z < 8; ++z) v[z] = z < split ? load_cluster_float2(peer_tile[z] + offset) : make_float2(0.0f, 0.0f);
-                        float2 sum = v[0];
-#pragma unroll
-                        for (int z = 1; z < 8; ++z) { sum.x += v[z].x; sum.y += v[z].y; }
-                        value[r][pass] = sum;
-                    }
-                    if constexpr (EPI == B200_EPI_RESIDUAL) {
-                        if (feature0 < p.out) {
-                            const float* source = p.residual + static_cast<int64_t>(row) * p.out + feature0;
-                            if ((p.out & 1) == 0) carried[r][pass] = *reinterpret_cast<const float2*>(source);
-                            else carried[r][pass] = make_float2(source[0], feature0 + 1 < p.out ? source[1] : 0.0f);
-                        }
-                    }
-                }
-            }
-#pragma unroll
-            for (int r = 0; r < kBatch; ++r) {
-                const int tile_row = base + r, row = m0 + tile_row;
-                if (tile_row >= last || row >= p.rows) break;
-                const float scale = row_scale[tile_row];
-                float squares = 0.0f;
-                Candidate best{-INFINITY, INT32_MAX};
-#pragma unroll
-                for (int pass = 0; pass < kPasses; ++pass) {
-                    const int feature0 = n0 + pass * 64 + lane * 2;
-                    if (!ready || feature0 >= p.out) continue;
-                    const float a = value[r][pass].x * scale, b = value[r][pass].y * scale;
-                    if constexpr (EPI == B200_EPI_ARGMAX) {
-                        const Candidate pair = pair_candidate(feature0, a, b, p.out);
-                        if (preferred(pair, best)) best = pair;
-                    } else {
-                        finish_pair<EPI>(p, row, feature0, a, b, carried[r][pass], squares);
-                    }
-                }
-                if constexpr (EPI == B200_EPI_RESIDUAL) {
-                    if (p.sumsq_out) {
-#pragma unroll
-                        for (int o = 16; o > 0; o >>= 1) squares += __shfl_xor_sync(0xffffffffu, squares, o);
-                        if (lane == 0) p.sumsq_out[static_cast<int64_t>(blockIdx.y) * p.rows + row] = squares;
-                    }
-                }
-                if constexpr (EPI == B200_EPI_ARGMAX) {
-#pragma unroll
-                    for (int o = 16; o > 0; o >>= 1) {
-                        const Candidate other{__shfl_xor_sync(0xffffffffu, best.value, o), __shfl_xor_sync(0xffffffffu, best.index, o)};
-                        if (preferred(other, best)) best = other;
-                    }
-                    if (lane == 0) {
-                        p.best_value[static_cast<int64_t>(blockIdx.y) * p.rows + row] = best.value;
-                        p.best_index[static_cast<int64_t>(blockIdx.y) * p.rows + row] = best.index;
-                    }
-                }
-            }
-        }
+        finish_rows<EPI, kTileN>(p, tile, peer_tile, split, row_scale, m0, n0, static_cast<int>(blockIdx.y), first, last, warp, kGemmThreads / 32, lane, ready);
     }
     if (split > 1) {
         __syncwarp();
@@ -369,6 +379,166 @@ __global__ void __launch_bounds__(kGemmThreads, STAGES == 2 && TN == 128 ? 2 : 1
     if (warp == 1) {
         tc_fence_after_sync();
         tmem_dealloc(tmem_base, kTileN);
+    }
+}
+
+// ---- persistent variant: more tiles than SMs, no K split -----------------------------------------------------------
+// One CTA per SM walks tiles t = blockIdx.x, blockIdx.x + gridDim.x, ... (token tile fastest, so neighbouring CTAs share
+// a weight tile).  The accumulator is double-buffered in tensor memory (2 x 128 columns) and the epilogue has its own
+// shared-memory tile next to a 3-stage operand ring, so warps 2-5 finish tile j while the producer and the issuing
+// thread are already streaming and multiplying tile j + 1: the tensor pipe does not idle during epilogues and the ring
+// never drains between tiles.
+constexpr int kPersistStages = 3;
+constexpr int kPersistStageBytes = 3 * kBoxBytes;                      // x_hi, x_lo, W boxes of one K block: 48 KB
+constexpr int kPersistTileBytes = kTileM * (128 + 4) * 4;              // row-major f32 tile of the epilogue, padded rows
+constexpr int kPersistSmem = kPersistStages * kPersistStageBytes + kPersistTileBytes + 1024 + 1024;
+constexpr uint32_t kPersistInstruction = GemmShape<128, 3>::instruction;
+
+template <int EPI>
+__global__ void __launch_bounds__(kGemmThreads, 1) linear_gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_hi,
+                                                                                 const __grid_constant__ CUtensorMap map_lo,
+                                                                                 const __grid_constant__ CUtensorMap map_w,
+                                                                                 const GemmParams gp, const int row_tiles, const int tiles) {
+    constexpr int kTileN = 128, kTileStride = kTileN + 4;
+    const LinearParams& p = gp.base;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+    float* tile = reinterpret_cast<float*>(smem + kPersistStages * kPersistStageBytes);
+    uint8_t* control = smem + kPersistStages * kPersistStageBytes + kPersistTileBytes;
+    uint64_t* full = reinterpret_cast<uint64_t*>(control);
+    uint64_t* empty = full + kPersistStages;
+    uint64_t* acc_full = empty + kPersistStages;    // [2] the products of a tile are complete (tcgen05.commit)
+    uint64_t* acc_empty = acc_full + 2;             // [2] the epilogue has read the buffer (one arrival per epilogue warp)
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+    volatile int* alive_flag = reinterpret_cast<volatile int*>(control + 256);
+    float* row_scale = reinterpret_cast<float*>(control + 512);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int k_blocks = (p.in + kBlockK - 1) / kBlockK;
+    const bool has_lo = p.x_lo != nullptr;
+    const int my_tiles = (tiles - static_cast<int>(blockIdx.x) + static_cast<int>(gridDim.x) - 1) / static_cast<int>(gridDim.x);
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kPersistStages; ++s) {
+            mbar_init(&full[s], 1);
+            mbar_init(&empty[s], 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(&acc_full[b], 1);
+            mbar_init(&acc_empty[b], 4);
+        }
+        *alive_flag = 1;
+        mbar_fence_init();
+    }
+    if (warp == 1) {
+        tmem_alloc(tmem_slot, 2 * kTileN);
+        tmem_relinquish();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+
+    grid_dependency_wait();   // the shadow (and residual, cache, sums of squares) come from the preceding kernels
+    grid_launch_dependents();
+
+    if (warp == 0) {
+        if (lane == 0) {
+            tma_prefetch_descriptor(&map_hi);
+            tma_prefetch_descriptor(&map_lo);
+            tma_prefetch_descriptor(&map_w);
+            int it = 0;   // K blocks issued so far, over all tiles: the ring does not restart between tiles
+            bool alive = true;
+            for (int j = 0; j < my_tiles && alive; ++j) {
+                const int t = blockIdx.x + j * gridDim.x;
+                const int m0 = (t % row_tiles) * kTileM, n0 = (t / row_tiles) * kTileN;
+                for (int i = 0; i < k_blocks; ++i, ++it) {
+                    const int s = it % kPersistStages;
+                    const uint32_t phase = (it / kPersistStages) & 1;
+                    if (!mbar_wait(&empty[s], phase ^ 1)) { atomicExch(gp.status, B200_DEVICE_TIMEOUT); alive = false; break; }
+                    uint8_t* stage = smem + s * kPersistStageBytes;
+                    mbar_expect_tx(&full[s], has_lo ? kPersistStageBytes : kPersistStageBytes - kBoxBytes);
+                    tma_load_2d(stage, &map_hi, i * kBlockK, m0, &full[s]);
+                    if (has_lo) tma_load_2d(stage + kBoxBytes, &map_lo, i * kBlockK, m0, &full[s]);
+                    tma_load_2d(stage + 2 * kBoxBytes, &map_w, i * kBlockK, n0, &full[s]);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            int it = 0;
+            bool alive = true;
+            for (int j = 0; j < my_tiles && alive; ++j) {
+                const int buffer = j & 1;
+                // the epilogue of the tile that used this buffer two tiles ago must have read it (passes at once for j < 2)
+                if (!mbar_wait(&acc_empty[buffer], ((j >> 1) & 1) ^ 1)) { atomicExch(gp.status, B200_DEVICE_TIMEOUT); break; }
+                tc_fence_after_sync();
+                const uint32_t accumulator = tmem_base + static_cast<uint32_t>(buffer * kTileN);
+                for (int i = 0; i < k_blocks; ++i, ++it) {
+                    const int s = it % kPersistStages;
+                    const uint32_t phase = (it / kPersistStages) & 1;
+                    if (!mbar_wait(&full[s], phase)) { atomicExch(gp.status, B200_DEVICE_TIMEOUT); alive = false; break; }
+                    tc_fence_after_sync();
+                    const uint32_t stage = smem_u32(smem + s * kPersistStageBytes);
+                    const uint64_t hi = operand_descriptor(stage), lo = operand_descriptor(stage + kBoxBytes);
+                    const uint64_t w = operand_descriptor(stage + 2 * kBoxBytes);
+#pragma unroll
+                    for (int k = 0; k < kBlockK / 16; ++k) {
+                        tc_mma_bf16(accumulator, hi + 2 * k, w + 2 * k, kPersistInstruction, (i | k) != 0);
+                        if (has_lo) tc_mma_bf16(accumulator, lo + 2 * k, w + 2 * k, kPersistInstruction, 1);
+                    }
+                    tc_commit(&empty[s]);
+                }
+                if (alive) tc_commit(&acc_full[buffer]);
+            }
+        }
+    } else {
+        // ---- epilogue warps 2-5: TMEM lanes 32 * (warp % 4) .. + 31; named barrier 2 joins the four warps ----
+        const int quarter = warp & 3;
+        const int tile_row = quarter * 32 + lane;
+        const uint32_t own_tile[8] = {smem_u32(tile), 0u, 0u, 0u, 0u, 0u, 0u, 0u};
+        for (int j = 0; j < my_tiles; ++j) {
+            const int t = blockIdx.x + j * gridDim.x;
+            const int m0 = (t % row_tiles) * kTileM, n0 = (t / row_tiles) * kTileN;
+            const int buffer = j & 1;
+            const int row = m0 + tile_row;
+            float scale = 1.0f;
+            if (p.sumsq_in && row < p.rows) {
+                float total = 0.0f;
+                for (int i = 0; i < p.parts_in; ++i) total += __ldg(p.sumsq_in + static_cast<int64_t>(i) * p.rows + row);
+                scale = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(total, static_cast<float>(p.in)), static_cast<float>(p.eps))));
+            }
+            row_scale[tile_row] = scale;   // the previous tile's rows were finished before the barrier that ended it
+            const bool ready = mbar_wait(&acc_full[buffer], (j >> 1) & 1);
+            if (!ready && lane == 0) { atomicExch(gp.status, B200_DEVICE_TIMEOUT); *alive_flag = 0; }
+            tc_fence_after_sync();
+            if (ready) {
+#pragma unroll 1
+                for (int c = 0; c < kTileN / 32; ++c) {
+                    uint32_t r[32];
+                    tmem_load_32(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(buffer * kTileN + c * 32), r);
+                    float4* out4 = reinterpret_cast<float4*>(tile + tile_row * kTileStride + c * 32);
+#pragma unroll
+                    for (int q = 0; q < 8; ++q)
+                        out4[q] = make_float4(__uint_as_float(r[4 * q]), __uint_as_float(r[4 * q + 1]), __uint_as_float(r[4 * q + 2]),
+                                              __uint_as_float(r[4 * q + 3]));
+                }
+            }
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&acc_empty[buffer]);   // the issuing thread may reuse this accumulator
+            asm volatile("bar.sync 2, 128;" ::: "memory");    // the tile (and the row scales) are in shared memory
+            if (*alive_flag == 0) break;                       // same decision in all four warps
+            const int rows_here = min(kTileM, p.rows - m0);
+            finish_rows<EPI, kTileN>(p, tile, own_tile, 1, row_scale, m0, n0, t / row_tiles, 0, rows_here, quarter, 4, lane, true);
+            asm volatile("bar.sync 2, 128;" ::: "memory");    // the next tile may overwrite the shared-memory tile
+        }
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after_sync();
+        tmem_dealloc(tmem_base, 2 * kTileN);
     }
 }
 
@@ -388,9 +558,18 @@ int encode_operand(CUtensorMap* map, const void* base, int rows, int columns, in
 
 // Tile width of a launch: 128 features; 256 only for very wide matrices (vocabulary projections), where the tiles still
 // fill the SMs several times over and the wide tile halves the activation bytes pulled per weight byte.
-int choose_tile_features(int rows, int out) {
+// Launches the persistent kernel serves: prefill-sized passes (8 or more token tiles, more tiles than SMs) whose K is short
+// enough that the epilogues are a large share of a tile's time (measured: K 768 +28 %, K 2048 +5 %, K 8192 -11 % against the
+// one-tile-per-CTA kernel with the wide tile).
+bool takes_persistent(int rows, int in, int out, int sms) {
+    const int row_tiles = (rows + kTileM - 1) / kTileM;
+    return row_tiles >= 8 && in <= 2048 && row_tiles * ((out + 127) / 128) > sms;
+}
+
+int choose_tile_features(int rows, int in, int out) {
     int device = 0, sms = 148;
     if (cudaGetDevice(&device) == cudaSuccess) sms = sm_count(device);
+    if (takes_persistent(rows, in, out, sms)) return 128;
     const int row_tiles = (rows + kTileM - 1) / kTileM;
     return row_tiles * ((out + 255) / 256) >= 2 * sms ? 256 : 128;
 }
@@ -405,7 +584,7 @@ int choose_stages(int rows) { return rows > 64 ? 2 : 4; }
 int choose_split(int rows, int in, int out) {
     int device = 0, sms = 148;
     if (cudaGetDevice(&device) == cudaSuccess) sms = sm_count(device);
-    const int tn = choose_tile_features(rows, out);
+    const int tn = choose_tile_features(rows, in, out);
     const int tiles = ((rows + kTileM - 1) / kTileM) * ((out + tn - 1) / tn);
     const int k_blocks = (in + kBlockK - 1) / kBlockK;
     int split = sms / (tiles > 0 ? tiles : 1);
@@ -442,9 +621,29 @@ int launch_epilogue(int epilogue, const CUtensorMap& hi, const CUtensorMap& lo, 
 }  // namespace
 
 int linear_gemm_parts(int rows, int in, int out) {
-    (void)in;
-    const int tn = choose_tile_features(rows, out);
+    const int tn = choose_tile_features(rows, in, out);
     return (out + tn - 1) / tn;   // one partial per feature tile: a row of a tile is finished by one CTA of the cluster
+}
+
+template <int EPI>
+int launch_persistent_epilogue(const CUtensorMap& hi, const CUtensorMap& lo, const CUtensorMap& w, const GemmParams& gp, int row_tiles, int tiles,
+                               int sms, cudaStream_t stream) {
+    auto kernel = linear_gemm_persistent_kernel<EPI>;
+    B200_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kPersistSmem));
+    return cuda_status(launch_dependent(kernel, dim3(static_cast<unsigned>(tiles < sms ? tiles : sms)), dim3(kGemmThreads), kPersistSmem, stream, hi, lo,
+                                        w, gp, row_tiles, tiles), "linear_gemm_persistent_kernel launch");
+}
+
+int launch_persistent(int epilogue, const CUtensorMap& hi, const CUtensorMap& lo, const CUtensorMap& w, const GemmParams& gp, int row_tiles,
+                      int tiles, int sms, cudaStream_t stream) {
+    switch (epilogue) {
+    case B200_EPI_STORE: return launch_persistent_epilogue<B200_EPI_STORE>(hi, lo, w, gp, row_tiles, tiles, sms, stream);
+    case B200_EPI_RESIDUAL: return launch_persistent_epilogue<B200_EPI_RESIDUAL>(hi, lo, w, gp, row_tiles, tiles, sms, stream);
+    case B200_EPI_SWIGLU: return launch_persistent_epilogue<B200_EPI_SWIGLU>(hi, lo, w, gp, row_tiles, tiles, sms, stream);
+    case B200_EPI_QKV: return launch_persistent_epilogue<B200_EPI_QKV>(hi, lo, w, gp, row_tiles, tiles, sms, stream);
+    case B200_EPI_ARGMAX: return launch_persistent_epilogue<B200_EPI_ARGMAX>(hi, lo, w, gp, row_tiles, tiles, sms, stream);
+    }
+    return B200_UNSUPPORTED;
 }
 
 int launch_linear_gemm(const LinearParams& p, int epilogue, cudaStream_t stream) {
@@ -455,11 +654,15 @@ int launch_linear_gemm(const LinearParams& p, int epilogue, cudaStream_t stream)
     B200_CUDA(cudaGetDevice(&device));
     GemmParams gp{p, device_status_word(device)};
     alignas(64) CUtensorMap hi, lo, w;
-    const int tn = choose_tile_features(p.rows, p.out);
+    const int sms = sm_count(device);
+    const int row_tiles = (p.rows + kTileM - 1) / kTileM, tiles128 = row_tiles * ((p.out + 127) / 128);
+    const bool persistent = takes_persistent(p.rows, p.in, p.out, sms);
+    const int tn = persistent ? 128 : choose_tile_features(p.rows, p.in, p.out);
     int status = encode_operand(&hi, p.x_hi, p.rows, p.in, kTileM);
     if (status == B200_OK) status = encode_operand(&lo, p.x_lo ? p.x_lo : p.x_hi, p.rows, p.in, kTileM);
     if (status == B200_OK) status = encode_operand(&w, p.weight, p.out, p.in, tn);
     if (status != B200_OK) return status;
+    if (persistent) return launch_persistent(epilogue, hi, lo, w, gp, row_tiles, tiles128, sms, stream);
     const int stages = choose_stages(p.rows);
     if (tn == 256) return launch_epilogue<256, 3>(epilogue, hi, lo, w, gp, stream);
     return stages == 2 ? launch_epilogue<128, 2>(epilogue, hi, lo, w, gp, stream) : launch_epilogue<128, 4>(epilogue, hi, lo, w, gp, stream);
