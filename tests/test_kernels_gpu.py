@@ -394,11 +394,13 @@ def test_shadow_protocol_swiglu_and_attention_output():
 
 @pytest.mark.parametrize("rows,inner,out,epilogue", [(40, 768, 1280, 0), (130, 2048, 768, 1), (300, 768, 4096, 2), (17, 4096, 200, 1),
                                                      (128, 72, 136, 0), (32, 4096, 1024, 1), (256, 2048, 3072, 2),
-                                                     (1000, 512, 2560, 0)])
+                                                     (1000, 512, 2560, 0), (20, 256, 76000, 0), (1100, 2304, 2304, 1)])
 def test_dense_tensor_core_linear(rows, inner, out, epilogue):
     """More than 16 rows (or a wide input) take the tcgen05 kernel: shadow input, split norm, every epilogue family.
-    Launches with few tiles split K over a thread-block cluster (2..8 CTAs, the partial tiles summed through distributed
-    shared memory); the last case has enough tiles to run unsplit."""
+    Launches with few tiles split K over a thread-block cluster (the partial tiles summed through distributed shared
+    memory); (1000, 512, 2560) runs on the persistent variant (8 token tiles, short K, more tiles than SMs), (20, 256,
+    76000) on the 256-wide tile (vocabulary-sized output), (1100, 2304, 2304) on the plain one-tile-per-CTA kernel with
+    two CTAs per SM."""
     l = B.lib()
     rng = np.random.default_rng(rows + inner + out)
     x = rng.standard_normal((rows, inner), dtype=np.float32) * 2
@@ -444,7 +446,8 @@ def test_dense_tensor_core_linear(rows, inner, out, epilogue):
         assert rel(osq.cpu().numpy().sum(axis=0), (want.astype(np.float64) ** 2).sum(axis=1)) < 1e-4
 
 
-@pytest.mark.parametrize("rows,inner,vocab", [(16, 768, 32000), (5, 256, 1000), (40, 512, 5000), (32, 2048, 1024), (200, 256, 777 * 2)])
+@pytest.mark.parametrize("rows,inner,vocab", [(16, 768, 32000), (5, 256, 1000), (40, 512, 5000), (32, 2048, 1024), (200, 256, 777 * 2),
+                                              (20, 256, 76000)])
 def test_fused_logits_argmax(rows, inner, vocab):
     """Logits + greedy choice without logits in memory: per-tile candidates from the projection's epilogue (streaming kernel
     up to 16 rows, tcgen05 kernel above, K-split clusters when the tiles are few), then the merge.  Duplicated weight
