@@ -369,16 +369,17 @@ void DecodePlan::run_layers(const float* x, Index batch, Index length, std::span
         const bool parallel = world > 1;
         const Index hd = D / owner_.heads();
         const Index H = owner_.heads() / world, HK = owner_.kv_heads() / world, Dl = H * hd, Fl = F / world;
-        const int parts_o = parallel ? 1 : b200_linear_shadow_parts(rows, D, D);
-        const int parts_down = parallel ? 1 : b200_linear_shadow_parts(rows, F, D);
+        // With symmetric memory mapped (and the rows fitting a slot) the projections write their partial rows into this
+        // rank's slot and one kernel sums the ranks' slots over NVLink and rebuilds the shadow; otherwise NCCL.
+        const bool peer_sum = parallel && runtime::tp_symmetric_ready(device, static_cast<std::size_t>(rows * D) * sizeof(float));
+        const int parts_summed = peer_sum ? b200_tp_reduce_parts(D) : 1;   // partial sums of squares the rebuilt shadow comes with
+        const int parts_o = parallel ? parts_summed : b200_linear_shadow_parts(rows, D, D);
+        const int parts_down = parallel ? parts_summed : b200_linear_shadow_parts(rows, F, D);
         auto* sq_attn = static_cast<float*>(sq_attn_.mutable_data());
         auto* sq_ffn = static_cast<float*>(sq_ffn_.mutable_data());
         // bf16 activations: the dense kernel (more than 16 rows) is given the hi plane only
         const bool single_plane = owner_.activation_dtype() == DType::bf16 && rows >= 17;
         auto lo_plane = [&](const Tensor& plane) -> const void* { return single_plane ? nullptr : plane.raw_data(); };
-        // With symmetric memory mapped (and the rows fitting a slot) the projections write their partial rows into this
-        // rank's slot and one kernel sums the ranks' slots over NVLink and rebuilds the shadow; otherwise NCCL.
-        const bool peer_sum = parallel && runtime::tp_symmetric_ready(device, static_cast<std::size_t>(rows * D) * sizeof(float));
         auto rebuild_shadow = [&](const Tensor* norm, float* sums, int slot) {
             if (peer_sum) {
                 runtime::tp_reduce_shadow(device, slot, rows, D, norm->raw_data(), code_of(norm->dtype()), h, hs_hi_.mutable_data(),

@@ -179,11 +179,6 @@ cudaError_t launch_dependent_cluster(void (*kernel)(Params...), dim3 grid, dim3 
 __device__ __forceinline__ void cluster_sync_all() {
     asm volatile("barrier.cluster.arrive.release.aligned;\n barrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
-__device__ __forceinline__ uint32_t cluster_cta_rank() {
-    uint32_t rank;
-    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
-    return rank;
-}
 __device__ __forceinline__ uint32_t map_peer_shared(uint32_t local_address, uint32_t peer_rank) {
     uint32_t remote;
     asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_address), "r"(peer_rank));
@@ -193,13 +188,6 @@ __device__ __forceinline__ uint32_t map_peer_shared(uint32_t local_address, uint
 __device__ __forceinline__ float2 load_cluster_float2(uint32_t cluster_address) {
     float2 value;
     asm("ld.shared::cluster.v2.f32 {%0, %1}, [%2];" : "=f"(value.x), "=f"(value.y) : "r"(cluster_address));
-    return value;
-}
-__device__ __forceinline__ float load_peer_shared(uint32_t local_address, uint32_t peer_rank) {
-    uint32_t remote;
-    float value;
-    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_address), "r"(peer_rank));
-    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(value) : "r"(remote) : "memory");
     return value;
 }
 

@@ -11,9 +11,9 @@
 //   2. Thread 0 of every CTA waits until arrive[r] >= e for all r in its OWN region (local polling, acquire loads).
 //      The wait is bounded (~2 s of %globaltimer); on expiry the device status word is set, the kernel still finishes
 //      its bookkeeping and every later call skips the wait, so a lost rank surfaces as an error status, not a hang.
-//   3. A CTA takes one row: it pulls the row from every rank's slot with uncached 16-byte loads (ld.global.cv: remote
+//   3. A CTA takes 1024 columns of one row, one 16-byte vector per thread: it pulls them from every rank's slot with uncached loads (ld.global.cv: remote
 //      lines must not be served from a stale L1), adds them in rank order 0..W-1 (every rank computes the same bits),
-//      writes the f32 row, the shadow planes of row * norm_weight, and the row's sum of squares.
+//      writes the f32 values, the shadow planes of value * norm_weight, and its partial of the row's sum of squares.
 //   4. The last CTA to leave stores the call number (exit ticket), so the next call sees e + 1.
 // Slot reuse: a rank overwrites slot s two calls later.  By then it has passed the wait of the call in between, which
 // needs every peer's arrival for that call, and a peer arrives there only after its own kernel of the earlier call (the
@@ -66,7 +66,7 @@ __global__ void __launch_bounds__(kReduceThreads) tp_reduce_shadow_kernel(const 
     auto* mine = reinterpret_cast<Control*>(peers.region[rank]);
     const uint32_t call = mine->calls + 1;   // stable during the kernel: only the last CTA to leave advances it
     if (threadIdx.x == 0) {
-        if (blockIdx.x == 0) {
+        if (blockIdx.x == 0 && blockIdx.y == 0) {
             __threadfence_system();
             for (int r = 0; r < world; ++r) store_release_system(&reinterpret_cast<Control*>(peers.region[r])->arrive[rank], call);
         }
@@ -89,49 +89,48 @@ __global__ void __launch_bounds__(kReduceThreads) tp_reduce_shadow_kernel(const 
         proceed = ok;
     }
     __syncthreads();
-    const int64_t row = blockIdx.x;
+    const int64_t row = blockIdx.y;
     float squares = 0.0f;
-    if (proceed && row < rows) {
-        const int64_t vectors = width >> 2;   // width % 4 == 0 (checked by the launcher)
-        for (int64_t v = threadIdx.x; v < vectors; v += blockDim.x) {
-            float4 sum = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-            float4 part[kMaxRanks > 8 ? 8 : kMaxRanks];
-            // at most 8 ranks in one box: request all rows first, add in rank order
+    // One 16-byte vector per thread: every peer load of the CTA is in flight at once (one NVLink round trip per call).
+    const int64_t vectors = width >> 2;   // width % 4 == 0 (checked by the launcher)
+    const int64_t v = static_cast<int64_t>(blockIdx.x) * kReduceThreads + threadIdx.x;
+    if (proceed && row < rows && v < vectors) {
+        float4 sum = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        float4 part[8];
 #pragma unroll
-            for (int r = 0; r < 8; ++r) {
-                if (r < world) {
-                    const float4* source = reinterpret_cast<const float4*>(peers.region[r] + kControlBytes + static_cast<int64_t>(slot) * slot_bytes)
-                                           + row * vectors + v;
-                    part[r] = __ldcv(source);
-                }
+        for (int r = 0; r < 8; ++r) {
+            if (r < world) {
+                const float4* source = reinterpret_cast<const float4*>(peers.region[r] + kControlBytes + static_cast<int64_t>(slot) * slot_bytes)
+                                       + row * vectors + v;
+                part[r] = __ldcv(source);
             }
-#pragma unroll
-            for (int r = 0; r < 8; ++r) {
-                if (r < world) {
-                    sum.x = __fadd_rn(sum.x, part[r].x); sum.y = __fadd_rn(sum.y, part[r].y);
-                    sum.z = __fadd_rn(sum.z, part[r].z); sum.w = __fadd_rn(sum.w, part[r].w);
-                }
-            }
-            reinterpret_cast<float4*>(out + row * width)[v] = sum;
-            squares += sum.x * sum.x + sum.y * sum.y + sum.z * sum.z + sum.w * sum.w;
-            const int64_t c = v * 4;
-            float w[4] = {1.0f, 1.0f, 1.0f, 1.0f};
-            if (norm_weight) {
-#pragma unroll
-                for (int i = 0; i < 4; ++i)
-                    w[i] = norm_dtype == B200_BF16 ? __bfloat162float(static_cast<const __nv_bfloat16*>(norm_weight)[c + i])
-                                                   : static_cast<const float*>(norm_weight)[c + i];
-            }
-            const float e[4] = {__fmul_rn(sum.x, w[0]), __fmul_rn(sum.y, w[1]), __fmul_rn(sum.z, w[2]), __fmul_rn(sum.w, w[3])};
-            const __nv_bfloat162 h0 = __floats2bfloat162_rn(e[0], e[1]), h1 = __floats2bfloat162_rn(e[2], e[3]);
-            const __nv_bfloat162 l0 = __floats2bfloat162_rn(e[0] - __low2float(h0), e[1] - __high2float(h0));
-            const __nv_bfloat162 l1 = __floats2bfloat162_rn(e[2] - __low2float(h1), e[3] - __high2float(h1));
-            uint2 hi, lo;
-            hi.x = *reinterpret_cast<const uint32_t*>(&h0); hi.y = *reinterpret_cast<const uint32_t*>(&h1);
-            lo.x = *reinterpret_cast<const uint32_t*>(&l0); lo.y = *reinterpret_cast<const uint32_t*>(&l1);
-            *reinterpret_cast<uint2*>(out_hi + row * width + c) = hi;
-            *reinterpret_cast<uint2*>(out_lo + row * width + c) = lo;
         }
+#pragma unroll
+        for (int r = 0; r < 8; ++r) {
+            if (r < world) {
+                sum.x = __fadd_rn(sum.x, part[r].x); sum.y = __fadd_rn(sum.y, part[r].y);
+                sum.z = __fadd_rn(sum.z, part[r].z); sum.w = __fadd_rn(sum.w, part[r].w);
+            }
+        }
+        reinterpret_cast<float4*>(out + row * width)[v] = sum;
+        squares = sum.x * sum.x + sum.y * sum.y + sum.z * sum.z + sum.w * sum.w;
+        const int64_t c = v * 4;
+        float w[4] = {1.0f, 1.0f, 1.0f, 1.0f};
+        if (norm_weight) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+                w[i] = norm_dtype == B200_BF16 ? __bfloat162float(static_cast<const __nv_bfloat16*>(norm_weight)[c + i])
+                                               : static_cast<const float*>(norm_weight)[c + i];
+        }
+        const float e[4] = {__fmul_rn(sum.x, w[0]), __fmul_rn(sum.y, w[1]), __fmul_rn(sum.z, w[2]), __fmul_rn(sum.w, w[3])};
+        const __nv_bfloat162 h0 = __floats2bfloat162_rn(e[0], e[1]), h1 = __floats2bfloat162_rn(e[2], e[3]);
+        const __nv_bfloat162 l0 = __floats2bfloat162_rn(e[0] - __low2float(h0), e[1] - __high2float(h0));
+        const __nv_bfloat162 l1 = __floats2bfloat162_rn(e[2] - __low2float(h1), e[3] - __high2float(h1));
+        uint2 hi, lo;
+        hi.x = *reinterpret_cast<const uint32_t*>(&h0); hi.y = *reinterpret_cast<const uint32_t*>(&h1);
+        lo.x = *reinterpret_cast<const uint32_t*>(&l0); lo.y = *reinterpret_cast<const uint32_t*>(&l1);
+        *reinterpret_cast<uint2*>(out_hi + row * width + c) = hi;
+        *reinterpret_cast<uint2*>(out_lo + row * width + c) = lo;
     }
     for (int o = 16; o > 0; o >>= 1) squares += __shfl_xor_sync(0xffffffffu, squares, o);
     if ((threadIdx.x & 31) == 0) partial[threadIdx.x >> 5] = squares;
@@ -139,13 +138,13 @@ __global__ void __launch_bounds__(kReduceThreads) tp_reduce_shadow_kernel(const 
     if (threadIdx.x < 32) {
         float v = threadIdx.x < (blockDim.x >> 5) ? partial[threadIdx.x] : 0.0f;
         for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-        if (threadIdx.x == 0 && row < rows) sumsq_out[row] = v;
+        if (threadIdx.x == 0 && row < rows) sumsq_out[static_cast<int64_t>(blockIdx.x) * rows + row] = v;   // one partial per column chunk
     }
     // exit ticket: the last CTA of the call advances the owner's call counter
     if (threadIdx.x == 0) {
         __threadfence();
         const uint32_t finished = atomicAdd(&mine->ticket, 1u);
-        if (finished == gridDim.x - 1) {
+        if (finished == gridDim.x * gridDim.y - 1) {
             mine->ticket = 0;
             __threadfence();
             mine->calls = call;
@@ -159,6 +158,8 @@ __global__ void __launch_bounds__(kReduceThreads) tp_reduce_shadow_kernel(const 
 using namespace b200;
 
 extern "C" {
+
+int32_t b200_tp_reduce_parts(int64_t width) { return width > 0 ? static_cast<int32_t>((width + 4 * kReduceThreads - 1) / (4 * kReduceThreads)) : 0; }
 
 size_t b200_tp_region_bytes(size_t slot_bytes) { return kControlBytes + 2 * slot_bytes; }
 
@@ -181,7 +182,8 @@ int b200_tp_reduce_shadow(void* const* regions, int32_t rank, int32_t world, int
     }
     int device = 0;
     B200_CUDA(cudaGetDevice(&device));
-    return cuda_status(launch_dependent(tp_reduce_shadow_kernel, dim3(static_cast<unsigned>(rows)), dim3(kReduceThreads), 0, as_stream(stream), table,
+    const dim3 grid(static_cast<unsigned>(b200_tp_reduce_parts(width)), static_cast<unsigned>(rows));
+    return cuda_status(launch_dependent(tp_reduce_shadow_kernel, grid, dim3(kReduceThreads), 0, as_stream(stream), table,
                                         static_cast<int>(rank), static_cast<int>(world), static_cast<int>(slot), static_cast<int64_t>(slot_bytes),
                                         rows, width, norm_weight, static_cast<int>(norm_dtype), out, static_cast<__nv_bfloat16*>(out_hi),
                                         static_cast<__nv_bfloat16*>(out_lo), sumsq_out, device_status_word(device)),

@@ -260,8 +260,10 @@ B200_API int b200_take_device_status(int32_t device, void* stream, int32_t* stat
  * gives the address of a slot inside a region.  b200_tp_reduce_shadow, called by every rank at the same point of its
  * stream with regions[r] = rank r's region as mapped here, publishes "my slot is written", waits (bounded; on expiry the
  * device status word reads B200_DEVICE_TIMEOUT) for all ranks, and writes out[rows, width] = sum over ranks in rank order of
- * their slot rows, the shadow planes of out * norm_weight and the per-row sums of squares ([1][rows]).  The caller's
+ * their slot rows, the shadow planes of out * norm_weight and per-row partial sums of squares
+ * ([b200_tp_reduce_parts(width)][rows], one partial per 1024 columns).  The caller's
  * projection writes its partial rows into its own slot beforehand, alternating slots 0 and 1 from call to call. */
+B200_API int32_t b200_tp_reduce_parts(int64_t width);
 B200_API size_t b200_tp_region_bytes(size_t slot_bytes);
 B200_API void* b200_tp_slot(void* region, size_t slot_bytes, int32_t slot);
 B200_API int b200_tp_reduce_shadow(void* const* regions, int32_t rank, int32_t world, int32_t slot, size_t slot_bytes, int64_t rows,

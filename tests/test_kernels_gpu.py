@@ -542,14 +542,14 @@ def test_peer_memory_sum_one_gpu():
     """The tensor-parallel sum kernel on one GPU: as a group of one, and as rank 0 of two with the other rank's arrival and
     partial rows put in place by the host beforehand (two kernels that wait on one another never share a GPU)."""
     l = B.lib()
-    rows, width, slot_bytes = 5, 512, 16384
+    rows, width, slot_bytes = 5, 2560, 65536    # 2560 columns: three column chunks per row, the last one partial
     rng = np.random.default_rng(12)
     norm = W.bf16_bits((1 + 0.1 * rng.standard_normal(width)).astype(np.float32))
     nd = bf16_dev(norm)
     out = torch.zeros((rows, width), device="cuda")
     hi = torch.zeros((rows, width), dtype=torch.bfloat16, device="cuda")
     lo = torch.zeros_like(hi)
-    sums = torch.zeros((1, rows), device="cuda")
+    sums = torch.zeros((l.b200_tp_reduce_parts(width), rows), device="cuda")
     for world in (1, 2):
         regions, table = _tp_regions(world, slot_bytes)
         for call, slot in ((1, 0), (2, 1), (3, 0)):
@@ -568,7 +568,7 @@ def test_peer_memory_sum_one_gpu():
             want = parts[0] if world == 1 else parts[0] + parts[1]
             assert np.array_equal(out.cpu().numpy(), want)
             assert rel(shadow_to_f32(hi, lo), want * W.bf16_to_f32(norm)) < 2e-5
-            assert rel(sums.cpu().numpy()[0], (want.astype(np.float64) ** 2).sum(axis=1)) < 1e-5
+            assert rel(sums.cpu().numpy().sum(axis=0), (want.astype(np.float64) ** 2).sum(axis=1)) < 1e-5
             control = regions[0][:256].view(torch.int32).cpu().numpy()
             assert control[0] == call and control[32] == call and control[33] == 0      # arrive[0], calls, ticket
             if world == 2:
