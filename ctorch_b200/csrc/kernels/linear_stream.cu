@@ -516,7 +516,73 @@ int linear_argmax_parts(int rows, int in, int out) {
     return sp.tiles < sm_count(device) ? sp.tiles : sm_count(device);   // one candidate slice per CTA
 }
 
+// ---- thin outputs (adapter down-projections: a few dozen output features) for passes the dense kernel would serve ----
+// A 128-wide tensor-core tile would be one mostly empty tile with a K split of four CTAs at the kernel's latency floor.
+// Here a CTA takes one activation row and eight output features: 256 threads stride over K with 16-byte loads (eight
+// activation values from the hi (+ lo) planes, eight weights per feature), f32 FMAs, then a block reduction.  The
+// operands are a few hundred KB that every CTA finds in L2.
+constexpr int kThinFeatures = 8, kThinThreads = 256, kThinMaxOut = 64;
+
+__global__ void __launch_bounds__(kThinThreads) linear_thin_kernel(const LinearParams p) {
+    __shared__ float partial[kThinThreads / 32][kThinFeatures];
+    grid_dependency_wait();
+    grid_launch_dependents();
+    const int row = blockIdx.x, feature0 = blockIdx.y * kThinFeatures;
+    const auto* weight = static_cast<const __nv_bfloat16*>(p.weight);
+    float acc[kThinFeatures];
+#pragma unroll
+    for (int f = 0; f < kThinFeatures; ++f) acc[f] = 0.0f;
+    for (int k = threadIdx.x * 8; k < p.in; k += kThinThreads * 8) {
+        const uint4 hi = *reinterpret_cast<const uint4*>(p.x_hi + static_cast<int64_t>(row) * p.in + k);
+        uint4 lo = make_uint4(0u, 0u, 0u, 0u);
+        if (p.x_lo) lo = *reinterpret_cast<const uint4*>(p.x_lo + static_cast<int64_t>(row) * p.in + k);
+        const uint32_t h[4] = {hi.x, hi.y, hi.z, hi.w}, l[4] = {lo.x, lo.y, lo.z, lo.w};
+        float x[8];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            x[2 * i] = bf16_lo(h[i]) + bf16_lo(l[i]);
+            x[2 * i + 1] = bf16_hi(h[i]) + bf16_hi(l[i]);
+        }
+#pragma unroll
+        for (int f = 0; f < kThinFeatures; ++f) {
+            if (feature0 + f >= p.out) break;
+            const uint4 w = __ldg(reinterpret_cast<const uint4*>(weight + static_cast<int64_t>(feature0 + f) * p.in + k));
+            const uint32_t v[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+            for (int i = 0; i < 4; ++i) acc[f] = fmaf(x[2 * i], bf16_lo(v[i]), fmaf(x[2 * i + 1], bf16_hi(v[i]), acc[f]));
+        }
+    }
+#pragma unroll
+    for (int f = 0; f < kThinFeatures; ++f) acc[f] = warp_sum(acc[f]);
+    if ((threadIdx.x & 31) == 0) {
+#pragma unroll
+        for (int f = 0; f < kThinFeatures; ++f) partial[threadIdx.x >> 5][f] = acc[f];
+    }
+    __syncthreads();
+    if (threadIdx.x < kThinFeatures && feature0 + threadIdx.x < p.out) {
+        float total = 0.0f;
+#pragma unroll
+        for (int w = 0; w < kThinThreads / 32; ++w) total += partial[w][threadIdx.x];
+        float scale = 1.0f;
+        if (p.sumsq_in) {
+            float squares = 0.0f;
+            for (int i = 0; i < p.parts_in; ++i) squares += __ldg(p.sumsq_in + static_cast<int64_t>(i) * p.rows + row);
+            scale = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(squares, static_cast<float>(p.in)), static_cast<float>(p.eps))));
+        }
+        p.y[static_cast<int64_t>(row) * p.out + feature0 + threadIdx.x] = total * scale;
+    }
+}
+
+int launch_linear_thin(const LinearParams& p, cudaStream_t stream) {
+    const dim3 grid(static_cast<unsigned>(p.rows), static_cast<unsigned>((p.out + kThinFeatures - 1) / kThinFeatures));
+    return cuda_status(launch_dependent(linear_thin_kernel, grid, dim3(kThinThreads), 0, stream, p), "linear_thin_kernel launch");
+}
+
 int launch_linear_stream(const LinearParams& p, int epilogue, cudaStream_t stream) {
+    if (p.x_hi && (p.rows >= kGemmRows || p.in > kMaxIn) && epilogue == B200_EPI_STORE && p.out <= kThinMaxOut && p.rows <= 512
+        && p.weight_dtype == B200_BF16 && (p.in & 7) == 0
+        && ((reinterpret_cast<uintptr_t>(p.weight) | reinterpret_cast<uintptr_t>(p.x_hi) | reinterpret_cast<uintptr_t>(p.x_lo)) & 15) == 0)
+        return launch_linear_thin(p, stream);
     if (p.x_hi && (p.rows >= kGemmRows || p.in > kMaxIn)) return launch_linear_gemm(p, epilogue, stream);
     if (p.x_hi && !p.x_lo) return B200_UNSUPPORTED;   // the streaming kernel always multiplies both planes
     if (p.weight_dtype != B200_BF16 || p.in > kMaxIn || (p.in & 7) || (reinterpret_cast<uintptr_t>(p.weight) & 15))

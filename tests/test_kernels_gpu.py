@@ -394,13 +394,14 @@ def test_shadow_protocol_swiglu_and_attention_output():
 
 @pytest.mark.parametrize("rows,inner,out,epilogue", [(40, 768, 1280, 0), (130, 2048, 768, 1), (300, 768, 4096, 2), (17, 4096, 200, 1),
                                                      (128, 72, 136, 0), (32, 4096, 1024, 1), (256, 2048, 3072, 2),
-                                                     (1000, 512, 2560, 0), (20, 256, 76000, 0), (1100, 2304, 2304, 1)])
+                                                     (1000, 512, 2560, 0), (20, 256, 76000, 0), (1100, 2304, 2304, 1), (40, 4096, 32, 0), (300, 768, 24, 0)])
 def test_dense_tensor_core_linear(rows, inner, out, epilogue):
     """More than 16 rows (or a wide input) take the tcgen05 kernel: shadow input, split norm, every epilogue family.
     Launches with few tiles split K over a thread-block cluster (the partial tiles summed through distributed shared
     memory); (1000, 512, 2560) runs on the persistent variant (8 token tiles, short K, more tiles than SMs), (20, 256,
     76000) on the 256-wide tile (vocabulary-sized output), (1100, 2304, 2304) on the plain one-tile-per-CTA kernel with
-    two CTAs per SM."""
+    two CTAs per SM; the last two (at most 64 output features, store epilogue: adapter down-projections) on the thin CUDA-core
+    kernel."""
     l = B.lib()
     rng = np.random.default_rng(rows + inner + out)
     x = rng.standard_normal((rows, inner), dtype=np.float32) * 2
