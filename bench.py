@@ -198,6 +198,13 @@ def barrier(dist, local: int):
             dist.barrier()
 
 
+def describe(name: str, spec: dict) -> str:
+    """The workload in words: BASELINE configuration and its shape (the JSON line carries no model keys)."""
+    return (f"{name}: GQA decoder, vocab {spec['vocab']}, d_model {spec['d_model']}, {spec['layers']} layers, "
+            f"{spec['heads']}/{spec['kv_heads']} heads, SwiGLU {spec['hidden']}, {spec['dtype']} weights"
+            + (f", rank-{spec['lora_rank']} adapters on q and v" if spec.get("lora_rank") else ""))
+
+
 def run_reference(args, spec, weights) -> dict:
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
@@ -207,8 +214,7 @@ def run_reference(args, spec, weights) -> dict:
     return {"impl": "reference", "metric": METRIC, "value": result["value"], "unit": UNIT, "n_gpus": args.gpus,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": args.workload, "batch_per_gpu": spec["batch"], "layers": spec["layers"], "d_model": spec["d_model"],
-                       "vocab": spec["vocab"], "note": "CPU decoder of the reference, f32 math on " + spec["dtype"] + " weights, rank 0 only"},
+            "config": {"workload": describe(args.workload, spec), "batch_per_gpu": spec["batch"], "note": "CPU decoder of the reference, f32 math on " + spec["dtype"] + " weights, rank 0 only"},
             "cpu_baseline": {k: result[k] for k in ("value", "unit", "cores", "kind", "sample")},
             "e2e": {"value": result["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
             "gpu_launches": 0}
@@ -295,8 +301,8 @@ def run_b200(args, spec, weights) -> dict:
         "dtype": ("bf16 weights and KV, f32 accumulate and activations" if args.activations == "f32" else
                   "bf16 weights and KV, f32 accumulate, bf16 activations in passes over more than 16 rows") if spec["dtype"] == "bf16" else "f32",
         "data": "synthetic",
-        "config": {"workload": args.workload, "batch_per_gpu": batch, "prompt": prompt_len, "mean_context": mean_context,
-                   "layers": spec["layers"], "d_model": spec["d_model"], "vocab": spec["vocab"], "parallelism": f"tp{world} (heads, KV heads and SwiGLU features sliced; 2 all-reduces per layer)" if sliced else f"replicas x{world}",
+        "config": {"workload": describe(args.workload, spec), "batch_per_gpu": batch, "prompt": prompt_len, "mean_context": mean_context,
+                   "parallelism": f"tp{world} (heads, KV heads and SwiGLU features sliced; 2 all-reduces per layer)" if sliced else f"replicas x{world}",
                    "l2": "inputs larger than L2: %.0f MB of weights and KV are streamed per step" % ((linear_bytes + kv_bytes) / 1e6),
                    "step_bytes": linear_bytes + kv_bytes,
                    "step_gbs": (linear_bytes + kv_bytes) / (device_ms / args.steps / 1000.0) / 1e9,
