@@ -151,7 +151,9 @@ typedef struct b200_shadow_linear_args {
     int32_t* best_index;           /* B200_EPI_ARGMAX: same shape, feature index of best_value */
 } b200_shadow_linear_args;
 /* Up to 16 rows with in <= 2048: streaming kernel (bulk-TMA weight ring, mma.sync).  More rows or a wider input:
- * dense tcgen05 kernel (TMA operand tiles, accumulator in tensor memory).  B200_UNSUPPORTED when in % 8 != 0. */
+ * dense tcgen05 kernel (TMA operand tiles, accumulator in tensor memory; K split over a thread-block cluster when the
+ * tiles are few, a persistent variant for prefill-sized passes), except store-epilogue calls with at most 64 output
+ * features (adapter down-projections), which a CUDA-core kernel serves.  B200_UNSUPPORTED when in % 8 != 0. */
 B200_API int b200_linear_shadow(const b200_shadow_linear_args* args, void* stream);
 /* Number of row-sum partials a residual-epilogue call with these sizes writes (its feature tiles), 0 if unsupported. */
 B200_API int32_t b200_linear_shadow_parts(int64_t rows, int64_t in, int64_t out);
