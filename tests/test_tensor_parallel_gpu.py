@@ -1,6 +1,7 @@
-"""KV-head tensor parallelism over two GPUs (one process per GPU, NCCL all-reduce on the library's stream): each rank
-computes half of the heads and SwiGLU features; logits must match the single-GPU run and the CPU oracle within the
-bf16 tolerance, and every rank must generate the same tokens.  Skipped on a box with one GPU."""
+"""KV-head tensor parallelism over two and four GPUs (one process per GPU; sums over NVLink peer memory for single-token
+steps, NCCL all-reduce on the library's stream for prefill chunks): each rank computes its share of the heads and SwiGLU
+features; logits must match the single-GPU run and the CPU oracle within the bf16 tolerance, and every rank must generate the
+same tokens.  Skipped on a box with fewer GPUs."""
 import json
 import os
 import subprocess
@@ -13,13 +14,14 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 BF16_TOL = 2e-2
 
 
-def test_two_rank_tensor_parallel_matches_single_gpu():
+@pytest.mark.parametrize("world", [2, 4])
+def test_tensor_parallel_matches_single_gpu(world):
     import torch
-    if torch.cuda.device_count() < 2:
-        pytest.skip("needs two GPUs")
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
     env = dict(os.environ, PYTHONPATH=ROOT, NCCL_NVLS_ENABLE="0")
-    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr", "127.0.0.1",
-           "--master-port", "29671", os.path.join(ROOT, "tests", "tp_worker.py")]
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", str(world), "--master-addr", "127.0.0.1",
+           "--master-port", str(29671 + world), os.path.join(ROOT, "tests", "tp_worker.py")]
     result = subprocess.run(cmd, cwd=ROOT, env=env, capture_output=True, text=True, timeout=900)
     assert result.returncode == 0, (result.stdout[-1500:], result.stderr[-8000:])
     decoder, reports, at = json.JSONDecoder(), [], result.stdout.find('{"rank"')
@@ -27,7 +29,7 @@ def test_two_rank_tensor_parallel_matches_single_gpu():
         value, end = decoder.raw_decode(result.stdout, at)
         reports.append(value)
         at = result.stdout.find('{"rank"', end)
-    assert sorted(r["rank"] for r in reports) == [0, 1]
+    assert sorted(r["rank"] for r in reports) == list(range(world))
     for report in reports:
         for case in report["cases"]:
             assert case["prefill"] < BF16_TOL and case["step"] < BF16_TOL, case
