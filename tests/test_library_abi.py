@@ -86,3 +86,26 @@ def test_no_cpu_fallback():
     out = C.c_void_p()
     assert B.lib().dl_linear(x.h, w.h, None, C.byref(out)) == 1
     assert b"no CPU compute path" in B.lib().dl_last_error()
+
+
+def test_decoder_options_are_validated_on_the_host():
+    """Tensor-parallel slicing, activation and cache dtypes are checked when they are set (no GPU involved)."""
+    l = B.lib()
+    dec = C.c_void_p()
+    B.check(l.dl_transformer_decoder_create(1, 64, 8, 4, 96, 16, B.options(B.BF16), C.byref(dec)))
+    assert l.dl_transformer_decoder_set_tensor_parallel(dec, 0, 2) == 0          # 4 + 2 heads, 48 features per rank
+    assert l.dl_transformer_decoder_set_tensor_parallel(dec, 2, 2) == 1 and b"rank must lie" in l.dl_last_error()
+    assert l.dl_transformer_decoder_set_tensor_parallel(dec, 0, 3) == 1 and b"split evenly" in l.dl_last_error()
+    assert l.dl_transformer_decoder_set_tensor_parallel(dec, 0, 8) == 1 and b"split evenly" in l.dl_last_error()   # 4 KV heads
+    assert l.dl_transformer_decoder_set_tensor_parallel(dec, 0, 1) == 0
+    assert l.dl_transformer_decoder_set_activation_dtype(dec, B.BF16) == 0
+    assert l.dl_transformer_decoder_set_activation_dtype(dec, 1) == 1 and b"f32 or bf16" in l.dl_last_error()       # f64
+    assert l.dl_transformer_decoder_set_cache_dtype(dec, 1) == 1 and b"f32 or bf16" in l.dl_last_error()
+    l.dl_module_release(dec)
+    plain = C.c_void_p()
+    B.check(l.dl_transformer_decoder_create(1, 64, 8, 4, 96, 16, B.options(B.F32), C.byref(plain)))
+    assert l.dl_transformer_decoder_set_activation_dtype(plain, B.BF16) == 1 and b"bf16 decoder" in l.dl_last_error()
+    l.dl_module_release(plain)
+    # the group itself lives on a GPU
+    assert l.dl_b200_tp_init(B.cpu(), 0, 1, (C.c_char * 128)()) == 1 and b"CUDA device" in l.dl_last_error()
+    assert l.dl_b200_tp_symmetric_open(B.cuda(0), (C.c_char * 64)(), 1) == 1 and b"not initialised" in l.dl_last_error()
