@@ -151,7 +151,7 @@ def _declare(l: C.CDLL) -> None:
         "b200_linear_argmax_parts": (i32, [i64, i64, i64]),
         "b200_tp_reduce_parts": (i32, [i64]), "b200_tp_region_bytes": (sz, [sz]), "b200_tp_slot": (vp, [vp, sz, i32]),
         "b200_tp_reduce_shadow": (C.c_int, [pp, i32, i32, i32, sz, i64, i64, vp, i32, vp, vp, vp, vp, vp]),
-        "b200_argmax_finish": (C.c_int, [vp, vp, i32, i64, vp, vp, vp, i64, vp, vp]),
+        "b200_argmax_finish": (C.c_int, [vp, vp, i32, i64, vp, vp, vp, i64, vp, pp, i32, vp]),
         "b200_scaled_add": (C.c_int, [vp, vp, C.c_float, i64, vp]),
         "b200_take_device_status": (C.c_int, [i32, vp, C.POINTER(i32)]),
     }

@@ -334,7 +334,7 @@ bool DecodePlan::prepare_choice(const Linear& output, Index rows, int device) {
 }
 
 void DecodePlan::choose(const Linear& output, Index rows, Index* next, Index* ids, Index* history, Index history_rows, std::int32_t* counter,
-                        void* stream) {
+                        std::span<b200_kv_cache* const> advance, void* stream) {
     const Index V = output.weight().size(0), D = owner_.dimensions();
     const Index parts = b200_linear_argmax_parts(rows, D, V);
     if (parts <= 0 || !best_value_.defined() || best_value_.numel() < parts * rows)
@@ -349,7 +349,7 @@ void DecodePlan::choose(const Linear& output, Index rows, Index* next, Index* id
     args.best_index = static_cast<std::int32_t*>(best_index_.mutable_data());
     shadow_linear(args, stream, "logits + argmax");
     runtime::check(b200_argmax_finish(args.best_value, args.best_index, static_cast<std::int32_t>(parts), rows, next, ids, history, history_rows,
-                                      counter, stream), "argmax merge");
+                                      counter, advance.data(), static_cast<std::int32_t>(advance.size()), stream), "argmax merge");
     probe(2);
 }
 
@@ -606,11 +606,16 @@ void Generation::enqueue_step(void* stream, Index max_length) {
     plan.run_layers(x_.data<float>(), batch_, 1, *cache_, max_length, stream, plan.shadows_for(batch_));
     std::vector<b200_kv_cache*> handles;
     for (auto& layer : *cache_) handles.push_back(layer.handle());
+    if (fused_choice_ && handles.size() <= 64) {   // the merge kernel of the fused choice also advances the caches
+        plan.choose(*output_, batch_, static_cast<Index*>(next_.mutable_data()), static_cast<Index*>(ids_.mutable_data()),
+                    static_cast<Index*>(history_.mutable_data()), max_steps_, static_cast<int32_t*>(counter_.mutable_data()), handles, stream);
+        return;
+    }
     runtime::check(b200_kv_cache_advance(handles.data(), static_cast<int32_t>(handles.size()), 1, stream), "KV advance");
     probe(2);
     if (fused_choice_) {
         plan.choose(*output_, batch_, static_cast<Index*>(next_.mutable_data()), static_cast<Index*>(ids_.mutable_data()),
-                    static_cast<Index*>(history_.mutable_data()), max_steps_, static_cast<int32_t*>(counter_.mutable_data()), stream);
+                    static_cast<Index*>(history_.mutable_data()), max_steps_, static_cast<int32_t*>(counter_.mutable_data()), {}, stream);
         return;
     }
     plan.logits(*output_, batch_, static_cast<float*>(logits_.mutable_data()), stream);

@@ -41,8 +41,9 @@ public:
     // whether the fused path serves this projection and row count; choose() enqueues the projection with the argmax
     // epilogue and the merge, which also feeds the chosen ids back (ids, history, counter as b200_token_feedback).
     bool prepare_choice(const Linear& output, Index rows, int device);
+    // `advance`: caches (at most 64) whose lengths the merge kernel moves on by one token, sparing the step a launch.
     void choose(const Linear& output, Index rows, Index* next, Index* ids, Index* history, Index history_rows, std::int32_t* counter,
-                void* stream);
+                std::span<b200_kv_cache* const> advance, void* stream);
     // Who ran the plan last: the final hidden state in the workspaces belongs to that user (nullptr: Module::decode).
     void set_user(const void* user) { user_ = user; }
     const void* user() const { return user_; }

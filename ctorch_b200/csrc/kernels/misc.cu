@@ -1,6 +1,7 @@
 // Small operators of the token loop (embedding gather, stand-alone RMSNorm, argmax, row select) and the host
 // utilities shared by the kernel files (error text, driver entry point lookup, device status word).
 #include "linear_common.cuh"
+#include "kv_cache.cuh"
 
 #include <cstring>
 #include <mutex>
@@ -266,9 +267,10 @@ __global__ void token_feedback_kernel(const int64_t* next, int64_t batch, int64_
 
 // Merge of the per-tile candidates of the fused logits + argmax: warp w takes rows w, w + warps, ...; its lanes walk the
 // tiles, a butterfly leaves the row's choice, and lane 0 does the token bookkeeping of token_feedback_kernel.
+struct LengthList { int32_t* lengths[64]; int32_t counts[64]; int32_t caches; };
 __global__ void __launch_bounds__(1024) argmax_finish_kernel(const float* best_value, const int32_t* best_index, int parts, int64_t rows,
                                                              int64_t* next, int64_t* ids, int64_t* history, int64_t history_rows,
-                                                             int32_t* counter) {
+                                                             int32_t* counter, const LengthList advance) {
     grid_dependency_wait();
     grid_launch_dependents();
     const int32_t step = *counter;
@@ -298,6 +300,9 @@ __global__ void __launch_bounds__(1024) argmax_finish_kernel(const float* best_v
             if (history && step < history_rows) history[static_cast<int64_t>(step) * rows + row] = token;
         }
     }
+    // end of a step: the caches (one per layer) move on by the token every earlier kernel of the step appended and read
+    for (int c = 0; c < advance.caches; ++c)
+        for (int i = threadIdx.x; i < advance.counts[c]; i += blockDim.x) advance.lengths[c][i] += 1;
     __syncthreads();
     if (threadIdx.x == 0) *counter = step + 1;
 }
@@ -398,11 +403,24 @@ int b200_rotary(const float* x, int64_t outer, int64_t length, int64_t head_dim,
 }
 
 int b200_argmax_finish(const float* best_value, const int32_t* best_index, int32_t parts, int64_t rows, int64_t* next, int64_t* ids,
-                       int64_t* history, int64_t history_rows, int32_t* counter, void* stream) {
-    if (!best_value || !best_index || !next || !counter || parts <= 0 || rows <= 0) { set_error("b200_argmax_finish: bad pointer or size"); return B200_BAD_ARGUMENT; }
+                       int64_t* history, int64_t history_rows, int32_t* counter, b200_kv_cache* const* caches, int32_t cache_count,
+                       void* stream) {
+    if (!best_value || !best_index || !next || !counter || parts <= 0 || rows <= 0 || cache_count < 0 || cache_count > 64
+        || (cache_count > 0 && !caches)) {
+        set_error("b200_argmax_finish: bad pointer or size");
+        return B200_BAD_ARGUMENT;
+    }
+    b200::LengthList advance{};
+    advance.caches = cache_count;
+    for (int i = 0; i < cache_count; ++i) {
+        if (!caches[i]) { set_error("b200_argmax_finish: cache %d is NULL", i); return B200_BAD_ARGUMENT; }
+        advance.lengths[i] = caches[i]->lengths;
+        advance.counts[i] = caches[i]->sequences;
+    }
     const unsigned threads = rows >= 32 ? 1024 : static_cast<unsigned>(rows) * 32;
     return cuda_status(launch_dependent(b200::argmax_finish_kernel, dim3(1), dim3(threads), 0, as_stream(stream), best_value, best_index,
-                                        static_cast<int>(parts), rows, next, ids, history, history_rows, counter), "argmax_finish_kernel launch");
+                                        static_cast<int>(parts), rows, next, ids, history, history_rows, counter, advance),
+                       "argmax_finish_kernel launch");
 }
 
 int b200_sample(const float* x, int64_t rows, int64_t width, double temperature, const double* uniform, int64_t* index, void* stream) {

@@ -162,9 +162,11 @@ B200_API int32_t b200_linear_shadow_parts(int64_t rows, int64_t in, int64_t out)
 B200_API int32_t b200_linear_argmax_parts(int64_t rows, int64_t in, int64_t out);
 /* Second half of the fused logits + greedy choice: merges the `parts` per-tile candidates of every row (same rule), writes
  * the chosen feature index to next[rows], and does what b200_token_feedback does with it (ids, history, counter; any of
- * ids / history may be NULL).  One launch of one CTA. */
+ * ids / history may be NULL).  With caches (at most 64, one per layer) it also does b200_kv_cache_advance(caches, count, 1): the
+ * step's token becomes part of every cache.  One launch of one CTA. */
 B200_API int b200_argmax_finish(const float* best_value, const int32_t* best_index, int32_t parts, int64_t rows, int64_t* next,
-                                int64_t* ids, int64_t* history, int64_t history_rows, int32_t* counter, void* stream);
+                                int64_t* ids, int64_t* history, int64_t history_rows, int32_t* counter,
+                                b200_kv_cache* const* caches, int32_t cache_count, void* stream);
 /* b200_embedding that also writes the shadow of out * norm_weight and one partial sum of squares per row ([1][rows]). */
 B200_API int b200_embedding_shadow(const void* table, int32_t table_dtype, const int64_t* ids, int64_t rows, int64_t vocab,
                                    int64_t width, const void* norm_weight, int32_t norm_dtype, float* out, void* out_hi,

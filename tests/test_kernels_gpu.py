@@ -486,7 +486,7 @@ def test_fused_logits_argmax(rows, inner, vocab):
                               None, None, None, 0, None, best_value.data_ptr(), best_index.data_ptr())
     B.kcheck(l.b200_linear_shadow(C.byref(args), stream()))
     B.kcheck(l.b200_argmax_finish(best_value.data_ptr(), best_index.data_ptr(), parts, rows, next_ids.data_ptr(), ids.data_ptr(),
-                                  history.data_ptr(), 3, counter.data_ptr(), stream()))
+                                  history.data_ptr(), 3, counter.data_ptr(), None, 0, stream()))
     sync()
     got = next_ids.cpu().numpy()
     # a tie in the oracle's f32 sums may not be a tie in the tensor-core sums (other summation order) only if the clone rows
