@@ -119,7 +119,9 @@ __device__ __forceinline__ int balanced_pages_per_split(int pages, int planned) 
     return needed > 0 ? (pages + needed - 1) / needed : planned;
 }
 
-template <int HD, int STAGES>
+// MULTI: items of several positions (prefill chunks); the decode instantiation keeps one position per item and one key
+// count for all of its rows.
+template <int HD, int STAGES, bool MULTI>
 __global__ void __launch_bounds__(kFastThreads) attention_mma_kernel(const __grid_constant__ CUtensorMap kmap,
                                                                      const __grid_constant__ CUtensorMap vmap,
                                                                      const AttnParams p) {
@@ -139,10 +141,11 @@ __global__ void __launch_bounds__(kFastThreads) attention_mma_kernel(const __gri
     // the group.  Prefill: 16 / group positions share every K/V byte the CTA streams.
     const int item = blockIdx.x, split = blockIdx.y;
     const int kvh = item % p.kv.kv_heads, block = item / p.kv.kv_heads;
-    const int blocks_per_sequence = (p.tokens_per_sequence + p.positions_per_item - 1) / p.positions_per_item;
+    const int positions = MULTI ? p.positions_per_item : 1;
+    const int blocks_per_sequence = (p.tokens_per_sequence + positions - 1) / positions;
     const int sequence = block / blocks_per_sequence;
-    const int t_first = (block - sequence * blocks_per_sequence) * p.positions_per_item;
-    const int t_count = min(p.positions_per_item, p.tokens_per_sequence - t_first);
+    const int t_first = (block - sequence * blocks_per_sequence) * positions;
+    const int t_count = MULTI ? min(positions, p.tokens_per_sequence - t_first) : 1;
     const int row = sequence * p.tokens_per_sequence + t_first;   // first activation row of the item
     const int base_len = p.kv.lengths[sequence];
     const int kv_len = base_len + (p.causal ? t_first + t_count : 0);   // keys the item's last position sees
@@ -201,10 +204,10 @@ __global__ void __launch_bounds__(kFastThreads) attention_mma_kernel(const __gri
         const int g = lane >> 2, t = lane & 3;
         uint32_t qa[HD / 16][4];
         // this thread's two fragment rows: position and head inside the item, and the keys each may see
-        const int pos0 = g / group, pos1 = (g + 8) / group;
+        const int pos0 = MULTI ? g / group : 0, pos1 = MULTI ? (g + 8) / group : 0;
         const bool v0 = g < group * t_count, v1 = g + 8 < group * t_count;
-        const int limit0 = v0 ? base_len + (p.causal ? t_first + pos0 + 1 : 0) : 0;
-        const int limit1 = v1 ? base_len + (p.causal ? t_first + pos1 + 1 : 0) : 0;
+        const int limit0 = MULTI ? (v0 ? base_len + (p.causal ? t_first + pos0 + 1 : 0) : 0) : kv_len;
+        const int limit1 = MULTI ? (v1 ? base_len + (p.causal ? t_first + pos1 + 1 : 0) : 0) : kv_len;
         {
             const float* q0 = p.q + (static_cast<int64_t>(row + pos0) * p.heads + kvh * group + (g - pos0 * group)) * HD;
             const float* q1 = p.q + (static_cast<int64_t>(row + pos1) * p.heads + kvh * group + (g + 8 - pos1 * group)) * HD;
@@ -252,7 +255,7 @@ __global__ void __launch_bounds__(kFastThreads) attention_mma_kernel(const __gri
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
                     const int token = token_base + n * 8 + (e & 1);
-                    const float v = token < ((e >> 1) ? limit1 : limit0) ? sc[n][e] * p.scale : -INFINITY;
+                    const float v = token < (MULTI ? ((e >> 1) ? limit1 : limit0) : kv_len) ? sc[n][e] * p.scale : -INFINITY;
                     sc[n][e] = v;
                     mx[e >> 1] = fmaxf(mx[e >> 1], v);
                 }
@@ -340,7 +343,7 @@ __global__ void __launch_bounds__(kFastThreads) attention_mma_kernel(const __gri
             acc += weight * merge_o[(w * 16 + r) * HD + d];
             l += weight * merge_ml[(w * 16 + r) * 2 + 1];
         }
-        const int position = r / group;
+        const int position = MULTI ? r / group : 0;
         const int64_t head_item = static_cast<int64_t>(row + position) * p.heads + kvh * group + (r - position * group);
         if (p.num_splits == 1) {
             store_result(p, head_item * HD + d, acc / l);
@@ -462,7 +465,7 @@ __global__ void attention_combine_kernel(const AttnParams p) {
 
 template <int HD, int STAGES> int launch_fast(const b200_kv_cache* cache, const AttnParams& p, cudaStream_t stream) {
     using S = FastShape<HD, STAGES>;
-    auto kernel = attention_mma_kernel<HD, STAGES>;
+    auto kernel = p.positions_per_item > 1 ? attention_mma_kernel<HD, STAGES, true> : attention_mma_kernel<HD, STAGES, false>;
     B200_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, S::smem_bytes));
     const int blocks_per_sequence = (p.tokens_per_sequence + p.positions_per_item - 1) / p.positions_per_item;
     const dim3 grid(static_cast<unsigned>(p.rows / p.tokens_per_sequence) * blocks_per_sequence * p.kv.kv_heads, p.num_splits);
