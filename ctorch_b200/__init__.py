@@ -113,6 +113,7 @@ def _declare(l: C.CDLL) -> None:
         "dl_generation_create": (C.c_int, [vp, vp, vp, vp, i64, i64, pp]), "dl_generation_release": (None, [vp]),
         "dl_generation_prefill": (C.c_int, [vp, vp]), "dl_generation_step": (C.c_int, [vp, i64]),
         "dl_generation_step_host": (C.c_int, [vp, C.POINTER(i64), C.POINTER(i64)]),
+        "dl_generation_run_host": (C.c_int, [vp, C.POINTER(i64), i64, C.POINTER(i64)]),
         "dl_generation_tokens": (C.c_int, [vp, pp]), "dl_generation_logits": (C.c_int, [vp, pp]),
         "dl_generation_launches_per_step": (i64, [vp]),
         "dl_decoder_generate": (C.c_int, [vp, vp, vp, vp, i64, vp, pp]),
@@ -479,6 +480,14 @@ class Generation:
         ip = C.POINTER(C.c_int64)
         check(lib().dl_generation_step_host(self.h, ids_in.ctypes.data_as(ip) if ids_in is not None else None,
                                             ids_out.ctypes.data_as(ip)))
+
+    def run_host(self, ids_in: np.ndarray | None, steps: int) -> np.ndarray:
+        """`steps` host-in-the-loop steps in one library call; returns the chosen ids [steps, batch]."""
+        ip = C.POINTER(C.c_int64)
+        out = np.empty((steps, self.batch), dtype=np.int64)
+        check(lib().dl_generation_run_host(self.h, ids_in.ctypes.data_as(ip) if ids_in is not None else None, steps,
+                                           out.ctypes.data_as(ip)))
+        return out
 
     def step_sampled(self, temperature: float, uniforms: np.ndarray) -> np.ndarray:
         u = np.ascontiguousarray(uniforms, dtype=np.float64)

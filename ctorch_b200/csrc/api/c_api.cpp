@@ -337,6 +337,14 @@ dl_status dl_generation_step(dl_generation* generation, int64_t steps) {
 dl_status dl_generation_step_host(dl_generation* generation, const int64_t* ids_in, int64_t* ids_out) {
     return invoke([&] { need(generation, "generation").value->step_host(ids_in, ids_out); });
 }
+dl_status dl_generation_run_host(dl_generation* generation, const int64_t* ids_in, int64_t steps, int64_t* ids_out) {
+    return invoke([&] {
+        auto& run = *need(generation, "generation").value;
+        if (steps < 0 || (steps > 0 && !ids_out)) throw std::invalid_argument("run_host needs a non-negative step count and a result buffer");
+        const int64_t batch = run.batch();
+        for (int64_t i = 0; i < steps; ++i) run.step_host(i == 0 ? ids_in : ids_out + (i - 1) * batch, ids_out + i * batch);
+    });
+}
 dl_status dl_generation_step_sampled(dl_generation* generation, double temperature, const double* uniforms, int64_t* ids_out) {
     return invoke([&] { need(generation, "generation").value->step_sampled(temperature, uniforms, ids_out); });
 }

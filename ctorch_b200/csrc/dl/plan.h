@@ -95,6 +95,7 @@ public:
     // the chosen ids go to ids_out [batch] (may be NULL) and feed the next step.
     void step_sampled(double temperature, const double* uniforms, Index* ids_out);
     Index generated() const { return generated_; }
+    Index batch() const { return batch_; }
     Tensor tokens() const;         // [batch, generated] int64 on the host (synchronises)
     // [batch, vocab] f32 on the device: logits the latest token was chosen from.  Steps choose their token without
     // writing logits; they are computed here, on demand, from the final hidden state of the last step, which is only

@@ -99,6 +99,26 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, uint32
     return false;
 }
 
+// One lane of a fully active warp (the same lane on every call).  The warp-specialised loops below keep the whole warp in
+// uniform control flow and put only the issuing instruction under this predicate: TMA and tcgen05 instructions take their
+// operands from uniform registers, which the compiler can only fill cheaply while control flow is warp-uniform.  A loop
+// run by one lane alone (`if (lane == 0) for (...)`) pays a chain of per-operand transfers for every instruction issued.
+__device__ __forceinline__ bool elect_one() {
+    uint32_t chosen;
+    asm volatile("{\n .reg .pred p;\n elect.sync _|p, 0xffffffff;\n selp.u32 %0, 1, 0, p;\n}" : "=r"(chosen));
+    return chosen != 0;
+}
+
+// The same for waits that last a whole main loop (epilogue warps waiting for an accumulator): the warp sleeps between
+// polls, so that its polling does not compete with the warps that issue the loads and the products.
+__device__ __forceinline__ bool mbar_wait_relaxed(uint64_t* bar, uint32_t parity, uint32_t limit = 4000000u) {
+    for (uint32_t i = 0; i < limit; ++i) {
+        if (mbar_try_wait(bar, parity)) return true;
+        __nanosleep(128);
+    }
+    return false;
+}
+
 // 2-D tiled TMA load global -> shared, completion on an mbarrier, this CTA only.
 __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int32_t x, int32_t y, uint64_t* bar) {
     asm volatile(

@@ -32,6 +32,16 @@ __device__ __forceinline__ void kv_store_pair(const KvView& kv, int which, int s
     }
 }
 
+// The same with the physical page of the position already known.
+__device__ __forceinline__ void kv_store_pair_at(const KvView& kv, int which, int page, int position, int head, int d, float a, float b) {
+    const int64_t at = ((static_cast<int64_t>(page) * kv.kv_heads + head) * kv.page_size + position % kv.page_size) * kv.head_dim + d;
+    if (kv.dtype == B200_BF16) {
+        *reinterpret_cast<__nv_bfloat162*>(static_cast<__nv_bfloat16*>(kv.pool[which]) + at) = __floats2bfloat162_rn(a, b);
+    } else {
+        *reinterpret_cast<float2*>(static_cast<float*>(kv.pool[which]) + at) = make_float2(a, b);
+    }
+}
+
 __device__ __forceinline__ float kv_load(const KvView& kv, int which, int64_t at) {
     return kv.dtype == B200_BF16 ? __bfloat162float(static_cast<const __nv_bfloat16*>(kv.pool[which])[at])
                                  : static_cast<const float*>(kv.pool[which])[at];

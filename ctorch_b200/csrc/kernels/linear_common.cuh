@@ -59,8 +59,10 @@ __device__ __forceinline__ Candidate pair_candidate(int feature0, float a, float
 //   store | residual add (src/nn/decoder.cpp:104-105) | SiLU(gate)*up on interleaved rows (src/nn/decoder.cpp:16) |
 //   q|k|v: adapter delta (src/nn/decoder.cpp:26-28), adjacent-pair RoPE (src/ops/contraction.cpp:44-49), q store,
 //   k/v append to the paged cache (src/nn/kv_cache.cpp:24-28)
+//   `place` (optional, q|k|v only): the row's position and physical cache page, looked up once per row by the caller
+//   (x = position, y = page) instead of once per feature pair here.
 template <int EPI>
-__device__ __forceinline__ void linear_epilogue(const LinearParams& p, int row, int feature0, float& a, float& b) {
+__device__ __forceinline__ void linear_epilogue(const LinearParams& p, int row, int feature0, float& a, float& b, const int2* place = nullptr) {
     const bool second = feature0 + 1 < p.out;
     if constexpr (EPI == B200_EPI_STORE) {
         p.y[static_cast<int64_t>(row) * p.out + feature0] = a;
@@ -80,7 +82,7 @@ __device__ __forceinline__ void linear_epilogue(const LinearParams& p, int row, 
     } else {
         const int D = p.heads * p.head_dim, KV = p.kv_heads * p.head_dim;
         const int sequence = row / p.tokens_per_sequence;
-        const int position = __ldg(p.kv.lengths + sequence) + row % p.tokens_per_sequence;
+        const int position = place ? place->x : __ldg(p.kv.lengths + sequence) + row % p.tokens_per_sequence;
         int region = 0, local = feature0;  // 0 = q, 1 = k, 2 = v
         if (local >= D) { region = 1; local -= D; }
         if (region == 1 && local >= KV) { region = 2; local -= KV; }
@@ -135,6 +137,8 @@ __device__ __forceinline__ void linear_epilogue(const LinearParams& p, int row, 
             float* q = p.q_out + static_cast<int64_t>(row) * D + local;
             q[0] = a;
             q[1] = b;
+        } else if (place) {
+            kv_store_pair_at(p.kv, region - 1, place->y, position, head, d, a, b);
         } else {
             kv_store_pair(p.kv, region - 1, sequence, position, head, d, a, b);
         }
@@ -153,5 +157,13 @@ int launch_linear_gemm(const LinearParams& p, int epilogue, cudaStream_t stream)
 int linear_gemm_parts(int rows, int in, int out);
 // Row count from which the dense tensor-core kernel replaces the streaming one.
 constexpr int kGemmRows = 17;
+// Decode batches on the tensor cores with the weights as the streamed operand (linear_decode.cu): up to 256 rows.
+struct DecodeShape {
+    int tiles, split, ctas, stages, stage_bytes, n_pad, n_alloc, tmem_columns, body_bytes, smem_bytes, token_tile, token_tiles;
+};
+DecodeShape linear_decode_shape(int rows, int in, int out, bool two_planes, int sms);
+bool linear_decode_takes(int rows);
+int linear_decode_parts(int rows, int in, int out);
+int launch_linear_decode(const LinearParams& p, int epilogue, cudaStream_t stream);
 
 }  // namespace b200

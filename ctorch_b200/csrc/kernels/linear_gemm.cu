@@ -19,7 +19,8 @@
 // then), and after a cluster barrier each CTA sums a band of rows of the tile over all peers (distributed shared
 // memory, fixed order z = 0..S-1, so results do not depend on timing) and runs the epilogue on that band.
 // Reference arithmetic replaced: src/ops/matmul.cpp:35-67 -> src/kernels/cpu/matmul.h:10-22 for rows = batch * length.
-#include "linear_common.cuh"
+#include "linear_rows.cuh"
+#include "tcgen05.cuh"
 
 namespace b200 {
 namespace {
@@ -44,187 +45,6 @@ struct GemmParams {
     LinearParams base;
     int32_t* status;
 };
-
-__device__ __forceinline__ void tmem_alloc(uint32_t* slot, uint32_t columns) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(slot)), "r"(columns) : "memory");
-}
-__device__ __forceinline__ void tmem_relinquish() { asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory"); }
-__device__ __forceinline__ void tmem_dealloc(uint32_t address, uint32_t columns) {
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(address), "r"(columns) : "memory");
-}
-__device__ __forceinline__ void tc_fence_before_sync() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after_sync() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_commit(uint64_t* bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
-__device__ __forceinline__ void tc_mma_bf16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
-    asm volatile(
-        "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
-        " tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}"
-        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
-}
-__device__ __forceinline__ void tmem_load_32(uint32_t address, uint32_t (&r)[32]) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,"
-        "%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
-          "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]),
-          "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
-          "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-        : "r"(address));
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-}
-
-// Shared-memory matrix descriptor of a K-major operand tile [rows][64 bf16] written by TMA with 128-byte swizzle:
-// 8-row groups of 1024 bytes follow each other (stride byte offset 1024), descriptor version 1, layout type 2.
-__device__ __forceinline__ uint64_t operand_descriptor(uint32_t smem_address) {
-    uint64_t d = 0;
-    d |= static_cast<uint64_t>((smem_address & 0x3ffff) >> 4);   // start address, 16-byte units
-    d |= static_cast<uint64_t>(1) << 16;                          // leading byte offset (unused for swizzled K-major)
-    d |= static_cast<uint64_t>(1024 >> 4) << 32;                  // stride byte offset between 8-row groups
-    d |= static_cast<uint64_t>(1) << 46;                          // descriptor version of this architecture
-    d |= static_cast<uint64_t>(2) << 61;                          // 128-byte swizzle
-    return d;
-}
-
-// One finished pair of adjacent features of one token row: shared epilogue, then the optional output shadow (hi + lo of
-// the value times the next norm weight) and the running sum of squares of the new residual stream.
-// `carried` holds the residual values of the pair (B200_EPI_RESIDUAL only), loaded ahead by the caller.
-template <int EPI>
-__device__ __forceinline__ void finish_pair(const LinearParams& p, int row, int feature0, float a, float b, float2 carried, float& squares) {
-    if constexpr (EPI == B200_EPI_RESIDUAL) {
-        const bool second = feature0 + 1 < p.out;
-        const int64_t at = static_cast<int64_t>(row) * p.out + feature0;
-        a = __fadd_rn(carried.x, a);
-        b = second ? __fadd_rn(carried.y, b) : 0.0f;
-        if ((p.out & 1) == 0) {
-            *reinterpret_cast<float2*>(p.y + at) = make_float2(a, b);
-        } else {
-            p.y[at] = a;
-            if (second) p.y[at + 1] = b;
-        }
-    } else {
-        linear_epilogue<EPI>(p, row, feature0, a, b);
-    }
-    if constexpr (EPI == B200_EPI_RESIDUAL) {
-        const bool second = feature0 + 1 < p.out;
-        squares += a * a + (second ? b * b : 0.0f);
-        if (p.out_hi) {
-            float wa = 1.0f, wb = 1.0f;
-            if (p.out_norm_weight) {
-                if (p.out_norm_dtype == B200_BF16) {
-                    const __nv_bfloat16* w = static_cast<const __nv_bfloat16*>(p.out_norm_weight) + feature0;
-                    wa = __bfloat162float(w[0]);
-                    wb = second ? __bfloat162float(w[1]) : 0.0f;
-                } else {
-                    const float* w = static_cast<const float*>(p.out_norm_weight) + feature0;
-                    wa = w[0];
-                    wb = second ? w[1] : 0.0f;
-                }
-            }
-            const float va = __fmul_rn(a, wa), vb = __fmul_rn(b, wb);
-            const __nv_bfloat162 hi = __floats2bfloat162_rn(va, vb);
-            const __nv_bfloat162 lo = __floats2bfloat162_rn(va - __low2float(hi), vb - __high2float(hi));
-            const int64_t at = static_cast<int64_t>(row) * p.out + feature0;
-            *reinterpret_cast<__nv_bfloat162*>(p.out_hi + at) = hi;
-            *reinterpret_cast<__nv_bfloat162*>(p.out_lo + at) = lo;
-        }
-    }
-    if constexpr (EPI == B200_EPI_SWIGLU) {
-        if (p.out_hi) {
-            const __nv_bfloat16 hi = __float2bfloat16_rn(a);
-            const int64_t at = static_cast<int64_t>(row) * (p.out >> 1) + (feature0 >> 1);
-            p.out_hi[at] = hi;
-            p.out_lo[at] = __float2bfloat16_rn(a - __bfloat162float(hi));
-        }
-    }
-}
-
-// Finishes the rows [first, last) of a tile held row-major in shared memory (`tile`, or the sum over the cluster's
-// `split` partial tiles `peer_tile[z]`).  Warp `worker` of `workers` takes kBatch consecutive rows per iteration: first
-// every value the rows need is requested (accumulators from shared memory or from the peers, residual pairs from global
-// memory), then the rows are finished, so the memory round trips of the rows overlap instead of queueing behind each
-// other.  Lanes run across the feature pairs: every global access is coalesced; per-row reductions are butterflies.
-template <int EPI, int kTileN>
-__device__ __forceinline__ void finish_rows(const LinearParams& p, const float* tile, const uint32_t (&peer_tile)[8], int split,
-                                            const float* row_scale, int m0, int n0, int feature_tile, int first, int last, int worker,
-                                            int workers, int lane, bool ready) {
-    constexpr int kTileStride = kTileN + 4;
-        constexpr int kBatch = 4, kPasses = kTileN / 64;
-        for (int base = first + worker * kBatch; base < last; base += workers * kBatch) {
-            float2 value[kBatch][kPasses], carried[kBatch][kPasses];
-#pragma unroll
-            for (int r = 0; r < kBatch; ++r) {
-                const int tile_row = base + r, row = m0 + tile_row;
-                const bool live_row = tile_row < last && row < p.rows;
-#pragma unroll
-                for (int pass = 0; pass < kPasses; ++pass) {
-                    const int c = pass * 64 + lane * 2;
-                    const int feature0 = n0 + c;
-                    value[r][pass] = make_float2(0.0f, 0.0f);
-                    carried[r][pass] = make_float2(0.0f, 0.0f);
-                    if (!live_row) continue;
-                    if (split == 1) {
-                        value[r][pass] = *reinterpret_cast<const float2*>(tile + tile_row * kTileStride + c);
-                    } else {
-                        const uint32_t offset = static_cast<uint32_t>(tile_row * kTileStride + c) * 4;
-                        float2 v[8];
-#pragma unroll
-                        for (int z = 0; z < 8; ++z) v[z] = z < split ? load_cluster_float2(peer_tile[z] + offset) : make_float2(0.0f, 0.0f);
-                        float2 sum = v[0];
-#pragma unroll
-                        for (int z = 1; z < 8; ++z) { sum.x += v[z].x; sum.y += v[z].y; }
-                        value[r][pass] = sum;
-                    }
-                    if constexpr (EPI == B200_EPI_RESIDUAL) {
-                        if (feature0 < p.out) {
-                            const float* source = p.residual + static_cast<int64_t>(row) * p.out + feature0;
-                            if ((p.out & 1) == 0) carried[r][pass] = *reinterpret_cast<const float2*>(source);
-                            else carried[r][pass] = make_float2(source[0], feature0 + 1 < p.out ? source[1] : 0.0f);
-                        }
-                    }
-                }
-            }
-#pragma unroll
-            for (int r = 0; r < kBatch; ++r) {
-                const int tile_row = base + r, row = m0 + tile_row;
-                if (tile_row >= last || row >= p.rows) break;
-                const float scale = row_scale[tile_row];
-                float squares = 0.0f;
-                Candidate best{-INFINITY, INT32_MAX};
-#pragma unroll
-                for (int pass = 0; pass < kPasses; ++pass) {
-                    const int feature0 = n0 + pass * 64 + lane * 2;
-                    if (!ready || feature0 >= p.out) continue;
-                    const float a = value[r][pass].x * scale, b = value[r][pass].y * scale;
-                    if constexpr (EPI == B200_EPI_ARGMAX) {
-                        const Candidate pair = pair_candidate(feature0, a, b, p.out);
-                        if (preferred(pair, best)) best = pair;
-                    } else {
-                        finish_pair<EPI>(p, row, feature0, a, b, carried[r][pass], squares);
-                    }
-                }
-                if constexpr (EPI == B200_EPI_RESIDUAL) {
-                    if (p.sumsq_out) {
-#pragma unroll
-                        for (int o = 16; o > 0; o >>= 1) squares += __shfl_xor_sync(0xffffffffu, squares, o);
-                        if (lane == 0) p.sumsq_out[static_cast<int64_t>(feature_tile) * p.rows + row] = squares;
-                    }
-                }
-                if constexpr (EPI == B200_EPI_ARGMAX) {
-#pragma unroll
-                    for (int o = 16; o > 0; o >>= 1) {
-                        const Candidate other{__shfl_xor_sync(0xffffffffu, best.value, o), __shfl_xor_sync(0xffffffffu, best.index, o)};
-                        if (preferred(other, best)) best = other;
-                    }
-                    if (lane == 0) {
-                        p.best_value[static_cast<int64_t>(feature_tile) * p.rows + row] = best.value;
-                        p.best_index[static_cast<int64_t>(feature_tile) * p.rows + row] = best.index;
-                    }
-                }
-            }
-        }
-    }
 
 template <int EPI, int TN, int STAGES>
 __global__ void __launch_bounds__(kGemmThreads, STAGES == 2 && TN == 128 ? 2 : 1) linear_gemm_kernel(const __grid_constant__ CUtensorMap map_hi,
@@ -621,6 +441,7 @@ int launch_epilogue(int epilogue, const CUtensorMap& hi, const CUtensorMap& lo, 
 }  // namespace
 
 int linear_gemm_parts(int rows, int in, int out) {
+    if (linear_decode_takes(rows)) return linear_decode_parts(rows, in, out);
     const int tn = choose_tile_features(rows, in, out);
     return (out + tn - 1) / tn;   // one partial per feature tile: a row of a tile is finished by one CTA of the cluster
 }
@@ -647,6 +468,7 @@ int launch_persistent(int epilogue, const CUtensorMap& hi, const CUtensorMap& lo
 }
 
 int launch_linear_gemm(const LinearParams& p, int epilogue, cudaStream_t stream) {
+    if (linear_decode_takes(p.rows)) return launch_linear_decode(p, epilogue, stream);   // decode batches: weights streamed once
     if (p.weight_dtype != B200_BF16 || !p.x_hi || (p.in & 7) || (p.out_hi && (p.out & 1))
         || ((reinterpret_cast<uintptr_t>(p.weight) | reinterpret_cast<uintptr_t>(p.x_hi) | reinterpret_cast<uintptr_t>(p.x_lo)) & 15))
         return B200_UNSUPPORTED;

@@ -69,17 +69,28 @@ def tensor_shapes(spec: dict) -> list[tuple[str, tuple[int, ...]]]:
     return out
 
 
-def make_weights(spec: dict, seed: int = 1234, scale: float = 0.02) -> list[np.ndarray]:
-    """Ordered tensors in the model dtype (float32 arrays, or uint16 bf16 bit patterns)."""
-    tensors = []
-    for index, (name, shape) in enumerate(tensor_shapes(spec)):
+def make_weights(spec: dict, seed: int = 1234, scale: float = 0.02, threads: int | None = None) -> list[np.ndarray]:
+    """Ordered tensors in the model dtype (float32 arrays, or uint16 bf16 bit patterns).  Every tensor has its own
+    generator seeded by (seed, index), so the draws do not depend on how many worker threads make them."""
+    def one(item):
+        index, (name, shape) = item
         rng = np.random.default_rng([seed, index])
         if name.endswith("norm.weight") or name.endswith("normalization.weight"):
             w = (1.0 + 0.1 * rng.standard_normal(shape)).astype(np.float32)
         else:
-            w = (scale * rng.standard_normal(shape, dtype=np.float32)).astype(np.float32)
-        tensors.append(bf16_bits(w) if spec["dtype"] == "bf16" else w)
-    return tensors
+            w = rng.standard_normal(shape, dtype=np.float32)
+            w *= np.float32(scale)
+        return bf16_bits(w) if spec["dtype"] == "bf16" else w
+
+    items = list(enumerate(tensor_shapes(spec)))
+    if threads is None:
+        import os
+        threads = min(16, len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1))
+    if threads <= 1 or len(items) < 4:
+        return [one(item) for item in items]
+    from concurrent.futures import ThreadPoolExecutor
+    with ThreadPoolExecutor(max_workers=threads) as pool:   # numpy releases the GIL inside the generators
+        return list(pool.map(one, items))
 
 
 def make_lora(spec: dict, seed: int = 4321) -> list[np.ndarray] | None:

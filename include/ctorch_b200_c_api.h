@@ -174,6 +174,11 @@ DL_API dl_status dl_generation_step(dl_generation* generation, int64_t steps);
  * NULL to continue from the device-resident ids) is copied to the device, one step runs, the chosen ids are
  * copied back into ids_out [batch] (host) and the call waits for them. */
 DL_API dl_status dl_generation_step_host(dl_generation* generation, const int64_t* ids_in, int64_t* ids_out);
+/* `steps` tokens with the host in the loop, in one call: step i copies its ids [batch] from the host to the device (ids_in
+ * for i = 0, the ids step i - 1 returned afterwards), runs, and copies the chosen ids back into ids_out[i * batch ...]
+ * before step i + 1 starts - the loop of examples/decoder_generate.cpp:20-31 with its per-token host round trip, without
+ * an interpreter between the steps.  ids_out: host, [steps, batch]. */
+DL_API dl_status dl_generation_run_host(dl_generation* generation, const int64_t* ids_in, int64_t steps, int64_t* ids_out);
 /* One token drawn from softmax(logits / temperature) (the sibling example's loop, examples/text_generate.cpp:37-41): the
  * caller supplies one uniform variate in [0, 1) per sequence from its own generator; the draw is the inverse of the
  * running sum in index order, as std::discrete_distribution does.  Host in the loop like dl_generation_step_host.

@@ -36,8 +36,9 @@ class Config(C.Structure):
 def build(ref: bool = True) -> None:
     """Compile the port and, when the reference tree is present, the reference harness."""
     subprocess.run(["make", "-s", "port"], cwd=HERE, check=True)
-    if ref and os.path.isdir(os.environ.get("CTORCH_REFERENCE", "/root/reference")):
-        subprocess.run(["make", "-s", "-j8", "ref"], cwd=HERE, check=True)
+    reference = os.environ.get("CTORCH_REFERENCE", "/root/reference")
+    if ref and os.path.isdir(reference):
+        subprocess.run(["make", "-s", "-j8", "ref", "REF=" + reference], cwd=HERE, check=True)
 
 
 def have_ref() -> bool:
@@ -90,7 +91,7 @@ class CpuLib:
             f("cache_dtype", C.c_int, [C.c_void_p, C.c_int64])
             f("cache_copy", C.c_int, [C.c_void_p, C.c_int64, C.c_int32, fp])
             f("generate_threads", C.c_int, [C.c_void_p, ip] + [C.c_int64] * 4 + [ip])
-            f("timed_decode", C.c_int, [C.c_void_p, ip] + [C.c_int64] * 5 + [C.POINTER(C.c_double)])
+            f("timed_decode", C.c_int, [C.c_void_p, ip] + [C.c_int64] * 6 + [C.POINTER(C.c_double)])
             f("linear", C.c_int, [fp, C.c_void_p, C.c_int32, C.c_int64, C.c_int64, C.c_int64, fp])
             f("rotary", C.c_int, [fp] + [C.c_int64] * 4 + [C.c_double, C.c_int64, C.c_int64, fp])
             f("lora_linear", C.c_int, [fp, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32] + [C.c_int64] * 4
@@ -243,17 +244,21 @@ class CpuDecoder:
         return tokens
 
 
-def timed_decode(model: "CpuDecoder", prompt: np.ndarray, warmup: int, steps: int, threads: int) -> float:
+def timed_decode(model: "CpuDecoder", prompt: np.ndarray, warmup: int, steps: int, threads: int, cached: int = 0) -> float:
     """Seconds the CPU checker needs for `steps` greedy single-token steps of the whole batch after a prefill and
-    `warmup` untimed steps, with the batch spread over `threads` workers (each with its own cache)."""
+    `warmup` untimed steps, with the batch spread over `threads` workers (each with its own cache).  `cached` (reference
+    build only) puts that many positions of pseudo-random K and V into every cache before the prompt, so that the steps
+    attend over a long context without a CPU prefill of that length."""
     prompt = np.ascontiguousarray(prompt, dtype=np.int64)
     batch, plen = prompt.shape
     threads = max(1, min(threads, batch))
     if model.l.kind != "port":
         seconds = C.c_double()
-        model.l.check(model.l.timed_decode(model.handle, _ptr(prompt, C.c_int64), batch, plen, warmup, steps, threads,
+        model.l.check(model.l.timed_decode(model.handle, _ptr(prompt, C.c_int64), batch, plen, warmup, steps, threads, cached,
                                            C.byref(seconds)))
         return seconds.value
+    if cached:
+        raise ValueError("the plain-C restatement has no cache pre-fill; pass cached=0")
     # port: ctypes releases the GIL during calls, so Python threads run the C code in parallel
     import threading
     import time

@@ -252,8 +252,11 @@ int ref_generate_threads(void* handle, const int64_t* prompt, int64_t batch, int
 // CPU-baseline timing: every worker prefills its slice of the batch and runs `warmup` single-token steps, all
 // workers meet at a barrier, then each runs `steps` timed single-token steps (greedy feedback) and they meet again.
 // seconds = wall time between the two barriers.
+// `cached` > 0: before the prompt is decoded every layer cache receives `cached` positions of seeded pseudo-random K and V
+// through the public KVCache::append, so that the timed steps attend over `cached + prompt_length + ...` positions without
+// paying a CPU prefill of that length (step time depends on the context length, not on the cached values).
 int ref_timed_decode(void* handle, const int64_t* prompt, int64_t batch, int64_t prompt_length, int64_t warmup,
-                     int64_t steps, int64_t threads, double* seconds) {
+                     int64_t steps, int64_t threads, int64_t cached, double* seconds) {
     if (threads > batch) threads = batch;
     std::vector<int> status(static_cast<std::size_t>(threads), 0);
     std::chrono::steady_clock::time_point begin, end;
@@ -270,6 +273,17 @@ int ref_timed_decode(void* handle, const int64_t* prompt, int64_t batch, int64_t
                 if (!count) return;
                 auto& model = *static_cast<Model*>(handle);
                 cache.layers = model.decoder->make_cache();
+                if (cached > 0) {
+                    const int64_t hd = model.cfg.d_model / model.cfg.heads;
+                    std::vector<float> filler(static_cast<std::size_t>(count * model.cfg.kv_heads * cached * hd));
+                    std::uint32_t state = 0x9e3779b9u + static_cast<std::uint32_t>(t);
+                    for (auto& value : filler) {   // uniform in [-1, 1): a linear congruential sequence is enough here
+                        state = state * 1664525u + 1013904223u;
+                        value = static_cast<float>(static_cast<std::int32_t>(state)) * (1.0f / 2147483648.0f);
+                    }
+                    const auto block = host_tensor(filler.data(), {count, model.cfg.kv_heads, cached, hd}, dl::DType::f32);
+                    for (auto& layer : cache.layers) layer.append(block, block);
+                }
                 auto last = model_decode(model, cache, prompt + first * prompt_length, count, prompt_length).select(1, prompt_length - 1);
                 next = dl::argmax(last, -1).to_vector<int64_t>();
                 for (int64_t i = 0; i < warmup; ++i)

@@ -394,14 +394,19 @@ def test_shadow_protocol_swiglu_and_attention_output():
 
 @pytest.mark.parametrize("rows,inner,out,epilogue", [(40, 768, 1280, 0), (130, 2048, 768, 1), (300, 768, 4096, 2), (17, 4096, 200, 1),
                                                      (128, 72, 136, 0), (32, 4096, 1024, 1), (256, 2048, 3072, 2),
-                                                     (1000, 512, 2560, 0), (20, 256, 76000, 0), (1100, 2304, 2304, 1), (40, 4096, 32, 0), (300, 768, 24, 0)])
+                                                     (1000, 512, 2560, 0), (20, 256, 76000, 0), (1100, 2304, 2304, 1), (40, 4096, 32, 0), (300, 768, 24, 0),
+                                                     (64, 2048, 16384, 2), (256, 2048, 16384, 2), (200, 8192, 2048, 1), (96, 2048, 2048, 1),
+                                                     (32, 2048, 32000, 0), (48, 1032, 1000, 0), (257, 768, 1280, 1)])
 def test_dense_tensor_core_linear(rows, inner, out, epilogue):
-    """More than 16 rows (or a wide input) take the tcgen05 kernel: shadow input, split norm, every epilogue family.
-    Launches with few tiles split K over a thread-block cluster (the partial tiles summed through distributed shared
-    memory); (1000, 512, 2560) runs on the persistent variant (8 token tiles, short K, more tiles than SMs), (20, 256,
-    76000) on the 256-wide tile (vocabulary-sized output), (1100, 2304, 2304) on the plain one-tile-per-CTA kernel with
-    two CTAs per SM; the last two (at most 64 output features, store epilogue: adapter down-projections) on the thin CUDA-core
-    kernel."""
+    """More than 16 rows (or a wide input) take the tcgen05 kernels: shadow input, split norm, every epilogue family.
+    Up to 256 rows run on the decode-batch kernel (weights as the streamed M operand, tokens as the N side): one, two or four
+    weight tiles per CTA ((256, 2048, 16384): two tiles and a K split of two; (32, 2048, 32000): two tiles, no split), K split
+    over a thread-block cluster with the partial tiles summed through distributed shared memory ((200, 8192, 2048): eight
+    CTAs, a row count that is no multiple of 16), ragged last tiles and K blocks ((48, 1032, 1000), (17, 4096, 200)).  More
+    rows run on the prefill kernel: (1000, 512, 2560) on its persistent variant (8 token tiles, short K, more tiles than
+    SMs), (1100, 2304, 2304) one tile per CTA with two CTAs per SM, (300, 768, 4096) and (257, 768, 1280) with a K split;
+    (40, 4096, 32) and (300, 768, 24) (at most 64 output features, store epilogue: adapter down-projections) on the thin
+    CUDA-core kernel."""
     l = B.lib()
     rng = np.random.default_rng(rows + inner + out)
     x = rng.standard_normal((rows, inner), dtype=np.float32) * 2
