@@ -85,6 +85,7 @@ def _declare(l: C.CDLL) -> None:
         "dl_argmax": (C.c_int, [vp, i64, i32, pp]), "dl_linear": (C.c_int, [vp, vp, vp, pp]),
         "dl_embedding": (C.c_int, [vp, vp, pp]), "dl_rms_norm": (C.c_int, [vp, Shape, vp, C.POINTER(C.c_double), pp]),
         "dl_synchronize": (C.c_int, [Device]),
+        "dl_tensordot": (C.c_int, [vp, vp, Shape, Shape, pp]),
         "dl_rotary_embedding": (C.c_int, [vp, vp, vp, pp]), "dl_grouped_query_attention": (C.c_int, [vp, vp, vp, vp, pp]),
         "dl_module_release": (None, [vp]), "dl_module_retain": (C.c_int, [vp, pp]),
         "dl_linear_create": (C.c_int, [i64, i64, i32, TensorOptions, pp]), "dl_linear_from_tensors": (C.c_int, [vp, vp, pp]),
@@ -116,6 +117,7 @@ def _declare(l: C.CDLL) -> None:
         "dl_generation_run_host": (C.c_int, [vp, C.POINTER(i64), i64, C.POINTER(i64)]),
         "dl_generation_tokens": (C.c_int, [vp, pp]), "dl_generation_logits": (C.c_int, [vp, pp]),
         "dl_generation_launches_per_step": (i64, [vp]),
+        "dl_b200_shadow_partial_rows": (i64, [i64, i64]),
         "dl_decoder_generate": (C.c_int, [vp, vp, vp, vp, i64, vp, pp]),
         "dl_generation_profile_step": (C.c_int, [vp, C.POINTER(C.c_double)]),
         "dl_b200_tp_unique_id": (C.c_int, [vp]), "dl_b200_tp_init": (C.c_int, [Device, i32, i32, vp]),
@@ -132,6 +134,7 @@ def _declare(l: C.CDLL) -> None:
         "b200_kv_cache_pages_per_sequence": (i32, [vp]), "b200_kv_cache_page_size": (i32, [vp]),
         "b200_kv_cache_pool_bytes": (sz, [vp]), "b200_kv_cache_advance": (C.c_int, [pp, i32, i32, vp]),
         "b200_kv_cache_gather": (C.c_int, [vp, i32, i32, vp, vp]), "b200_kv_cache_append": (C.c_int, [vp, vp, vp, i32, vp]),
+        "b200_permute": (C.c_int, [vp, C.POINTER(i64), C.POINTER(i64), i32, vp, vp]),
         "b200_embedding": (C.c_int, [vp, i32, vp, i64, i64, i64, vp, vp]),
         "b200_rms_norm": (C.c_int, [vp, vp, i32, i64, i64, C.c_double, vp, vp]),
         "b200_linear": (C.c_int, [vp, i64, i64, vp, i32, i64, vp, i32, C.c_double, C.c_int, vp, C.POINTER(QkvArgs), vp, vp]),

@@ -5,6 +5,10 @@
 Every .cu / .cpp under ctorch_b200/csrc is compiled to an object under ctorch_b200/build/ (rebuilt only when the
 source or a header is newer) and linked into one shared library with a static CUDA runtime, so that the library
 loads on machines without a GPU or driver.
+
+The library's SONAME is libctorch_b200.so.  Beside it the build leaves the reference package's names as symbolic
+links (libctorch.so and libctorch.so.0: target `ctorch`, SOVERSION 0), so that a program built for the reference
+with `-lctorch` and the headers under include/dl/ links against this directory unchanged.
 """
 from __future__ import annotations
 
@@ -73,11 +77,17 @@ def build(force: bool = False, verbose: bool = False) -> str:
         list(pool.map(run, jobs))
     if jobs or not os.path.exists(LIB):
         link = [NVCC, "-shared", "-gencode", "arch=compute_100a,code=sm_100a", "-cudart", "static",
-                "-Xcompiler", "-fPIC", "-o", LIB, *objects, "-lpthread", "-ldl"]
+                "-Xcompiler", "-fPIC", "-Xlinker", "-soname=libctorch_b200.so", "-o", LIB, *objects, "-lpthread", "-ldl"]
         result = subprocess.run(link, capture_output=True, text=True)
         if result.returncode != 0:
             sys.stderr.write(result.stdout + result.stderr)
             raise RuntimeError("link failed")
+    for alias in ("libctorch.so", "libctorch.so.0"):   # the reference package's library names
+        path = os.path.join(HERE, alias)
+        if not os.path.islink(path):
+            if os.path.exists(path):
+                os.remove(path)
+            os.symlink("libctorch_b200.so", path)
     return LIB
 
 

@@ -164,6 +164,9 @@ dl_status dl_rotary_embedding(const dl_tensor* input, const dl_tensor* cosine, c
         return dl::rotary_embedding(need(input, "tensor").value, need(cosine, "tensor").value, need(sine, "tensor").value);
     });
 }
+dl_status dl_tensordot(const dl_tensor* a, const dl_tensor* b, dl_shape axes_a, dl_shape axes_b, dl_tensor** output) {
+    return make_handle(output, [&] { return dl::tensordot(need(a, "tensor").value, need(b, "tensor").value, convert(axes_a), convert(axes_b)); });
+}
 dl_status dl_grouped_query_attention(const dl_tensor* query, const dl_tensor* key, const dl_tensor* value,
                                      const dl_tensor* keep_mask, dl_tensor** output) {
     return make_handle(output, [&] {
@@ -336,6 +339,9 @@ dl_status dl_generation_step(dl_generation* generation, int64_t steps) {
 }
 dl_status dl_generation_step_host(dl_generation* generation, const int64_t* ids_in, int64_t* ids_out) {
     return invoke([&] { need(generation, "generation").value->step_host(ids_in, ids_out); });
+}
+int64_t dl_b200_shadow_partial_rows(int64_t dimensions, int64_t hidden) {
+    return dimensions > 0 && hidden > 0 ? dl::nn::shadow_partial_rows(dimensions, hidden) : 0;
 }
 dl_status dl_generation_run_host(dl_generation* generation, const int64_t* ids_in, int64_t steps, int64_t* ids_out) {
     return invoke([&] {

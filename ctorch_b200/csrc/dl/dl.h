@@ -115,6 +115,7 @@ Tensor embedding(const Tensor& indices, const Tensor& weight);
 Tensor rms_norm(const Tensor& input, const Shape& normalized_shape, std::optional<Tensor> weight = std::nullopt,
                 std::optional<double> epsilon = std::nullopt);
 Tensor argmax(const Tensor& input, Index axis, KeepDim keep = KeepDim::no);
+Tensor tensordot(const Tensor& a, const Tensor& b, Shape axes_a, Shape axes_b);
 Tensor rotary_embedding(const Tensor& input, const Tensor& cosine, const Tensor& sine);
 Tensor grouped_query_attention(const Tensor& query, const Tensor& key, const Tensor& value,
                                std::optional<Tensor> keep_mask = std::nullopt);

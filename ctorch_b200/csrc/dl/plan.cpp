@@ -9,6 +9,8 @@ namespace dl::nn {
 
 namespace {
 
+constexpr Index kShadowDenseRows = 17;   // from this row count on the dense tensor-core kernels serve a shadow linear
+
 // Optional per-launch event trail (Generation::profile_step); kinds: 0 linear, 1 attention, 2 other.
 struct StepProbe {
     cudaStream_t stream;
@@ -224,6 +226,18 @@ void DecodePlan::refresh() {
     }
 }
 
+// Rows of the [parts, rows] buffers that carry the per-row partial sums of squares between two kernels: the largest count
+// any producer of a residual stream of width D may write - one partial per feature tile of the streaming kernel (whose
+// tiles shrink to 8 features when the inner size is large, so up to D / 8), of the dense kernels (D / 128) or of the
+// cross-GPU sum - whatever the row count of the pass (the producers choose their tiling from the inner sizes D and F).
+Index shadow_partial_rows(Index D, Index F) {
+    Index parts = 1;
+    for (const Index rows : {Index{1}, Index{kShadowDenseRows}})
+        for (const Index inner : {D, F})
+            parts = std::max<Index>(parts, b200_linear_shadow_parts(rows, inner, D));
+    return std::max<Index>(parts, b200_tp_reduce_parts(D));
+}
+
 bool DecodePlan::shadows_for(Index rows) const {
     if (!shadow_ || rows <= 0) return false;
     const Index world = owner_.tp_world();
@@ -248,7 +262,7 @@ void DecodePlan::reserve(Index rows, Index max_length, int device) {
             hs_hi_ = empty({rows, D}, half); hs_lo_ = empty({rows, D}, half);
             att_hi_ = empty({rows, D}, half); att_lo_ = empty({rows, D}, half);
             act_hi_ = empty({rows, F}, half); act_lo_ = empty({rows, F}, half);
-            const Index parts = std::max<Index>(256, (D + 127) / 128);  // at most one partial per feature tile of either kernel
+            const Index parts = shadow_partial_rows(D, F / owner_.tp_world());
             sq_attn_ = empty({parts, rows}, f32); sq_ffn_ = empty({parts, rows}, f32);
         }
         reserved_rows_ = rows;

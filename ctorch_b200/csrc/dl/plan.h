@@ -19,6 +19,8 @@ Tensor interleave_rows(const Tensor& even_rows, const Tensor& odd_rows);  // [n,
 Tensor concat_rows(std::span<const Tensor> parts);                          // [n_i,k] -> [sum n_i,k]
 Tensor add(const Tensor& a, const Tensor& b);                               // f32 CUDA tensors of one shape
 Tensor attention_block(GroupedQueryAttention& attention, const Tensor& input, KVCache& cache);
+// Rows of the plan's partial-sum-of-squares buffers for a residual stream of width D and a (per-rank) SwiGLU width F.
+Index shadow_partial_rows(Index D, Index F);
 
 class DecodePlan {
 public:

@@ -1,5 +1,7 @@
 // Device context, storage, dense tensors and the functional operators of the decoder path.
 #include "dl/dl.h"
+
+#include <algorithm>
 #include "dl/internal.h"
 
 #include <cuda_runtime.h>
@@ -341,6 +343,65 @@ Tensor argmax(const Tensor& input, Index axis, KeepDim keep) {
     runtime::set_device(device);
     runtime::check(b200_argmax(x.data<float>(), x.numel() / x.size(-1), x.size(-1), static_cast<Index*>(result.mutable_data()),
                                runtime::stream(device)), "argmax");
+    return result;
+}
+
+// dl::tensordot (src/ops/contraction.cpp:9-42): the contracted axes of `a` go last, those of `b` last as well (so that
+// the product is the linear kernel's x @ W^T), the result has a's remaining axes followed by b's.
+Tensor tensordot(const Tensor& a, const Tensor& b, Shape axes_a, Shape axes_b) {
+    const int device = cuda_index(a, "tensordot");
+    if (b.device() != a.device()) throw std::invalid_argument("tensordot inputs must share a device");
+    auto axes = [](Shape values, Index rank) {
+        Shape seen;
+        for (auto& axis : values) {
+            axis = wrap_axis(axis, rank);
+            if (std::find(seen.begin(), seen.end(), axis) != seen.end()) throw std::invalid_argument("tensordot axes must be distinct");
+            seen.push_back(axis);
+        }
+        return values;
+    };
+    axes_a = axes(std::move(axes_a), a.ndim());
+    axes_b = axes(std::move(axes_b), b.ndim());
+    if (axes_a.size() != axes_b.size()) throw std::invalid_argument("tensordot axis counts differ");
+    if (a.ndim() > 8 || b.ndim() > 8) throw std::invalid_argument("tensordot: at most 8 axes per operand");
+    Index inner = 1;
+    for (std::size_t i = 0; i < axes_a.size(); ++i) {
+        if (a.size(axes_a[i]) != b.size(axes_b[i])) throw std::invalid_argument("tensordot contracted dimensions differ");
+        inner *= a.size(axes_a[i]);
+    }
+    auto remaining = [](Index rank, const Shape& contracted) {
+        Shape result;
+        for (Index i = 0; i < rank; ++i)
+            if (std::find(contracted.begin(), contracted.end(), i) == contracted.end()) result.push_back(i);
+        return result;
+    };
+    Shape left = remaining(a.ndim(), axes_a), right = remaining(b.ndim(), axes_b), output;
+    Index rows = 1, columns = 1;
+    for (auto axis : left) { output.push_back(a.size(axis)); rows *= a.size(axis); }
+    for (auto axis : right) { output.push_back(b.size(axis)); columns *= b.size(axis); }
+    left.insert(left.end(), axes_a.begin(), axes_a.end());      // a: [remaining..., contracted...] = [rows, inner]
+    right.insert(right.end(), axes_b.begin(), axes_b.end());    // b: [remaining..., contracted...] = [columns, inner]
+    Tensor result = empty(output, {DType::f32, a.device()});
+    if (rows == 0 || columns == 0) return result;
+    runtime::set_device(device);
+    void* stream = runtime::stream(device);
+    if (inner == 0) {
+        runtime::check_cuda(cudaMemsetAsync(result.mutable_data(), 0, result.nbytes(), static_cast<cudaStream_t>(stream)), "cudaMemsetAsync");
+        synchronize(a.device());
+        return result;
+    }
+    auto dense = [&](const Tensor& source, const Shape& order, Index first, Index second) {
+        const Tensor x = as_f32(source);
+        Tensor out = empty({first, second}, {DType::f32, source.device()});
+        if (order.empty()) return x.reshape({first, second});
+        runtime::check(b200_permute(x.data<float>(), x.shape().data(), order.data(), static_cast<std::int32_t>(order.size()),
+                                    static_cast<float*>(out.mutable_data()), stream), "permute");
+        return out;
+    };
+    const Tensor x = dense(a, left, rows, inner), w = dense(b, right, columns, inner);
+    runtime::check(b200_linear(x.data<float>(), rows, inner, w.raw_data(), B200_F32, columns, nullptr, 0, 0.0, B200_EPI_STORE, nullptr, nullptr,
+                               static_cast<float*>(result.mutable_data()), stream), "tensordot");
+    synchronize(a.device());   // the dense copies die with this scope
     return result;
 }
 

@@ -131,10 +131,7 @@ __global__ void __launch_bounds__(kFastThreads) attention_mma_kernel(const __gri
     uint64_t* full = reinterpret_cast<uint64_t*>(smem + S::stages * S::stage_bytes);
     uint64_t* empty = full + S::stages;
 
-    const int trace = trace_begin(20);
-    trace_mark(trace, 0);
     grid_dependency_wait();   // q, the cache and the lengths come from the preceding kernels
-    trace_mark(trace, 1);
     grid_launch_dependents();
     // An item is (sequence, block of consecutive positions, KV head).  The 16 fragment rows of a warp hold the block's
     // positions times the head group: row r = position r / group, query head r % group.  Decode: one position, rows =
@@ -153,7 +150,7 @@ __global__ void __launch_bounds__(kFastThreads) attention_mma_kernel(const __gri
     const int per_split = balanced_pages_per_split(page_end, p.pages_per_split);
     const int page_begin = split * per_split;
     if (page_end > page_begin + per_split) page_end = page_begin + per_split;
-    if (page_begin >= page_end) { trace_end(trace); return; }  // uniform for the CTA
+    if (page_begin >= page_end) return;  // uniform for the CTA
     const int pages = page_end - page_begin;
     const int group = p.heads / p.kv.kv_heads;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -222,7 +219,6 @@ __global__ void __launch_bounds__(kFastThreads) attention_mma_kernel(const __gri
         }
         const int tok0 = (warp & (kGroupWarps - 1)) * 16;
         const int group_index = warp / kGroupWarps;
-        trace_mark(trace, 2);
         const int mi = lane >> 3, ri = lane & 7;
         bool alive = true;
         for (int i = group_index; i < pages && alive; i += kConsumerWarps / kGroupWarps) {
@@ -233,7 +229,6 @@ __global__ void __launch_bounds__(kFastThreads) attention_mma_kernel(const __gri
                 alive = false;
                 break;
             }
-            if (i == group_index) trace_mark(trace, 3);
             const uint32_t kbase = smem_u32(smem + s * S::stage_bytes);
             const uint32_t vbase = kbase + S::tile_bytes;
 
@@ -306,7 +301,6 @@ __global__ void __launch_bounds__(kFastThreads) attention_mma_kernel(const __gri
         }
     }
     __syncthreads();  // every page has been consumed: the stage memory can be reused for the merge
-    trace_mark(trace, 4);
 
     float* merge_o = reinterpret_cast<float*>(smem);                       // [warps][group][HD]
     float* merge_ml = merge_o + kConsumerWarps * 16 * HD;                   // [warps][16][2]
@@ -355,7 +349,6 @@ __global__ void __launch_bounds__(kFastThreads) attention_mma_kernel(const __gri
             }
         }
     }
-    trace_end(trace);
 }
 
 // Generic path: one (row, head) per CTA, four warps stride over the tokens of the split.
@@ -438,7 +431,6 @@ __global__ void __launch_bounds__(kGenericThreads) attention_generic_kernel(cons
 
 // Merge of the split partials: one (row, head) per CTA.
 __global__ void attention_combine_kernel(const AttnParams p) {
-    const int trace = trace_begin(21);
     grid_dependency_wait();
     grid_launch_dependents();
     const int hd = p.kv.head_dim;
@@ -460,7 +452,6 @@ __global__ void attention_combine_kernel(const AttnParams p) {
         for (int s = 0; s < valid; ++s) acc += expf(ml[2 * s] - m) * p.part_o[(head_item * p.num_splits + s) * hd + d];
         store_result(p, head_item * hd + d, acc / l);
     }
-    trace_end(trace);
 }
 
 template <int HD, int STAGES> int launch_fast(const b200_kv_cache* cache, const AttnParams& p, cudaStream_t stream) {
@@ -496,6 +487,14 @@ int attention_launch(const float* q, int64_t rows, int32_t tokens_per_sequence, 
         return B200_BAD_ARGUMENT;
     }
     if (cache->head_dim > 32 * kMaxDimsPerLane) { set_error("b200_attention_decode: head_dim above 256 is not supported"); return B200_UNSUPPORTED; }
+    {   // the kernels run on the current device: it must be the one that holds the cache (and, for the static entry, the scratch)
+        int current = -1;
+        B200_CUDA(cudaGetDevice(&current));
+        if (current != cache->device) {
+            set_error("b200_attention_decode: the cache lives on device %d, the current device is %d", cache->device, current);
+            return B200_BAD_ARGUMENT;
+        }
+    }
     if (max_length > cache->capacity) max_length = cache->capacity;
     const int group = heads / cache->kv_heads;
     const bool fast = kv_tensor_map(cache, 0) && group <= 16 && (cache->head_dim == 64 || cache->head_dim == 128);
@@ -522,6 +521,7 @@ int attention_launch(const float* q, int64_t rows, int32_t tokens_per_sequence, 
     p.out = out; p.out_hi = out_hi; p.out_lo = out_lo;
     p.scale = static_cast<float>(1.0 / std::sqrt(static_cast<double>(cache->head_dim)));
     p.status = device_status_word(cache->device);
+    if (!p.status) { set_error("b200_attention_decode: the device status word could not be allocated"); return B200_NO_DEVICE; }
     cudaStream_t s = as_stream(stream);
     int status;
     if (fast) {

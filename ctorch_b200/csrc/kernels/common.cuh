@@ -130,27 +130,6 @@ __device__ __forceinline__ void tma_prefetch_descriptor(const CUtensorMap* map) 
     asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(map)) : "memory");
 }
 
-// ---- development trace (compiled only with -DB200_TRACE; never part of the shipped library) ------------------------
-#ifdef B200_TRACE
-extern __device__ unsigned long long b200_step_trace[4096 * 3];
-extern __device__ unsigned int b200_step_trace_count;
-extern __device__ unsigned long long b200_step_marks[4096 * 8];
-__device__ __forceinline__ unsigned long long trace_now() { unsigned long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); return t; }
-__device__ __forceinline__ int trace_begin(int kind) {
-    if (threadIdx.x != 0 || blockIdx.x != 0 || blockIdx.y != 0) return -1;
-    const unsigned int slot = atomicAdd(&b200_step_trace_count, 1u) & 4095u;
-    b200_step_trace[slot * 3] = kind;
-    b200_step_trace[slot * 3 + 1] = trace_now();
-    return static_cast<int>(slot);
-}
-__device__ __forceinline__ void trace_end(int slot) { if (slot >= 0) b200_step_trace[slot * 3 + 2] = trace_now(); }
-__device__ __forceinline__ void trace_mark(int slot, int i) { if (slot >= 0) b200_step_marks[slot * 8 + i] = trace_now(); }
-#else
-__device__ __forceinline__ int trace_begin(int) { return -1; }
-__device__ __forceinline__ void trace_end(int) {}
-__device__ __forceinline__ void trace_mark(int, int) {}
-#endif
-
 // ---- programmatic dependent launch -----------------------------------------------------------------------------
 // A kernel launched with launch_dependent() may begin while its predecessor in the stream is still running.  It must
 // execute grid_dependency_wait() before it touches anything the predecessor writes (and before it writes anything

@@ -214,13 +214,7 @@ __global__ void __launch_bounds__(kThreads, 1) linear_decode_kernel(const __grid
             }
             row_scale[row] = scale;
             if (dp.epilogue == B200_EPI_QKV) {
-                // where the row's token goes: its position (cache length + offset inside the chunk) and physical page
-                const int global_row = row0 + row;
-                const int sequence = global_row / p.tokens_per_sequence;
-                const int position = __ldg(p.kv.lengths + sequence) + global_row % p.tokens_per_sequence;
-                int page_slot = position / p.kv.page_size;
-                if (page_slot >= p.kv.pages_per_seq) page_slot = p.kv.pages_per_seq - 1;
-                row_place[row] = make_int2(position, __ldg(p.kv.page_table + static_cast<int64_t>(sequence) * p.kv.pages_per_seq + page_slot));
+                row_place[row] = qkv_row_place(p, row0 + row);
             }
         }
         ready = mbar_wait_relaxed(accumulator_ready, 0);

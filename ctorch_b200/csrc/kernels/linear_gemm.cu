@@ -34,7 +34,7 @@ template <int TN, int STAGES> struct GemmShape {
     static constexpr int stages = STAGES;
     static constexpr int weight_bytes = TN * kBlockK * 2;
     static constexpr int stage_bytes = 2 * kBoxBytes + weight_bytes;   // x_hi, x_lo, W: 48 KB or 64 KB
-    static constexpr int smem = stages * stage_bytes + 1024 + 1024;   // alignment slack; barriers, TMEM slot, 128 row scales
+    static constexpr int smem = stages * stage_bytes + 1024 + 2048;   // alignment slack; barriers, TMEM slot, 128 row scales, 128 row places
     // Instruction descriptor: f32 accumulator, bf16 x bf16, both K-major, N = TN, M = 128.
     static constexpr uint32_t instruction = (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(TN >> 3) << 17)
                                             | (static_cast<uint32_t>(kTileM >> 4) << 24);
@@ -141,6 +141,7 @@ __global__ void __launch_bounds__(kGemmThreads, STAGES == 2 && TN == 128 ? 2 : 1
     constexpr int kTileStride = kTileN + 4;
     float* tile = reinterpret_cast<float*>(smem);
     float* row_scale = reinterpret_cast<float*>(smem + kStages * kStageBytes + 512);   // 128 floats behind the barriers
+    int2* row_place = reinterpret_cast<int2*>(smem + kStages * kStageBytes + 1024);    // q|k|v: position and cache page of every row
     volatile int* tile_ready = reinterpret_cast<volatile int*>(smem + kStages * kStageBytes + 256);   // one flag per epilogue warp
     const bool finisher = warp >= 2;
     const int quarter = warp & 3;
@@ -155,6 +156,7 @@ __global__ void __launch_bounds__(kGemmThreads, STAGES == 2 && TN == 128 ? 2 : 1
             scale = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(total, static_cast<float>(p.in)), static_cast<float>(p.eps))));
         }
         row_scale[tile_row] = scale;
+        if constexpr (EPI == B200_EPI_QKV) row_place[tile_row] = qkv_row_place(p, row);
         ready = mbar_wait(accumulator_ready, 0);
         if (!ready && lane == 0) atomicExch(gp.status, B200_DEVICE_TIMEOUT);
         tc_fence_after_sync();
@@ -188,7 +190,8 @@ __global__ void __launch_bounds__(kGemmThreads, STAGES == 2 && TN == 128 ? 2 : 1
 #pragma unroll
             for (int z = 0; z < 8; ++z) peer_tile[z] = z < split ? map_peer_shared(smem_u32(tile), static_cast<uint32_t>(z)) : 0u;
         }
-        finish_rows<EPI, kTileN>(p, tile, peer_tile, split, row_scale, m0, n0, static_cast<int>(blockIdx.y), first, last, warp, kGemmThreads / 32, lane, ready);
+        finish_rows<EPI, kTileN>(p, tile, peer_tile, split, row_scale, m0, n0, static_cast<int>(blockIdx.y), first, last, warp, kGemmThreads / 32, lane, ready,
+                                 EPI == B200_EPI_QKV ? row_place : nullptr);
     }
     if (split > 1) {
         __syncwarp();
@@ -211,7 +214,7 @@ __global__ void __launch_bounds__(kGemmThreads, STAGES == 2 && TN == 128 ? 2 : 1
 constexpr int kPersistStages = 3;
 constexpr int kPersistStageBytes = 3 * kBoxBytes;                      // x_hi, x_lo, W boxes of one K block: 48 KB
 constexpr int kPersistTileBytes = kTileM * (128 + 4) * 4;              // row-major f32 tile of the epilogue, padded rows
-constexpr int kPersistSmem = kPersistStages * kPersistStageBytes + kPersistTileBytes + 1024 + 1024;
+constexpr int kPersistSmem = kPersistStages * kPersistStageBytes + kPersistTileBytes + 1024 + 2048;
 constexpr uint32_t kPersistInstruction = GemmShape<128, 3>::instruction;
 
 template <int EPI>
@@ -232,6 +235,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) linear_gemm_persistent_kernel
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
     volatile int* alive_flag = reinterpret_cast<volatile int*>(control + 256);
     float* row_scale = reinterpret_cast<float*>(control + 512);
+    int2* row_place = reinterpret_cast<int2*>(control + 1024);   // q|k|v: position and cache page of every row of the tile
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int k_blocks = (p.in + kBlockK - 1) / kBlockK;
@@ -329,6 +333,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) linear_gemm_persistent_kernel
                 scale = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(total, static_cast<float>(p.in)), static_cast<float>(p.eps))));
             }
             row_scale[tile_row] = scale;   // the previous tile's rows were finished before the barrier that ended it
+            if constexpr (EPI == B200_EPI_QKV) row_place[tile_row] = qkv_row_place(p, row);
             const bool ready = mbar_wait(&acc_full[buffer], (j >> 1) & 1);
             if (!ready && lane == 0) { atomicExch(gp.status, B200_DEVICE_TIMEOUT); *alive_flag = 0; }
             tc_fence_after_sync();
@@ -350,7 +355,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1) linear_gemm_persistent_kernel
             asm volatile("bar.sync 2, 128;" ::: "memory");    // the tile (and the row scales) are in shared memory
             if (*alive_flag == 0) break;                       // same decision in all four warps
             const int rows_here = min(kTileM, p.rows - m0);
-            finish_rows<EPI, kTileN>(p, tile, own_tile, 1, row_scale, m0, n0, t / row_tiles, 0, rows_here, quarter, 4, lane, true);
+            finish_rows<EPI, kTileN>(p, tile, own_tile, 1, row_scale, m0, n0, t / row_tiles, 0, rows_here, quarter, 4, lane, true,
+                                     EPI == B200_EPI_QKV ? row_place : nullptr);
             asm volatile("bar.sync 2, 128;" ::: "memory");    // the next tile may overwrite the shared-memory tile
         }
     }
@@ -475,6 +481,7 @@ int launch_linear_gemm(const LinearParams& p, int epilogue, cudaStream_t stream)
     int device = 0;
     B200_CUDA(cudaGetDevice(&device));
     GemmParams gp{p, device_status_word(device)};
+    if (!gp.status) { set_error("the device status word could not be allocated"); return B200_NO_DEVICE; }
     alignas(64) CUtensorMap hi, lo, w;
     const int sms = sm_count(device);
     const int row_tiles = (p.rows + kTileM - 1) / kTileM, tiles128 = row_tiles * ((p.out + 127) / 128);

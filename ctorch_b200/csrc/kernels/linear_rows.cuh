@@ -5,6 +5,17 @@
 
 namespace b200 {
 
+// q|k|v epilogue: where the token of activation row `row` goes - its position (cache length + offset inside the chunk) and
+// the physical page of that position - looked up once per row instead of once per feature pair.
+__device__ __forceinline__ int2 qkv_row_place(const LinearParams& p, int row) {
+    if (row >= p.rows) return make_int2(0, 0);
+    const int sequence = row / p.tokens_per_sequence;
+    const int position = __ldg(p.kv.lengths + sequence) + row % p.tokens_per_sequence;
+    int page_slot = position / p.kv.page_size;
+    if (page_slot >= p.kv.pages_per_seq) page_slot = p.kv.pages_per_seq - 1;
+    return make_int2(position, __ldg(p.kv.page_table + static_cast<int64_t>(sequence) * p.kv.pages_per_seq + page_slot));
+}
+
 // One finished pair of adjacent features of one token row: shared epilogue, then the optional output shadow (hi + lo of
 // the value times the next norm weight) and the running sum of squares of the new residual stream.
 // `carried` holds the residual values of the pair (B200_EPI_RESIDUAL only), loaded ahead by the caller.

@@ -19,7 +19,6 @@
 #include <mutex>
 #include <type_traits>
 
-#define B200_MARK(i) trace_mark(trace, (i))
 
 namespace b200 {
 namespace {
@@ -83,15 +82,19 @@ __global__ void __launch_bounds__(kThreads, 2) linear_stream_kernel(const Stream
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int row0 = blockIdx.y * kRows;
-    const int trace = trace_begin(EPI);
     const int my_tiles = (sp.tiles - static_cast<int>(blockIdx.x) + static_cast<int>(gridDim.x) - 1) / static_cast<int>(gridDim.x);
 
+    // A bounded wait may run out in one consumer warp and not in another.  The warps therefore never leave on their own:
+    // the one that gave up raises this flag, still arrives at the next barrier of the consumers, and all of them test the
+    // flag behind that barrier and leave together.
+    __shared__ int consumers_gave_up;
     if (threadIdx.x == 0) {
         for (int s = 0; s < sp.slots; ++s) {
             mbar_init(&full[s], 1);
             mbar_init(&empty[s], kConsumers);
         }
         mbar_init(xbar, 1);
+        consumers_gave_up = 0;
         mbar_fence_init();
     }
     // Columns in .. in_padded+8 of the weight slots are never written by the copies; the last k-step may read up to
@@ -133,9 +136,7 @@ __global__ void __launch_bounds__(kThreads, 2) linear_stream_kernel(const Stream
     }
 
     // Weights are constants; the activations (and residual, cache, q) come from the preceding kernels.
-    B200_MARK(0);
     grid_dependency_wait();
-    B200_MARK(1);
     if constexpr (SHADOW) {
         // ---- consumers, shadow input: the rows arrive by bulk copy in their final form (one memory round trip, no
         // instructions); the row scales come from the producer's per-tile sums of squares.
@@ -184,8 +185,10 @@ __global__ void __launch_bounds__(kThreads, 2) linear_stream_kernel(const Stream
         }
         if (!mbar_wait(xbar, 0)) {
             if (lane == 0) atomicExch(sp.status, B200_DEVICE_TIMEOUT);
+            *static_cast<volatile int*>(&consumers_gave_up) = 1;
         }
         consumer_barrier();
+        if (*static_cast<volatile int*>(&consumers_gave_up)) return;   // the activations never arrived: same decision in every consumer warp
         if (threadIdx.x < kRows) {  // read again only after the barrier that follows the first tile's products
             float scale = 1.0f;
             if (p.sumsq_in && row0 + threadIdx.x < p.rows) {
@@ -198,7 +201,6 @@ __global__ void __launch_bounds__(kThreads, 2) linear_stream_kernel(const Stream
         }
         // Only now may the successor start: its weight prefetch would otherwise queue ahead of the copies above.
         grid_launch_dependents();
-        B200_MARK(2);
     } else
     // ---- consumers: stage the activations (the weight stream is already in flight) ----
     // Warp w owns rows w and w+8.  Both rows are read with independent 16-byte loads into registers (one L2 round
@@ -271,7 +273,6 @@ __global__ void __launch_bounds__(kThreads, 2) linear_stream_kernel(const Stream
         }
         consumer_barrier();
         grid_launch_dependents();
-        B200_MARK(2);
     }
 
     const int mi = lane >> 3, ri = lane & 7;
@@ -304,15 +305,14 @@ __global__ void __launch_bounds__(kThreads, 2) linear_stream_kernel(const Stream
             const uint32_t phase = (t / sp.slots) & 1;
             if (!mbar_wait(&full[s], phase)) {
                 if (lane == 0) atomicExch(sp.status, B200_DEVICE_TIMEOUT);
+                *static_cast<volatile int*>(&consumers_gave_up) = 1;
                 alive = false;
-                break;
             }
-            if (t == 0) B200_MARK(3);
             const uint32_t slot = smem_u32(slot_base + s * slot_bytes);
             // ldmatrix row addresses of the weight fragments: x4 = (features n*8.., k 0-7), (same, k 8-15),
             // (features (n+1)*8.., k 0-7), (same, k 8-15); x2 = the first two
             const uint32_t b_lane = slot + static_cast<uint32_t>((((NT == 1 ? 0 : (mi >> 1)) * 8 + ri) * x_stride + (mi & 1) * 8) * 2);
-            for (int j = warp; j < ksteps; j += kConsumers) {
+            for (int j = warp; alive && j < ksteps; j += kConsumers) {
                 uint32_t ah[4], al[4];
                 const uint32_t column_bytes = static_cast<uint32_t>(j * 32);
                 ldmatrix_x4(ah, a_hi + column_bytes);
@@ -335,10 +335,8 @@ __global__ void __launch_bounds__(kThreads, 2) linear_stream_kernel(const Stream
                 }
             }
             __syncwarp();
-            if (lane == 0) mbar_arrive(&empty[s]);
-            if (t == 0) B200_MARK(4);
+            if (alive && lane == 0) mbar_arrive(&empty[s]);
         }
-        if (!alive) break;
         // ---- add the eight K-slices and finish the tile ----
         {
             const int g = lane >> 2, tq = lane & 3;
@@ -350,7 +348,7 @@ __global__ void __launch_bounds__(kThreads, 2) linear_stream_kernel(const Stream
             }
         }
         consumer_barrier();
-        if (t == 0) B200_MARK(5);
+        if (*static_cast<volatile int*>(&consumers_gave_up)) break;   // a weight tile never arrived: every consumer warp leaves here
         // items of one row are TF/2 consecutive threads of a warp: thread i finishes the feature pair (r, f)
 #pragma unroll
         for (int base = 0; base < kRows * (TF / 2); base += kConsumers * 32) {
@@ -428,7 +426,6 @@ __global__ void __launch_bounds__(kThreads, 2) linear_stream_kernel(const Stream
             }
         }
         consumer_barrier();
-        if (t == 0) B200_MARK(6);
     }
     if constexpr (EPI == B200_EPI_ARGMAX) {
         // one candidate per row and CTA: thread (row r, first pair) holds the best of the CTA's tiles
@@ -442,8 +439,6 @@ __global__ void __launch_bounds__(kThreads, 2) linear_stream_kernel(const Stream
             }
         }
     }
-    B200_MARK(7);
-    trace_end(trace);
 }
 
 template <int TF, int EPI, bool SHADOW> int launch_mode(const StreamParams& sp, size_t smem, int ctas, int row_tiles, cudaStream_t stream) {
@@ -498,8 +493,8 @@ bool choose_tiling(int in, int out, int sms, StreamParams& sp, size_t& smem) {
 int linear_stream_parts(int rows, int in, int out) {
     if ((in & 7) || in <= 0 || out <= 0) return 0;
     if (rows >= kGemmRows || in > kMaxIn) return linear_gemm_parts(rows, in, out);
-    int device = 0;
-    if (cudaGetDevice(&device) != cudaSuccess) return 0;
+    int device = -1;
+    if (cudaGetDevice(&device) != cudaSuccess) { cudaGetLastError(); device = -1; }   // no device: the figures of a 148-SM part
     StreamParams sp{};
     size_t smem = 0;
     return choose_tiling(in, out, sm_count(device), sp, smem) ? sp.tiles : 0;
@@ -508,8 +503,8 @@ int linear_stream_parts(int rows, int in, int out) {
 int linear_argmax_parts(int rows, int in, int out) {
     if ((in & 7) || in <= 0 || out <= 0) return 0;
     if (rows >= kGemmRows || in > kMaxIn) return linear_gemm_parts(rows, in, out);
-    int device = 0;
-    if (cudaGetDevice(&device) != cudaSuccess) return 0;
+    int device = -1;
+    if (cudaGetDevice(&device) != cudaSuccess) { cudaGetLastError(); device = -1; }
     StreamParams sp{};
     size_t smem = 0;
     if (!choose_tiling(in, out, sm_count(device), sp, smem)) return 0;
@@ -598,6 +593,7 @@ int launch_linear_stream(const LinearParams& p, int epilogue, cudaStream_t strea
     StreamParams sp{};
     sp.base = p;
     sp.status = device_status_word(device);
+    if (!sp.status) { set_error("the device status word could not be allocated"); return B200_NO_DEVICE; }
     size_t smem = 0;
     if (!choose_tiling(p.in, p.out, sms, sp, smem)) return B200_UNSUPPORTED;
 

@@ -6,22 +6,6 @@
 #include <cstring>
 #include <mutex>
 
-#ifdef B200_TRACE
-namespace b200 {
-__device__ unsigned long long b200_step_trace[4096 * 3];
-__device__ unsigned int b200_step_trace_count;
-__device__ unsigned long long b200_step_marks[4096 * 8];
-}
-extern "C" __attribute__((visibility("default"))) int b200_step_marks_read(unsigned long long* host) {
-    return static_cast<int>(cudaMemcpyFromSymbol(host, b200::b200_step_marks, sizeof(unsigned long long) * 4096 * 8));
-}
-extern "C" __attribute__((visibility("default"))) int b200_step_trace_read(unsigned long long* host, unsigned int* count) {
-    cudaMemcpyFromSymbol(count, b200::b200_step_trace_count, sizeof(unsigned int));
-    const unsigned int zero = 0;
-    cudaMemcpyFromSymbol(host, b200::b200_step_trace, sizeof(unsigned long long) * 4096 * 3);
-    return static_cast<int>(cudaMemcpyToSymbol(b200::b200_step_trace_count, &zero, sizeof zero));
-}
-#endif
 
 namespace b200 {
 
@@ -82,7 +66,6 @@ namespace {
 template <class T>
 __global__ void embedding_kernel(const T* table, const int64_t* ids, int64_t rows, int64_t vocab, int64_t width, float* out,
                                  int32_t* status) {
-    const int trace = trace_begin(10);
     grid_dependency_wait();   // the ids may come from the previous step's token feedback
     grid_launch_dependents();
     const int64_t row = blockIdx.x;
@@ -92,7 +75,6 @@ __global__ void embedding_kernel(const T* table, const int64_t* ids, int64_t row
         id = id < 0 ? 0 : vocab - 1;
     }
     for (int64_t c = threadIdx.x; c < width; c += blockDim.x) out[row * width + c] = load_as_f32(table, id * width + c);
-    trace_end(trace);
 }
 
 // One CTA per row; f64 accumulation and f64 scale, one rounding (src/kernels/cpu/normalization.cpp:39-51).
@@ -131,7 +113,6 @@ __device__ __forceinline__ bool better(const Best& a, const Best& b) {  // is a 
 }
 __global__ void argmax_kernel(const float* x, int64_t width, int64_t* index) {
     __shared__ Best partial[32];
-    const int trace = trace_begin(11);
     grid_dependency_wait();
     grid_launch_dependents();
     const float* row = x + blockIdx.x * width;
@@ -154,7 +135,6 @@ __global__ void argmax_kernel(const float* x, int64_t width, int64_t* index) {
         }
         if (threadIdx.x == 0) index[blockIdx.x] = best.index;
     }
-    trace_end(trace);
 }
 
 __global__ void select_rows_kernel(const float* x, int64_t first, int64_t stride, int64_t width, float* out) {
@@ -178,6 +158,7 @@ int b200_embedding(const void* table, int32_t table_dtype, const int64_t* ids, i
     int device = 0;
     B200_CUDA(cudaGetDevice(&device));
     int32_t* status = device_status_word(device);
+    if (!status) { set_error("b200_embedding: the device status word could not be allocated"); return B200_NO_DEVICE; }
     const int threads = width >= 256 ? 256 : 64;
     if (table_dtype == B200_BF16)
         return cuda_status(launch_dependent(embedding_kernel<__nv_bfloat16>, dim3(static_cast<unsigned>(rows)), dim3(threads), 0, as_stream(stream),
@@ -248,6 +229,21 @@ __global__ void permute_0213_kernel(const float* in, int64_t a, int64_t b, int64
          i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
         const int64_t id = i % d, ib = (i / d) % b, ic = (i / d / b) % c, ia = i / d / b / c;  // i indexes out [a,c,b,d]
         out[i] = in[((ia * b + ib) * c + ic) * d + id];
+    }
+}
+
+// Dense copy of a permuted view: out axis i is in axis order[i]; `size` and `stride` are those of the output axes, the
+// strides measured in the input.
+struct PermuteShape { int64_t size[8], stride[8]; int32_t rank; };
+__global__ void permute_kernel(const float* in, const PermuteShape shape, int64_t total, float* out) {
+    for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < total;
+         i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+        int64_t rest = i, source = 0;
+        for (int axis = shape.rank - 1; axis >= 0; --axis) {
+            source += (rest % shape.size[axis]) * shape.stride[axis];
+            rest /= shape.size[axis];
+        }
+        out[i] = in[source];
     }
 }
 
@@ -437,6 +433,28 @@ int b200_permute_0213(const float* in, int64_t a, int64_t b, int64_t c, int64_t 
     return cuda_status(cudaGetLastError(), "permute_0213_kernel launch");
 }
 
+int b200_permute(const float* in, const int64_t* sizes, const int64_t* order, int32_t rank, float* out, void* stream) {
+    if (!in || !out || !sizes || !order || rank < 1 || rank > 8) { set_error("b200_permute: bad pointer or rank"); return B200_BAD_ARGUMENT; }
+    b200::PermuteShape shape{};
+    int64_t stride[8], count = 1;
+    bool seen[8] = {false, false, false, false, false, false, false, false};
+    for (int i = rank - 1; i >= 0; --i) {
+        if (sizes[i] < 0) { set_error("b200_permute: negative size"); return B200_BAD_ARGUMENT; }
+        stride[i] = count;
+        count *= sizes[i];
+    }
+    for (int i = 0; i < rank; ++i) {
+        if (order[i] < 0 || order[i] >= rank || seen[order[i]]) { set_error("b200_permute: order is not a permutation"); return B200_BAD_ARGUMENT; }
+        seen[order[i]] = true;
+        shape.size[i] = sizes[order[i]];
+        shape.stride[i] = stride[order[i]];
+    }
+    shape.rank = rank;
+    if (count == 0) return B200_OK;
+    b200::permute_kernel<<<b200::blocks_for(count), 256, 0, as_stream(stream)>>>(in, shape, count, out);
+    return cuda_status(cudaGetLastError(), "permute_kernel launch");
+}
+
 int b200_token_feedback(const int64_t* next, int64_t batch, int64_t* ids, int64_t* history, int64_t history_rows,
                         int32_t* counter, void* stream) {
     if (!next || !counter || batch <= 0) { set_error("b200_token_feedback: bad pointer or size"); return B200_BAD_ARGUMENT; }
@@ -516,6 +534,7 @@ extern "C" int b200_embedding_shadow(const void* table, int32_t table_dtype, con
     int device = 0;
     B200_CUDA(cudaGetDevice(&device));
     int32_t* status = device_status_word(device);
+    if (!status) { set_error("b200_embedding_shadow: the device status word could not be allocated"); return B200_NO_DEVICE; }
     auto* hi = static_cast<__nv_bfloat16*>(out_hi);
     auto* lo = static_cast<__nv_bfloat16*>(out_lo);
     if (table_dtype == B200_BF16)
@@ -536,8 +555,10 @@ extern "C" int b200_shadow_from_rows(const float* x, int64_t rows, int64_t width
     if (rows == 0) return B200_OK;
     int device = 0;
     B200_CUDA(cudaGetDevice(&device));
+    int32_t* status = device_status_word(device);
+    if (!status) { set_error("b200_shadow_from_rows: the device status word could not be allocated"); return B200_NO_DEVICE; }
     return cuda_status(launch_dependent(b200::embedding_shadow_kernel<float>, dim3(static_cast<unsigned>(rows)), dim3(256), 0, as_stream(stream),
                                         x, static_cast<const int64_t*>(nullptr), rows, width, norm_weight, static_cast<int>(norm_dtype),
                                         static_cast<float*>(nullptr), static_cast<__nv_bfloat16*>(out_hi), static_cast<__nv_bfloat16*>(out_lo),
-                                        sumsq_out, device_status_word(device)), "shadow_from_rows launch");
+                                        sumsq_out, status), "shadow_from_rows launch");
 }

@@ -182,11 +182,13 @@ int b200_tp_reduce_shadow(void* const* regions, int32_t rank, int32_t world, int
     }
     int device = 0;
     B200_CUDA(cudaGetDevice(&device));
+    int32_t* status = device_status_word(device);
+    if (!status) { set_error("b200_tp_reduce_shadow: the device status word could not be allocated"); return B200_NO_DEVICE; }
     const dim3 grid(static_cast<unsigned>(b200_tp_reduce_parts(width)), static_cast<unsigned>(rows));
     return cuda_status(launch_dependent(tp_reduce_shadow_kernel, grid, dim3(kReduceThreads), 0, as_stream(stream), table,
                                         static_cast<int>(rank), static_cast<int>(world), static_cast<int>(slot), static_cast<int64_t>(slot_bytes),
                                         rows, width, norm_weight, static_cast<int>(norm_dtype), out, static_cast<__nv_bfloat16*>(out_hi),
-                                        static_cast<__nv_bfloat16*>(out_lo), sumsq_out, device_status_word(device)),
+                                        static_cast<__nv_bfloat16*>(out_lo), sumsq_out, status),
                        "tp_reduce_shadow_kernel launch");
 }
 

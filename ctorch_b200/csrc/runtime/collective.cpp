@@ -9,10 +9,15 @@
 #include <cuda_runtime.h>
 #include <dlfcn.h>
 
+#include <chrono>
+#include <cstdlib>
 #include <cstring>
+#include <future>
+#include <memory>
 #include <mutex>
 #include <stdexcept>
 #include <string>
+#include <thread>
 
 namespace dl::runtime {
 
@@ -85,8 +90,39 @@ void tp_init(int device, int rank, int world, const void* id128) {
     stream(device);
     UniqueId id;
     std::memcpy(id.bytes, id128, sizeof id.bytes);
-    Comm comm = nullptr;
-    check_nccl(nccl().comm_init_rank(&comm, world, id, rank), "ncclCommInitRank");
+    // ncclCommInitRank returns only when every rank of the group has joined.  It runs on a helper thread while this one
+    // waits with a deadline (CTORCH_B200_TP_INIT_TIMEOUT_S, 120 s by default): a rank that never joins then costs the
+    // caller an error instead of a process that hangs for good.  The helper owns its state; after a timeout it is left
+    // behind (it ends with the process) and the device stays outside any group.
+    nccl();   // resolve the library on this thread, so that a missing NCCL is reported here
+    struct Attempt {
+        std::promise<int> done;
+        Comm comm = nullptr;
+    };
+    auto attempt = std::make_shared<Attempt>();
+    std::future<int> result = attempt->done.get_future();
+    std::thread([attempt, device, world, rank, id] {
+        int status = -1;
+        try {
+            set_device(device);
+            status = nccl().comm_init_rank(&attempt->comm, world, id, rank);
+        } catch (...) {
+            status = -1;
+        }
+        attempt->done.set_value(status);
+    }).detach();
+    double seconds = 120.0;
+    if (const char* text = std::getenv("CTORCH_B200_TP_INIT_TIMEOUT_S")) {
+        const double wanted = std::atof(text);
+        if (wanted > 0.0) seconds = wanted;
+    }
+    if (result.wait_for(std::chrono::duration<double>(seconds)) != std::future_status::ready)
+        throw std::runtime_error("NCCL: ncclCommInitRank timed out after " + std::to_string(seconds) + " s: not every rank of the group of "
+                                 + std::to_string(world) + " joined");
+    const int status = result.get();
+    if (status == -1) throw std::runtime_error("NCCL: ncclCommInitRank could not run on the helper thread");
+    check_nccl(status, "ncclCommInitRank");
+    Comm comm = attempt->comm;
     groups[device] = Group{};
     groups[device].comm = comm;
     groups[device].rank = rank;

@@ -26,14 +26,20 @@
 extern "C" {
 #endif
 
+#ifndef DL_API                  /* dl/export.h defines it when the reference's include paths are used */
 #if defined(__GNUC__)
 #define DL_API __attribute__((visibility("default")))
 #else
 #define DL_API
 #endif
+#endif
 
+#ifndef DL_VERSION
 #define DL_VERSION "0.3.0"      /* include/dl/version.h.in */
+#endif
+#ifndef DL_ABI_VERSION
 #define DL_ABI_VERSION 1
+#endif
 
 /* include/dl/c_api.h:15-58,72-77 */
 typedef struct dl_tensor dl_tensor;
@@ -118,6 +124,8 @@ DL_API dl_status dl_state_create(const char* const* names, const dl_tensor* cons
 
 /* include/dl/decoder_c_api.h:11-41 -- decoder operators, modules, cache and decode */
 typedef struct dl_decoder_cache dl_decoder_cache;
+/* include/dl/decoder_c_api.h:13-14 -- contraction over the given axes (f32 result; CUDA tensors only) */
+DL_API dl_status dl_tensordot(const dl_tensor* a, const dl_tensor* b, dl_shape axes_a, dl_shape axes_b, dl_tensor** output);
 DL_API dl_status dl_rotary_embedding(const dl_tensor* input, const dl_tensor* cosine, const dl_tensor* sine,
     dl_tensor** output);
 DL_API dl_status dl_grouped_query_attention(const dl_tensor* query, const dl_tensor* key, const dl_tensor* value,
@@ -188,6 +196,9 @@ DL_API dl_status dl_generation_step_sampled(dl_generation* generation, double te
 DL_API dl_status dl_generation_tokens(dl_generation* generation, dl_tensor** output);
 /* Logits [batch, vocab] (f32, device) the latest token was chosen from. */
 DL_API dl_status dl_generation_logits(dl_generation* generation, dl_tensor** output);
+/* Rows of the buffers in which a bf16 decoder of this width (and per-rank SwiGLU width) carries per-row partial sums of
+ * squares from one kernel to the next: the largest count any of its kernels may write.  Host arithmetic only. */
+DL_API int64_t dl_b200_shadow_partial_rows(int64_t dimensions, int64_t hidden);
 /* Kernel launches (graph nodes) of one captured decode step. */
 DL_API int64_t dl_generation_launches_per_step(const dl_generation* generation);
 /* One real step run eagerly with a CUDA event after every launch (for roofline reporting): milliseconds[0] =

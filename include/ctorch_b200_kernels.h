@@ -245,6 +245,10 @@ B200_API int b200_rotary(const float* x, int64_t outer, int64_t length, int64_t 
 /* in [a, b, c, d] -> out [a, c, b, d] (the transpose(1, 2) of src/nn/decoder.cpp:82,88 made dense). */
 B200_API int b200_permute_0213(const float* in, int64_t a, int64_t b, int64_t c, int64_t d, float* out, void* stream);
 
+/* Dense copy of a permuted f32 tensor (Tensor::permute + contiguous of the reference, as dl::tensordot uses it,
+ * src/ops/contraction.cpp:39-41): `sizes` are the input's `rank` sizes (rank <= 8), out axis i is input axis order[i]. */
+B200_API int b200_permute(const float* in, const int64_t* sizes, const int64_t* order, int32_t rank, float* out, void* stream);
+
 /* Token feedback of the greedy loop (examples/decoder_generate.cpp:28-30) kept on the device:
  * history[counter[0] * batch + s] = next[s]; ids[s] = next[s]; counter[0] += 1. */
 B200_API int b200_token_feedback(const int64_t* next, int64_t batch, int64_t* ids, int64_t* history, int64_t history_rows,

@@ -639,3 +639,31 @@ def test_dense_linear_with_single_plane_activations(rows, inner, out):
     args = B.ShadowLinearArgs(hi.data_ptr(), None, 8, 768, wd.data_ptr(), 64, None, 0, 0.0, 0, None, None, y.data_ptr(),
                               None, None, None, 0, None, None, None)
     assert l.b200_linear_shadow(C.byref(args), stream()) != 0
+
+
+@pytest.mark.parametrize("a_shape,b_shape,axes_a,axes_b", [((3, 4, 5), (5, 6), (2,), (0,)), ((2, 3, 4, 5), (4, 7, 3), (1, 2), (2, 0)),
+                                                             ((6, 8), (6, 8), (0, 1), (0, 1)), ((2, 5, 3), (4, 3, 5), (-2, -1), (2, 1))])
+def test_tensordot_matches_the_reference_rule(a_shape, b_shape, axes_a, axes_b):
+    """dl_tensordot (include/dl/decoder_c_api.h:13-14 of the reference, src/ops/contraction.cpp:9-42): contracted axes paired
+    in the given order, the result has a's remaining axes followed by b's; checked against numpy.tensordot in f64."""
+    rng = np.random.default_rng(len(a_shape) * 10 + len(b_shape))
+    a = rng.standard_normal(a_shape, dtype=np.float32)
+    b = rng.standard_normal(b_shape, dtype=np.float32)
+    ta, tb = B.Tensor.from_numpy(a, device=B.cuda(0)), B.Tensor.from_numpy(b, device=B.cuda(0))
+    xa = (C.c_int64 * len(axes_a))(*axes_a)
+    xb = (C.c_int64 * len(axes_b))(*axes_b)
+    out = C.c_void_p()
+    B.check(B.lib().dl_tensordot(ta.h, tb.h, B.Shape(xa, len(axes_a)), B.Shape(xb, len(axes_b)), C.byref(out)))
+    got = B.Tensor(out).numpy()
+    want = np.tensordot(a.astype(np.float64), b.astype(np.float64), axes=(list(axes_a), list(axes_b)))
+    assert got.shape == want.shape
+    assert rel(got, want) < 1e-5
+    # mismatching contracted sizes and repeated axes are refused with the reference's messages
+    bad = C.c_void_p(1)
+    last_a, first_b = (C.c_int64 * 1)(len(a_shape) - 1), (C.c_int64 * 1)(0)
+    if a_shape[-1] != b_shape[0]:
+        assert B.lib().dl_tensordot(ta.h, tb.h, B.Shape(last_a, 1), B.Shape(first_b, 1), C.byref(bad)) == 1
+        assert not bad.value and b"contracted dimensions differ" in B.lib().dl_last_error()
+    twice = (C.c_int64 * 2)(0, 0)
+    assert B.lib().dl_tensordot(ta.h, tb.h, B.Shape(twice, 2), B.Shape(twice, 2), C.byref(bad)) == 1
+    assert b"must be distinct" in B.lib().dl_last_error()

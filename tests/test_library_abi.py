@@ -16,7 +16,7 @@ def declared_symbols():
     names = []
     for header in ("ctorch_b200_c_api.h", "ctorch_b200_kernels.h"):
         text = open(os.path.join(ROOT, "include", header)).read()
-        names += [n for n in re.findall(r"(?:DL_API|B200_API)[^;(]*?\b(\w+)\s*\(", text) if n != "__attribute__"]
+        names += [n for n in re.findall(r"(?:DL_API|B200_API)[^;(]*?\b(\w+)\s*\(", text) if n not in ("__attribute__", "defined")]
     return names
 
 
@@ -109,3 +109,16 @@ def test_decoder_options_are_validated_on_the_host():
     # the group itself lives on a GPU
     assert l.dl_b200_tp_init(B.cpu(), 0, 1, (C.c_char * 128)()) == 1 and b"CUDA device" in l.dl_last_error()
     assert l.dl_b200_tp_symmetric_open(B.cuda(0), (C.c_char * 64)(), 1) == 1 and b"not initialised" in l.dl_last_error()
+
+
+def test_partial_sum_buffers_follow_the_kernels_tilings():
+    """The [parts, rows] buffers that carry per-row sums of squares between kernels are sized from the producers' own
+    tile counts.  With the SwiGLU width below the model width the streaming kernel tiles the down-projection by 8
+    features: d 4096 / hidden 2048 writes 512 partials per row, d 3072 / hidden 2048 writes 384 (host arithmetic only)."""
+    l = B.lib()
+    assert l.dl_b200_shadow_partial_rows(4096, 2048) >= 512
+    assert l.dl_b200_shadow_partial_rows(3072, 2048) >= 384
+    for d, f in ((768, 2048), (2048, 8192), (4096, 14336), (2304, 2048)):
+        need = max(l.b200_linear_shadow_parts(rows, inner, d) for rows in (1, 16, 17, 256) for inner in (d, f))
+        assert l.dl_b200_shadow_partial_rows(d, f) >= need >= 1
+    assert l.dl_b200_shadow_partial_rows(0, 8) == 0

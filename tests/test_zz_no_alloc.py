@@ -4,8 +4,9 @@ Some users of the library cannot allocate device memory on the token path: their
 belongs to a pool they do not control, or they cannot accept the device-wide synchronisation that comes with
 cudaMalloc / cudaFree.  For them the split partials of the decode attention live in a fixed array inside the library
 image.  The test calls both entry points through the C ABI on the same inputs, twice in a row (the built-in array is
-shared between calls and keeps the previous call's contents), and expects the same answer; it also checks that a shape
-beyond the array's size is refused with a message instead of overrunning it.
+shared between calls and keeps the previous call's contents), and expects the same answer; the answer is also held against
+the CPU oracle's grouped-query attention (the reference's softmax(q K^T / sqrt(hd)) V restated in C), so the test stands on
+its own.  It also checks that a shape beyond the array's size is refused with a message instead of overrunning it.
 
 This file is named to be collected last, so that a run that stops at the first failure has already run every other
 test; it must pass alone in a fresh process as well.
@@ -16,6 +17,7 @@ import numpy as np
 import pytest
 
 import ctorch_b200 as B
+import oracle
 from ctorch_b200 import workloads as W
 
 pytestmark = pytest.mark.gpu
@@ -70,6 +72,14 @@ def test_static_scratch_matches_caller_scratch_twice(dtype, head_dim, heads, kv_
             a, b = got.cpu().numpy(), want.cpu().numpy()
             assert np.isfinite(a).all() and np.abs(b).max() > 0
             assert float(np.abs(a - b).max() / np.abs(b).max()) < 1e-6, attempt
+            # against the CPU oracle: with one new token per sequence, row s attends over keys 0 .. lengths[s]
+            stored_k, stored_v = (W.bf16_to_f32(W.bf16_bits(k)), W.bf16_to_f32(W.bf16_bits(v))) if dtype == B.BF16 else (k, v)
+            queries = q.cpu().numpy()
+            for s, length in enumerate(lengths):
+                seen = int(length) + 1
+                reference = oracle.gqa_attention(queries[s][None, :, None, :], stored_k[s:s + 1, :, :seen], stored_v[s:s + 1, :, :seen])
+                error = float(np.abs(a[s].reshape(heads, head_dim) - reference[0, :, 0, :]).max() / np.abs(reference).max())
+                assert error < (1e-2 if dtype == B.BF16 else 1e-5), (attempt, s, error)   # the tolerances of the attention kernel tests
     finally:
         l.b200_kv_cache_release(cache)
 

@@ -30,7 +30,7 @@ def main():
     B.tensor_parallel_init(rank, world, local, peer_slot_bytes=64 << 10)
     report = {"rank": rank, "cases": []}
     for batch, adapters in ((4, True), (32, False)):     # streaming kernel with adapters; tensor-core kernel without
-        spec = dict(vocab=1024, d_model=512, layers=3, heads=8, kv_heads=4, hidden=1024, dtype="bf16", batch=batch, prompt=40,
+        spec = dict(vocab=1024, d_model=512, layers=3, heads=8, kv_heads=8 if world > 4 else 4, hidden=1024, dtype="bf16", batch=batch, prompt=40,
                     steps=6, context=64, tied=True, eps=1e-5, rope_base=10000.0)
         if adapters:
             spec.update(lora_rank=8, lora_alpha=16.0)
