@@ -75,7 +75,7 @@ __device__ __forceinline__ void linear_epilogue(const LinearParams& p, int row, 
         if (second) p.y[at + 1] = b;
     } else if constexpr (EPI == B200_EPI_SWIGLU) {
         // rows 2j (gate_j) and 2j+1 (up_j) of the interleaved weight
-        a = __fmul_rn(silu_reference(a), b);
+        a = __fmul_rn(p.x_hi ? silu_fast(a) : silu_reference(a), b);   // shadow input = bf16 model: see silu_fast
         if (p.y) p.y[static_cast<int64_t>(row) * (p.out >> 1) + (feature0 >> 1)] = a;
     } else if constexpr (EPI == B200_EPI_ARGMAX) {
         // nothing is stored: the kernels reduce the pairs of a tile to one candidate per row themselves

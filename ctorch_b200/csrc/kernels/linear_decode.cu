@@ -1,11 +1,12 @@
-// Dense projection for decode batches (up to 128 activation rows): y = epilogue(scale_rows(x @ W^T)) with the WEIGHTS as
+// Dense projection for decode batches (up to 128 activation rows; the code also walks token tiles of 128 for more): y = epilogue(scale_rows(x @ W^T)) with the WEIGHTS as
 // the streamed operand.  A decode step reads every weight once and the activations are small, so the kernel is built to
 // keep the weight stream going and to spend no tensor time on padding:
 //
 //   * operands are swapped against the prefill kernel (linear_gemm.cu): a 128-feature weight tile is the A operand
 //     (M = 128) and the tokens are the N side of tcgen05.mma (N = rows rounded up to 16).  A product costs about
-//     max(48, N / 2) cycles, so 32 rows cost a quarter of what a 128-row token tile costs, and one CTA covers all tokens:
-//     every weight byte crosses L2 -> SM exactly once;
+//     max(48, N / 2) cycles when it re-uses the A operand of its predecessor (the hi and lo planes of the activations
+//     are multiplied back to back against the same weight slice), so 32 rows cost a quarter of what a 128-row token tile
+//     costs; up to 128 rows one CTA covers all tokens and every weight byte crosses L2 -> SM exactly once;
 //   * a CTA multiplies `tiles` (1, 2 or 4) adjacent weight tiles against each activation K block, one f32 accumulator
 //     [128 features x N tokens] per tile in tensor memory, which divides the activation bytes pulled per weight byte;
 //   * few feature tiles: K is split over a thread-block cluster (grid z, up to 8 CTAs); the partial accumulators are pushed
@@ -17,8 +18,8 @@
 //     flow, with ONE elected lane issuing a K block's instructions from fully unrolled code (tile count and plane count
 //     are template parameters): issued from a loop with run-time bounds the same products took three times as long;
 //   * warps 2-5 read the accumulators back (tcgen05.ld: one feature per thread, 32 tokens per instruction) and write them
-//     transposed into row-major [token][feature] slabs, from where all six warps finish token rows with the shared
-//     epilogues (linear_rows.cuh);
+//     transposed into row-major [token][feature] slabs, from where all twelve warps finish token rows with the shared
+//     epilogues (linear_rows.cuh); six more warps exist only for that: a row's epilogue is a dependent chain per lane;
 //   * one kernel function serves every epilogue (run-time switch): consecutive launches of a decode step then share their
 //     instructions instead of starting cold;
 //   * the launch shape (tiles per CTA, K split, ring depth) comes from a small cost model that knows how many clusters of
@@ -33,11 +34,11 @@ namespace {
 constexpr int kFeatures = 128;            // features per weight tile (M of the products)
 constexpr int kBlockK = 64;               // bf16 columns per stage: one 128-byte swizzle row
 constexpr int kWeightBox = kFeatures * kBlockK * 2;   // 16 KB
-constexpr int kThreads = 192;
+constexpr int kThreads = 384;             // 12 warps: producer, tensor-core issue, 4 accumulator readers; all 12 finish rows
 constexpr int kMaxStages = 8;
 constexpr int kControlBytes = 3584;       // barriers, TMEM slot, flags, row scales, row places (position and cache page)
 constexpr int kTileStride = kFeatures + 4;
-constexpr int kMaxRows = 128;            // above, the prefill kernel (tokens as the M side) is the faster one
+constexpr int kMaxRows = 128;             // above, the prefill kernel (tokens as the M side) is faster inside a decode step
 constexpr int kHalfSmem = 113 * 1024;     // two CTAs of this size share an SM
 
 struct DecodeParams {
@@ -201,7 +202,7 @@ __global__ void __launch_bounds__(kThreads, 1) linear_decode_kernel(const __grid
     // finishes its rows with all six warps, lanes across the features (linear_rows.cuh).  When the slabs of all weight
     // tiles fit the drained operand ring there is one barrier per launch and no CTA is written to after it; otherwise
     // the tiles take turns and a second barrier frees the slabs for the next one.
-    const bool finisher = warp >= 2;
+    const bool finisher = warp >= 2 && warp < 6;   // the four warps that read tensor memory (lanes 32 * (warp % 4) ..)
     const int quarter = warp & 3;
     bool ready = false;
     if (finisher) {
