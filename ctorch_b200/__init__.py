@@ -118,6 +118,7 @@ def _declare(l: C.CDLL) -> None:
         "dl_generation_tokens": (C.c_int, [vp, pp]), "dl_generation_logits": (C.c_int, [vp, pp]),
         "dl_generation_launches_per_step": (i64, [vp]),
         "dl_b200_shadow_partial_rows": (i64, [i64, i64]),
+        "dl_onnx_save_decoder": (C.c_int, [C.c_char_p, vp, vp, vp]),
         "dl_decoder_generate": (C.c_int, [vp, vp, vp, vp, i64, vp, pp]),
         "dl_generation_profile_step": (C.c_int, [vp, C.POINTER(C.c_double)]),
         "dl_b200_tp_unique_id": (C.c_int, [vp]), "dl_b200_tp_init": (C.c_int, [Device, i32, i32, vp]),
@@ -332,12 +333,13 @@ class DecoderModel:
     """Embedding + TransformerDecoder + output Linear, the arrangement of the reference's ByteDecoder example, built
     through the C ABI from the canonical ordered tensor list (see ctorch_b200.workloads.tensor_shapes)."""
 
-    def __init__(self, spec: dict, tensors: list[np.ndarray], lora: list[np.ndarray] | None = None, device: int = 0,
+    def __init__(self, spec: dict, tensors: list[np.ndarray], lora: list[np.ndarray] | None = None, device: int | None = 0,
                  cache_dtype: str | None = None, tensor_parallel: tuple[int, int] | None = None,
                  activation_dtype: str | None = None):
+        """`device=None` keeps the modules on the host: enough for state handling and the ONNX export, not for compute."""
         l = lib()
         self.spec = spec
-        self.dev = cuda(device)
+        self.dev = cuda(device) if device is not None else cpu()
         code = BF16 if spec["dtype"] == "bf16" else F32
         D, hd = spec["d_model"], spec["d_model"] // spec["heads"]
         dec = C.c_void_p()
@@ -358,7 +360,8 @@ class DecoderModel:
         for name, array in zip(order, tensors[1:1 + len(order)]):
             state[name] = Tensor.from_numpy(array, dtype=code)
         self.decoder.load_state(state)
-        self.decoder.to(self.dev)
+        if device is not None:
+            self.decoder.to(self.dev)
         if activation_dtype is not None:
             check(l.dl_transformer_decoder_set_activation_dtype(self.decoder.h, BF16 if activation_dtype == "bf16" else F32))
         if cache_dtype is not None:
@@ -395,6 +398,12 @@ class DecoderModel:
             check(l.dl_transformer_decoder_set_tensor_parallel(self.decoder.h, tensor_parallel[0], tensor_parallel[1]))
         self.cache = None
         self.new_cache()
+
+    def save_onnx(self, path: str, with_head: bool = True) -> None:
+        """The decoder as an ONNX file with its KV cache as graph ports: input_ids -> logits with the embedding and output
+        layers, features -> hidden states without them."""
+        check(lib().dl_onnx_save_decoder(os.fsencode(path), self.decoder.h, self.embedding.h if with_head else None,
+                                         self.output.h if with_head else None))
 
     def load_archive_state(self, state: dict[str, Tensor]) -> None:
         """Weights from an archive of the reference's example model: "tokens.weight" (shared with the output projection

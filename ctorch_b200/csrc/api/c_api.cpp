@@ -340,6 +340,19 @@ dl_status dl_generation_step(dl_generation* generation, int64_t steps) {
 dl_status dl_generation_step_host(dl_generation* generation, const int64_t* ids_in, int64_t* ids_out) {
     return invoke([&] { need(generation, "generation").value->step_host(ids_in, ids_out); });
 }
+dl_status dl_onnx_save_decoder(const char* path, const dl_module* decoder, const dl_module* embedding, const dl_module* output) {
+    return invoke([&] {
+        if (!path) throw std::invalid_argument("path is NULL");
+        const auto model = std::dynamic_pointer_cast<dl::nn::TransformerDecoder>(need(decoder, "module").value);
+        if (!model) throw std::invalid_argument("module is not a TransformerDecoder");
+        if (!embedding && !output) return dl::onnx::save_decoder(path, *model);
+        if (!embedding || !output) throw std::invalid_argument("decoder export needs both embedding and output layers");
+        const auto table = std::dynamic_pointer_cast<dl::nn::Embedding>(embedding->value);
+        const auto head = std::dynamic_pointer_cast<dl::nn::Linear>(output->value);
+        if (!table || !head) throw std::invalid_argument("decoder export needs an Embedding and a Linear");
+        dl::onnx::save_decoder(path, *table, *model, *head);
+    });
+}
 int64_t dl_b200_shadow_partial_rows(int64_t dimensions, int64_t hidden) {
     return dimensions > 0 && hidden > 0 ? dl::nn::shadow_partial_rows(dimensions, hidden) : 0;
 }

@@ -373,4 +373,11 @@ namespace io {
 void save(const std::filesystem::path& path, std::span<const NamedTensor> state);
 StateDict load(const std::filesystem::path& path);   // tensors in host memory
 }  // namespace io
+
+// ---- extensions/onnx/include/dl/onnx.h:30-35 of the reference: the decoder with its KV cache as graph ports ----
+namespace onnx {
+void save_decoder(const std::string& path, const nn::TransformerDecoder& decoder);
+void save_decoder(const std::string& path, const nn::Embedding& embedding, const nn::TransformerDecoder& decoder, const nn::Linear& output);
+}  // namespace onnx
+
 }  // namespace dl

@@ -196,6 +196,10 @@ DL_API dl_status dl_generation_step_sampled(dl_generation* generation, double te
 DL_API dl_status dl_generation_tokens(dl_generation* generation, dl_tensor** output);
 /* Logits [batch, vocab] (f32, device) the latest token was chosen from. */
 DL_API dl_status dl_generation_logits(dl_generation* generation, dl_tensor** output);
+/* extensions/onnx/include/dl/onnx_c_api.h:17-18 -- the decoder as an ONNX file (opset 24) with one past_key_i / past_value_i
+ * input and one present_key_i / present_value_i output per layer; embedding and output both given: int64 input_ids in,
+ * logits out; both NULL: features in, hidden states out.  Host work only (weights are read back from their device). */
+DL_API dl_status dl_onnx_save_decoder(const char* path, const dl_module* decoder, const dl_module* embedding, const dl_module* output);
 /* Rows of the buffers in which a bf16 decoder of this width (and per-rank SwiGLU width) carries per-row partial sums of
  * squares from one kernel to the next: the largest count any of its kernels may write.  Host arithmetic only. */
 DL_API int64_t dl_b200_shadow_partial_rows(int64_t dimensions, int64_t hidden);

@@ -98,6 +98,7 @@ class CpuLib:
               + [C.c_double, fp, C.c_void_p])
             f("sample", C.c_int, [fp, C.c_int64, C.c_int64, C.c_double, C.POINTER(C.c_double), ip])
             f("save_state", C.c_int, [C.c_void_p, C.c_char_p])
+            f("save_onnx", C.c_int, [C.c_void_p, C.c_char_p, C.c_int])
             f("archive_size", C.c_int64, [C.c_char_p])
             f("archive_entry", C.c_int, [C.c_char_p, C.c_int64, C.c_char_p, C.c_int64, ip, ip, C.POINTER(C.c_int32), C.c_void_p, C.c_int64])
 
@@ -176,6 +177,10 @@ class CpuDecoder:
     def save_state(self, path: str) -> None:
         """Reference only: the model's weights written by the reference's dl::io::save."""
         self.l.check(self.l.save_state(self.handle, path.encode()))
+
+    def save_onnx(self, path: str, with_head: bool) -> None:
+        """Reference only: the decoder written by the reference's own ONNX exporter (dl::onnx::save_decoder)."""
+        self.l.check(self.l.save_onnx(self.handle, path.encode(), int(with_head)))
 
     def close(self):
         if self.cache:

@@ -9,6 +9,7 @@
 //   * the reference's CPU decoder can be timed as the CPU baseline on the benchmark host.
 // Function names and argument meaning mirror decoder_oracle.c with the prefix ref_.
 #include "dl/dl.h"
+#include "dl/onnx.h"
 
 #include <cstdint>
 #include <cstdio>
@@ -305,6 +306,16 @@ int ref_timed_decode(void* handle, const int64_t* prompt, int64_t batch, int64_t
     for (int value : status)
         if (value) return 1;
     return 0;
+}
+
+// The model written by the reference's ONNX exporter (extensions/onnx/src/decoder.cpp): with_head != 0 exports
+// input_ids -> logits with the (tied) table, otherwise features -> hidden states.
+int ref_save_onnx(void* handle, const char* path, int with_head) {
+    return guarded([&] {
+        auto& model = *static_cast<Model*>(handle);
+        if (with_head) dl::onnx::save_decoder(path, *model.tokens, *model.decoder, *model.output);
+        else dl::onnx::save_decoder(path, *model.decoder);
+    });
 }
 
 int ref_gqa_attention(const float* query, const float* key, const float* value, int64_t batch, int64_t heads,

@@ -1,4 +1,4 @@
-"""Regenerates tests/golden/decoder_golden.npz and the weight archives tests/golden/*.ct by running the seeded cases of cases.py on the UNMODIFIED
+"""Regenerates tests/golden/decoder_golden.npz, the weight archives tests/golden/*.ct and the ONNX files tests/golden/*.onnx by running the seeded cases of cases.py on the UNMODIFIED
 reference CPU library (oracle/_ref, built by `make -C oracle ref` where the reference tree is present).
 
     python tests/golden/make_golden.py
@@ -60,6 +60,9 @@ def main():
     for name, spec in archive_cases().items():   # weight archives written by the reference's dl::io::save
         model = oracle.CpuDecoder(spec, W.make_weights(spec, seed=77), kind="ref")
         model.save_state(os.path.join(here, name + ".ct"))
+        # the same decoder written by the reference's ONNX exporter: features -> hidden states, and input_ids -> logits
+        model.save_onnx(os.path.join(here, name + "_decoder.onnx"), False)
+        model.save_onnx(os.path.join(here, name + "_lm.onnx"), True)
         model.close()
     np.savez_compressed(os.path.join(os.path.dirname(os.path.abspath(__file__)), "decoder_golden.npz"), **out)
     print("wrote", len(out), "arrays")
