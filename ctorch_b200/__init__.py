@@ -47,7 +47,7 @@ class ShadowLinearArgs(C.Structure):
                 ("out", C.c_int64), ("sumsq_in", C.c_void_p), ("parts_in", C.c_int32), ("eps", C.c_double), ("epilogue", C.c_int),
                 ("residual", C.c_void_p), ("qkv", C.POINTER(QkvArgs)), ("y", C.c_void_p), ("out_hi", C.c_void_p),
                 ("out_lo", C.c_void_p), ("out_norm_weight", C.c_void_p), ("out_norm_dtype", C.c_int32), ("sumsq_out", C.c_void_p),
-                ("best_value", C.c_void_p), ("best_index", C.c_void_p)]
+                ("best_value", C.c_void_p), ("best_index", C.c_void_p), ("y_copies", C.POINTER(C.c_void_p)), ("copies", C.c_int32)]
 
 
 class B200Error(RuntimeError):
@@ -154,7 +154,8 @@ def _declare(l: C.CDLL) -> None:
         "b200_sample": (C.c_int, [vp, i64, i64, C.c_double, vp, vp, vp]),
         "dl_generation_step_sampled": (C.c_int, [vp, C.c_double, vp, vp]),
         "b200_linear_argmax_parts": (i32, [i64, i64, i64]),
-        "b200_tp_reduce_parts": (i32, [i64]), "b200_tp_region_bytes": (sz, [sz]), "b200_tp_slot": (vp, [vp, sz, i32]),
+        "b200_tp_argmax_finish": (C.c_int, [pp, i32, i32, sz, i32, vp, vp, i32, i64, vp, vp, vp, i64, vp, pp, i32, vp]),
+        "b200_tp_reduce_parts": (i32, [i64]), "b200_tp_region_bytes": (sz, [sz, i32]), "b200_tp_slot": (vp, [vp, sz, i32, i32, i32]),
         "b200_tp_reduce_shadow": (C.c_int, [pp, i32, i32, i32, sz, i64, i64, vp, i32, vp, vp, vp, vp, vp]),
         "b200_argmax_finish": (C.c_int, [vp, vp, i32, i64, vp, vp, vp, i64, vp, pp, i32, vp]),
         "b200_scaled_add": (C.c_int, [vp, vp, C.c_float, i64, vp]),

@@ -23,7 +23,10 @@ void tp_all_reduce(int device, float* data, std::size_t count);
 void tp_symmetric_handle(int device, std::size_t slot_bytes, void* handle64);
 void tp_symmetric_open(int device, const void* handles, int world);
 bool tp_symmetric_ready(int device, std::size_t bytes);   // mapped on all ranks and a slot holds `bytes`
-float* tp_partial_slot(int device, int slot);              // this rank's partial rows, slot 0 or 1
+float* tp_partial_slot(int device, int slot, int owner = -1);   // this rank's partial rows of sum 0 or 1 in rank `owner`'s region (own by default)
+void tp_argmax_finish(int device, std::int32_t first_index, const float* best_value, const std::int32_t* best_index, std::int32_t parts,
+                      std::int64_t rows, std::int64_t* next, std::int64_t* ids, std::int64_t* history, std::int64_t history_rows,
+                      std::int32_t* counter, b200_kv_cache* const* caches, std::int32_t cache_count);
 void tp_reduce_shadow(int device, int slot, std::int64_t rows, std::int64_t width, const void* norm_weight, int norm_dtype, float* out,
                       void* out_hi, void* out_lo, float* sumsq_out);
 }  // namespace runtime

@@ -332,10 +332,23 @@ void DecodePlan::logits(const Linear& output, Index rows, float* out, void* stre
     probe(0);
 }
 
+// With tensor parallelism over mapped peer memory the vocabulary is split over the ranks in whole 128-row tiles: this rank's
+// slice of the output table, as (first row, rows).  {0, V} otherwise.
+std::pair<Index, Index> DecodePlan::vocabulary_slice(const Linear& output, Index rows, int device) const {
+    const Index V = output.weight().size(0);
+    const int world = owner_.tp_world(), rank = owner_.tp_rank();
+    if (world <= 1 || rows > 1024 || !runtime::tp_symmetric_ready(device, 1)) return {0, V};
+    const Index tiles = (V + 127) / 128, each = (tiles + world - 1) / world * 128;
+    if (each * (world - 1) >= V) return {0, V};   // a vocabulary too small to give every rank a slice: replicated logits
+    const Index first = each * rank;
+    return {first, std::min(each, V - first)};
+}
+
 bool DecodePlan::prepare_choice(const Linear& output, Index rows, int device) {
-    const Index V = output.weight().size(0), D = owner_.dimensions();
+    const Index D = owner_.dimensions();
     if (!shadows_for(rows) || output.weight().dtype() != DType::bf16 || output.weight().size(1) != D) return false;
-    const Index parts = b200_linear_argmax_parts(rows, D, V);
+    const Index slice = vocabulary_slice(output, rows, device).second;
+    const Index parts = b200_linear_argmax_parts(rows, D, slice);
     if (parts <= 0) return false;
     if (!best_value_.defined() || best_value_.numel() < parts * rows || best_value_.device().index != device) {
         synchronize(Device::cuda(device));
@@ -350,20 +363,30 @@ bool DecodePlan::prepare_choice(const Linear& output, Index rows, int device) {
 void DecodePlan::choose(const Linear& output, Index rows, Index* next, Index* ids, Index* history, Index history_rows, std::int32_t* counter,
                         std::span<b200_kv_cache* const> advance, void* stream) {
     const Index V = output.weight().size(0), D = owner_.dimensions();
-    const Index parts = b200_linear_argmax_parts(rows, D, V);
+    const int device = h_.device().index;
+    const auto [first, slice] = vocabulary_slice(output, rows, device);
+    const bool split = slice != V;
+    const Index parts = b200_linear_argmax_parts(rows, D, slice);
     if (parts <= 0 || !best_value_.defined() || best_value_.numel() < parts * rows)
         throw std::logic_error("fused logits + argmax was not prepared for this row count");
     b200_shadow_linear_args args{};
     args.x_hi = hs_hi_.raw_data(); args.rows = rows; args.in = D;
     args.x_lo = owner_.activation_dtype() == DType::bf16 && rows >= 17 ? nullptr : hs_lo_.raw_data();
-    args.weight = output.weight().raw_data(); args.out = V;
+    args.weight = static_cast<const char*>(output.weight().raw_data()) + static_cast<std::size_t>(first) * static_cast<std::size_t>(D) * 2;
+    args.out = slice;
     args.sumsq_in = sq_attn_.data<float>(); args.parts_in = last_parts_; args.eps = owner_.normalization().epsilon();
     args.epilogue = B200_EPI_ARGMAX;
     args.best_value = static_cast<float*>(best_value_.mutable_data());
     args.best_index = static_cast<std::int32_t*>(best_index_.mutable_data());
     shadow_linear(args, stream, "logits + argmax");
-    runtime::check(b200_argmax_finish(args.best_value, args.best_index, static_cast<std::int32_t>(parts), rows, next, ids, history, history_rows,
-                                      counter, advance.data(), static_cast<std::int32_t>(advance.size()), stream), "argmax merge");
+    if (split) {
+        // every rank holds the best of its slice; the candidates meet over peer memory and every rank picks the same token
+        runtime::tp_argmax_finish(device, static_cast<std::int32_t>(first), args.best_value, args.best_index, static_cast<std::int32_t>(parts), rows,
+                                  next, ids, history, history_rows, counter, advance.data(), static_cast<std::int32_t>(advance.size()));
+    } else {
+        runtime::check(b200_argmax_finish(args.best_value, args.best_index, static_cast<std::int32_t>(parts), rows, next, ids, history, history_rows,
+                                          counter, advance.data(), static_cast<std::int32_t>(advance.size()), stream), "argmax merge");
+    }
     probe(2);
 }
 
@@ -448,6 +471,12 @@ void DecodePlan::run_layers(const float* x, Index batch, Index length, std::span
             b200_shadow_linear_args out_proj{};
             out_proj.x_hi = att_hi_.raw_data(); out_proj.x_lo = lo_plane(att_lo_); out_proj.rows = rows; out_proj.in = Dl;
             out_proj.weight = packed.wo; out_proj.out = D; out_proj.y = peer_sum ? runtime::tp_partial_slot(device, 0) : h;
+            float* o_copies[7];
+            if (peer_sum) {   // the partial rows go to this rank's slot in every peer's memory from the projection's own epilogue
+                for (int r = 0, c = 0; r < world; ++r)
+                    if (r != rank) o_copies[c++] = runtime::tp_partial_slot(device, 0, r);
+                out_proj.y_copies = o_copies; out_proj.copies = world - 1;
+            }
             out_proj.epilogue = adds_residual ? B200_EPI_RESIDUAL : B200_EPI_STORE; out_proj.residual = adds_residual ? in : nullptr;
             if (!parallel) {
                 out_proj.out_hi = hs_hi_.mutable_data(); out_proj.out_lo = hs_lo_.mutable_data();
@@ -464,6 +493,12 @@ void DecodePlan::run_layers(const float* x, Index batch, Index length, std::span
             b200_shadow_linear_args down{};
             down.x_hi = act_hi_.raw_data(); down.x_lo = lo_plane(act_lo_); down.rows = rows; down.in = Fl;
             down.weight = packed.wd; down.out = D; down.y = peer_sum ? runtime::tp_partial_slot(device, 1) : h;
+            float* down_copies[7];
+            if (peer_sum) {
+                for (int r = 0, c = 0; r < world; ++r)
+                    if (r != rank) down_copies[c++] = runtime::tp_partial_slot(device, 1, r);
+                down.y_copies = down_copies; down.copies = world - 1;
+            }
             down.epilogue = adds_residual ? B200_EPI_RESIDUAL : B200_EPI_STORE; down.residual = adds_residual ? h : nullptr;
             if (!parallel) {
                 down.out_hi = hs_hi_.mutable_data(); down.out_lo = hs_lo_.mutable_data();

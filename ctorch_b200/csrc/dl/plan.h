@@ -13,6 +13,8 @@
 
 #include <cuda_runtime.h>
 
+#include <utility>
+
 namespace dl::nn {
 
 Tensor interleave_rows(const Tensor& even_rows, const Tensor& odd_rows);  // [n,k],[n,k] -> [2n,k]
@@ -43,6 +45,9 @@ public:
     // whether the fused path serves this projection and row count; choose() enqueues the projection with the argmax
     // epilogue and the merge, which also feeds the chosen ids back (ids, history, counter as b200_token_feedback).
     bool prepare_choice(const Linear& output, Index rows, int device);
+    // This rank's rows of the output table under tensor parallelism with mapped peer memory (first row, count); the whole
+    // table otherwise.  The ranks then exchange one (value, index) candidate per row instead of each reading the table.
+    std::pair<Index, Index> vocabulary_slice(const Linear& output, Index rows, int device) const;
     // `advance`: caches (at most 64) whose lengths the merge kernel moves on by one token, sparing the step a launch.
     void choose(const Linear& output, Index rows, Index* next, Index* ids, Index* history, Index history_rows, std::int32_t* counter,
                 std::span<b200_kv_cache* const> advance, void* stream);

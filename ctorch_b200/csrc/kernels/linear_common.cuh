@@ -37,7 +37,25 @@ struct LinearParams {
     // B200_EPI_ARGMAX: per feature tile and row, the preferred value and its feature index
     float* best_value;                 // [tiles][rows]
     int32_t* best_index;               // [tiles][rows]
+    // Store and residual epilogues: further [rows, out] f32 matrices that receive the same result rows as y.  Tensor
+    // parallelism points them at this rank's slot in every peer's memory, so the partial sums travel over NVLink from
+    // the projection's own epilogue (plain peer stores) and the sum that follows reads local memory only.
+    float* y_copy[7];
+    int copies;
 };
+
+// The result pair of (row, feature0) to every extra destination (see LinearParams::y_copy).
+__device__ __forceinline__ void store_copies(const LinearParams& p, int64_t at, float a, float b, bool second) {
+    for (int c = 0; c < p.copies; ++c) {
+        float* target = p.y_copy[c] + at;
+        if (second && (reinterpret_cast<uintptr_t>(target) & 7) == 0) {
+            *reinterpret_cast<float2*>(target) = make_float2(a, b);
+        } else {
+            target[0] = a;
+            if (second) target[1] = b;
+        }
+    }
+}
 
 // (value, index) ordering of the reference's argmax (src/kernels/cpu/reduction.cpp:128-151): a NaN beats every number,
 // and among equals (or among NaNs) the lower index wins.
@@ -67,12 +85,14 @@ __device__ __forceinline__ void linear_epilogue(const LinearParams& p, int row, 
     if constexpr (EPI == B200_EPI_STORE) {
         p.y[static_cast<int64_t>(row) * p.out + feature0] = a;
         if (second) p.y[static_cast<int64_t>(row) * p.out + feature0 + 1] = b;
+        store_copies(p, static_cast<int64_t>(row) * p.out + feature0, a, b, second);
     } else if constexpr (EPI == B200_EPI_RESIDUAL) {
         const int64_t at = static_cast<int64_t>(row) * p.out + feature0;
         a = __fadd_rn(p.residual[at], a);
         b = second ? __fadd_rn(p.residual[at + 1], b) : 0.0f;
         p.y[at] = a;
         if (second) p.y[at + 1] = b;
+        store_copies(p, at, a, b, second);
     } else if constexpr (EPI == B200_EPI_SWIGLU) {
         // rows 2j (gate_j) and 2j+1 (up_j) of the interleaved weight
         a = __fmul_rn(p.x_hi ? silu_fast(a) : silu_reference(a), b);   // shadow input = bf16 model: see silu_fast

@@ -33,6 +33,7 @@ __device__ __forceinline__ void finish_pair(const LinearParams& p, int row, int 
             p.y[at] = a;
             if (second) p.y[at + 1] = b;
         }
+        store_copies(p, at, a, b, second);
     } else {
         linear_epilogue<EPI>(p, row, feature0, a, b, place);
     }

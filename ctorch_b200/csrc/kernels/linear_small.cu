@@ -289,6 +289,15 @@ extern "C" int b200_linear_shadow(const b200_shadow_linear_args* args, void* str
     p.out_hi = static_cast<__nv_bfloat16*>(args->out_hi); p.out_lo = static_cast<__nv_bfloat16*>(args->out_lo);
     p.out_norm_weight = args->out_norm_weight; p.out_norm_dtype = args->out_norm_dtype; p.sumsq_out = args->sumsq_out;
     p.best_value = args->best_value; p.best_index = args->best_index;
+    if (args->copies < 0 || args->copies > 7 || (args->copies > 0 && (!args->y_copies || (epilogue != B200_EPI_STORE && epilogue != B200_EPI_RESIDUAL)))) {
+        set_error("b200_linear_shadow: at most 7 result copies, for store and residual epilogues only");
+        return B200_BAD_ARGUMENT;
+    }
+    p.copies = args->copies;
+    for (int c = 0; c < p.copies; ++c) {
+        if (!args->y_copies[c]) { set_error("b200_linear_shadow: result copy %d is NULL", c); return B200_BAD_ARGUMENT; }
+        p.y_copy[c] = args->y_copies[c];
+    }
     const int status = fill_qkv(p, epilogue, args->qkv, args->rows, args->out);
     if (status != B200_OK) return status;
     const int launched = launch_linear_stream(p, epilogue, as_stream(stream));

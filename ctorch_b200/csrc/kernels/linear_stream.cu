@@ -374,6 +374,7 @@ __global__ void __launch_bounds__(kThreads, 2) linear_stream_kernel(const Stream
                     a = __fadd_rn(carried.x, a);
                     b = __fadd_rn(carried.y, b);
                     *reinterpret_cast<float2*>(p.y + static_cast<int64_t>(row) * p.out + feature0) = make_float2(a, b);
+                    store_copies(p, static_cast<int64_t>(row) * p.out + feature0, a, b, true);
                 }
             } else {
                 if (live) linear_epilogue<EPI>(p, row, feature0, a, b);

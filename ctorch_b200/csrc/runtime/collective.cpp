@@ -156,7 +156,7 @@ void tp_symmetric_handle(int device, std::size_t slot_bytes, void* handle64) {
     if (!handle64 || slot_bytes == 0 || (slot_bytes & 255)) throw std::invalid_argument("slot size must be a positive multiple of 256 bytes");
     set_device(device);
     void* region = nullptr;
-    const std::size_t bytes = b200_tp_region_bytes(slot_bytes);
+    const std::size_t bytes = b200_tp_region_bytes(slot_bytes, group.world);
     check_runtime(cudaMalloc(&region, bytes), "cudaMalloc(symmetric region)");
     check_runtime(cudaMemset(region, 0, bytes), "cudaMemset(symmetric region)");
     check_runtime(cudaDeviceSynchronize(), "cudaDeviceSynchronize");
@@ -194,10 +194,12 @@ bool tp_symmetric_ready(int device, std::size_t bytes) {
     return device >= 0 && device < 64 && groups[device].mapped && bytes <= groups[device].slot_bytes;
 }
 
-float* tp_partial_slot(int device, int slot) {
+// Where this rank's partial rows of sum `slot` go in the region of rank `owner` (its own region, or a peer's as mapped here).
+float* tp_partial_slot(int device, int slot, int owner) {
     std::lock_guard<std::mutex> lock(group_mutex);
     const Group& group = groups[device];
-    return static_cast<float*>(b200_tp_slot(group.regions[group.rank], group.slot_bytes, slot));
+    if (owner < 0) owner = group.rank;
+    return static_cast<float*>(b200_tp_slot(group.regions[owner], group.slot_bytes, group.world, slot, group.rank));
 }
 
 void tp_reduce_shadow(int device, int slot, std::int64_t rows, std::int64_t width, const void* norm_weight, int norm_dtype, float* out,
@@ -209,6 +211,18 @@ void tp_reduce_shadow(int device, int slot, std::int64_t rows, std::int64_t widt
     }
     check(b200_tp_reduce_shadow(group.regions, group.rank, group.world, slot, group.slot_bytes, rows, width, norm_weight, norm_dtype, out,
                                 out_hi, out_lo, sumsq_out, stream(device)), "peer-memory sum");
+}
+
+void tp_argmax_finish(int device, std::int32_t first_index, const float* best_value, const std::int32_t* best_index, std::int32_t parts,
+                      std::int64_t rows, std::int64_t* next, std::int64_t* ids, std::int64_t* history, std::int64_t history_rows,
+                      std::int32_t* counter, b200_kv_cache* const* caches, std::int32_t cache_count) {
+    Group group;
+    {
+        std::lock_guard<std::mutex> lock(group_mutex);
+        group = groups[device];
+    }
+    check(b200_tp_argmax_finish(group.regions, group.rank, group.world, group.slot_bytes, first_index, best_value, best_index, parts, rows, next,
+                                ids, history, history_rows, counter, caches, cache_count, stream(device)), "cross-rank greedy choice");
 }
 
 int tp_world(int device) {

@@ -149,6 +149,8 @@ typedef struct b200_shadow_linear_args {
     float* sumsq_out;              /* residual epilogue: [b200_linear_shadow_parts(rows, in, out)][rows] */
     float* best_value;             /* B200_EPI_ARGMAX: [b200_linear_argmax_parts(rows, in, out)][rows] */
     int32_t* best_index;           /* B200_EPI_ARGMAX: same shape, feature index of best_value */
+    float* const* y_copies;        /* store / residual epilogues: `copies` (0..7) further [rows, out] f32 matrices that receive the */
+    int32_t copies;                /*   same rows as y - a tensor-parallel rank's slot in each peer's memory (plain peer stores) */
 } b200_shadow_linear_args;
 /* Up to 16 rows with in <= 2048: streaming kernel (bulk-TMA weight ring, mma.sync).  More rows or a wider input:
  * dense tcgen05 kernel (TMA operand tiles, accumulator in tensor memory; K split over a thread-block cluster when the
@@ -263,20 +265,33 @@ B200_API int b200_scaled_add(float* y, const float* x, float scale, int64_t coun
 B200_API int b200_take_device_status(int32_t device, void* stream, int32_t* status);
 
 /* ---- tensor-parallel sum over NVLink peer memory (no reference counterpart: the reference has no tensor parallelism) ----
- * Every rank owns a region of b200_tp_region_bytes(slot_bytes) bytes of its own device memory (zero-filled, cudaMalloc'ed,
- * mapped by every rank of the group, e.g. through CUDA IPC): control words and two slots of partial rows; b200_tp_slot
- * gives the address of a slot inside a region.  b200_tp_reduce_shadow, called by every rank at the same point of its
- * stream with regions[r] = rank r's region as mapped here, publishes "my slot is written", waits (bounded; on expiry the
- * device status word reads B200_DEVICE_TIMEOUT) for all ranks, and writes out[rows, width] = sum over ranks in rank order of
- * their slot rows, the shadow planes of out * norm_weight and per-row partial sums of squares
- * ([b200_tp_reduce_parts(width)][rows], one partial per 1024 columns).  The caller's
- * projection writes its partial rows into its own slot beforehand, alternating slots 0 and 1 from call to call. */
+ * Every rank owns a region of b200_tp_region_bytes(slot_bytes, world) bytes of its own device memory (zero-filled,
+ * cudaMalloc'ed, mapped by every rank of the group, e.g. through CUDA IPC): control words and, for each of two alternating
+ * sums, one slot of partial rows PER SENDER; b200_tp_slot(region, slot_bytes, world, slot, sender) is the address where
+ * rank `sender` deposits its partial rows of sum `slot` in that region.  A rank's projection writes its partial rows into
+ * its slot of EVERY region (b200_shadow_linear_args: y = the local one, y_copies = the peers'), so the rows cross NVLink
+ * from the projection's epilogue.  b200_tp_reduce_shadow, called by every rank at the same point of its stream with
+ * regions[r] = rank r's region as mapped here, then publishes "my rows are written" to all ranks, waits (bounded; on
+ * expiry the device status word reads B200_DEVICE_TIMEOUT) for all ranks' signals, and writes out[rows, width] = sum over
+ * senders in rank order of the slots of its OWN region (local loads only), the shadow planes of out * norm_weight and
+ * per-row partial sums of squares ([b200_tp_reduce_parts(width)][rows], one partial per 1024 columns).  Callers alternate
+ * slots 0 and 1 from call to call. */
 B200_API int32_t b200_tp_reduce_parts(int64_t width);
-B200_API size_t b200_tp_region_bytes(size_t slot_bytes);
-B200_API void* b200_tp_slot(void* region, size_t slot_bytes, int32_t slot);
+B200_API size_t b200_tp_region_bytes(size_t slot_bytes, int32_t world);
+B200_API void* b200_tp_slot(void* region, size_t slot_bytes, int32_t world, int32_t slot, int32_t sender);
 B200_API int b200_tp_reduce_shadow(void* const* regions, int32_t rank, int32_t world, int32_t slot, size_t slot_bytes, int64_t rows,
                                    int64_t width, const void* norm_weight, int32_t norm_dtype, float* out, void* out_hi, void* out_lo,
                                    float* sumsq_out, void* stream);
+
+/* Greedy choice with the vocabulary split over the ranks (no reference counterpart): this rank ran the logits projection
+ * with B200_EPI_ARGMAX over the table rows [first_index, first_index + its slice) and holds per-tile candidates as for
+ * b200_argmax_finish.  The call merges them, deposits one (value, global index) pair per row in every rank's region
+ * (behind the slots: b200_tp_region_bytes covers the area; at most 1024 rows), waits (bounded) for all ranks' pairs and
+ * merges those under the same rule, so every rank feeds back the same token; then the bookkeeping of b200_argmax_finish. */
+B200_API int b200_tp_argmax_finish(void* const* regions, int32_t rank, int32_t world, size_t slot_bytes, int32_t first_index,
+                                   const float* best_value, const int32_t* best_index, int32_t parts, int64_t rows, int64_t* next,
+                                   int64_t* ids, int64_t* history, int64_t history_rows, int32_t* counter,
+                                   b200_kv_cache* const* caches, int32_t cache_count, void* stream);
 
 #ifdef __cplusplus
 }

@@ -534,19 +534,23 @@ def test_temperature_sampling(rows, width, temperature):
 
 def _tp_regions(world, slot_bytes):
     l = B.lib()
-    size = l.b200_tp_region_bytes(slot_bytes)
+    size = l.b200_tp_region_bytes(slot_bytes, world)
     regions = [torch.zeros((size,), dtype=torch.uint8, device="cuda") for _ in range(world)]
     table = (C.c_void_p * world)(*[r.data_ptr() for r in regions])
     return regions, table
 
 
-def _slot_view(region, slot_bytes, slot, rows, width):
-    return region[4096 + slot * slot_bytes: 4096 + slot * slot_bytes + rows * width * 4].view(torch.float32).view(rows, width)
+def _slot_view(region, slot_bytes, world, slot, sender, rows, width):
+    """Where rank `sender` deposits its partial rows of sum `slot` inside one rank's region."""
+    at = B.lib().b200_tp_slot(region.data_ptr(), slot_bytes, world, slot, sender) - region.data_ptr()
+    assert at == 4096 + (slot * world + sender) * slot_bytes
+    return region[at: at + rows * width * 4].view(torch.float32).view(rows, width)
 
 
 def test_peer_memory_sum_one_gpu():
     """The tensor-parallel sum kernel on one GPU: as a group of one, and as rank 0 of two with the other rank's arrival and
-    partial rows put in place by the host beforehand (two kernels that wait on one another never share a GPU)."""
+    partial rows put in place by the host beforehand (two kernels that wait on one another never share a GPU).  The rows of
+    every sender lie in the summing rank's own region: the projections push them there."""
     l = B.lib()
     rows, width, slot_bytes = 5, 2560, 65536    # 2560 columns: three column chunks per row, the last one partial
     rng = np.random.default_rng(12)
@@ -560,8 +564,8 @@ def test_peer_memory_sum_one_gpu():
         regions, table = _tp_regions(world, slot_bytes)
         for call, slot in ((1, 0), (2, 1), (3, 0)):
             parts = [rng.standard_normal((rows, width), dtype=np.float32) for _ in range(world)]
-            for r in range(world):
-                _slot_view(regions[r], slot_bytes, slot, rows, width).copy_(torch.from_numpy(parts[r]))
+            for r in range(world):   # every sender's rows lie in rank 0's own region: the sum reads local memory only
+                _slot_view(regions[0], slot_bytes, world, slot, r, rows, width).copy_(torch.from_numpy(parts[r]))
             if world == 2:   # rank 1 "arrived" for this call
                 regions[0][4:8].view(torch.int32)[0] = call
             torch.cuda.synchronize()
@@ -667,3 +671,84 @@ def test_tensordot_matches_the_reference_rule(a_shape, b_shape, axes_a, axes_b):
     twice = (C.c_int64 * 2)(0, 0)
     assert B.lib().dl_tensordot(ta.h, tb.h, B.Shape(twice, 2), B.Shape(twice, 2), C.byref(bad)) == 1
     assert b"must be distinct" in B.lib().dl_last_error()
+
+
+@pytest.mark.parametrize("rows,inner,out,epilogue", [(4, 512, 1024, 1), (40, 1024, 512, 1), (200, 768, 1280, 0), (16, 2048, 768, 0)])
+def test_projection_pushes_its_rows_to_extra_destinations(rows, inner, out, epilogue):
+    """y_copies of a shadow linear: every extra destination receives exactly the rows written to y - the mechanism by which
+    a tensor-parallel rank's projection deposits its partial sums in the peers' memory from its own epilogue (here the
+    destinations are buffers of the same GPU).  Streaming kernel (4 and 16 rows), decode-batch kernel (40), prefill kernel (200)."""
+    l = B.lib()
+    rng = np.random.default_rng(rows + out)
+    x = rng.standard_normal((rows, inner), dtype=np.float32)
+    w = W.bf16_bits(0.05 * rng.standard_normal((out, inner), dtype=np.float32))
+    res = rng.standard_normal((rows, out), dtype=np.float32)
+    xd, wd, rd = dev(x), bf16_dev(w), dev(res)
+    hi = torch.zeros((rows, inner), dtype=torch.bfloat16, device="cuda")
+    lo = torch.zeros_like(hi)
+    sq = torch.zeros((1, rows), dtype=torch.float32, device="cuda")
+    y = torch.zeros((rows, out), dtype=torch.float32, device="cuda")
+    copies = [torch.full((rows, out), -7.0, dtype=torch.float32, device="cuda") for _ in range(3)]
+    table = (C.c_void_p * 3)(*[c.data_ptr() for c in copies])
+    torch.cuda.synchronize()
+    B.kcheck(l.b200_shadow_from_rows(xd.data_ptr(), rows, inner, None, 0, hi.data_ptr(), lo.data_ptr(), sq.data_ptr(), stream()))
+    args = B.ShadowLinearArgs(hi.data_ptr(), lo.data_ptr(), rows, inner, wd.data_ptr(), out, None, 0, 0.0, epilogue,
+                              rd.data_ptr() if epilogue == 1 else None, None, y.data_ptr(), None, None, None, 0, None, None, None, table, 3)
+    B.kcheck(l.b200_linear_shadow(C.byref(args), stream()))
+    sync()
+    want = oracle.linear(x, w) + (res if epilogue == 1 else 0)
+    assert rel(y.cpu().numpy(), want) < 3e-5
+    for copy in copies:
+        assert torch.equal(copy, y)
+    bad = B.ShadowLinearArgs(hi.data_ptr(), lo.data_ptr(), rows, inner, wd.data_ptr(), out, None, 0, 0.0, 2, None, None, y.data_ptr(),
+                             None, None, None, 0, None, None, None, table, 3)
+    assert l.b200_linear_shadow(C.byref(bad), stream()) != 0      # copies belong to the store and residual epilogues
+
+
+def test_cross_rank_greedy_choice_one_gpu():
+    """The merge of the vocabulary-split greedy choice on one GPU: as a group of one, and as rank 0 of two with the other
+    rank's candidates and signal put in place by the host.  Ties between ranks go to the lower global index, NaN wins, and a
+    row whose best value sits in the peer's slice takes the peer's index."""
+    l = B.lib()
+    rows, parts, slot_bytes, first = 6, 5, 4096, 1000
+    rng = np.random.default_rng(3)
+    values = rng.standard_normal((parts, rows)).astype(np.float32)
+    indices = rng.permutation(parts * rows).reshape(parts, rows).astype(np.int32)
+    values[2, 1] = values[:, 1].max() + 1          # row 1: this rank wins clearly
+    values[:, 2] = -5.0                            # row 2: the peer will win
+    values[3, 3] = 9.0                             # row 3: exact tie with the peer, whose global index is lower
+    values[1, 4] = np.nan                          # row 4: NaN on this rank
+    local_best = []
+    for r in range(rows):
+        order = sorted(range(parts), key=lambda t: (not np.isnan(values[t, r]), -values[t, r] if not np.isnan(values[t, r]) else 0, indices[t, r]))
+        local_best.append((values[order[0], r], int(indices[order[0], r]) + first))
+    vd, idd = dev(values), dev(indices)
+    for world in (1, 2):
+        regions, table = _tp_regions(world, slot_bytes)
+        next_ids = torch.full((rows,), -1, dtype=torch.int64, device="cuda")
+        ids = torch.zeros((rows,), dtype=torch.int64, device="cuda")
+        history = torch.zeros((4, rows), dtype=torch.int64, device="cuda")
+        counter = torch.zeros((2,), dtype=torch.int32, device="cuda")
+        want = [index for _, index in local_best]
+        if world == 2:
+            area = 4096 + 2 * world * slot_bytes
+            peer_values = np.array([-1.0, -100.0, 3.0, 9.0, 50.0, np.inf], dtype=np.float32)
+            peer_index = np.array([7, 8, 9, 10, 11, 12], dtype=np.int32)
+            packed = (peer_index.astype(np.uint32).astype(np.uint64) << np.uint64(32)) | peer_values.view(np.uint32).astype(np.uint64)
+            regions[0][area + 1024 * 8: area + 1024 * 8 + rows * 8].view(torch.int64).copy_(torch.from_numpy(packed.view(np.int64)))
+            regions[0][(34 + 1) * 4:(34 + 2) * 4].view(torch.int32)[0] = 1      # chosen[1] = call 1: the peer's candidates are in place
+            want = [local_best[0][1] if local_best[0][0] > -1.0 else 7, want[1], 9, 10, want[4], 12]
+        torch.cuda.synchronize()
+        B.kcheck(l.b200_tp_argmax_finish(table, 0, world, slot_bytes, first, vd.data_ptr(), idd.data_ptr(), parts, rows, next_ids.data_ptr(),
+                                         ids.data_ptr(), history.data_ptr(), 4, counter.data_ptr(), None, 0, stream()))
+        sync()
+        status = C.c_int32()
+        B.kcheck(l.b200_take_device_status(0, stream(), C.byref(status)))
+        assert status.value == 0
+        assert next_ids.cpu().tolist() == want, (world, next_ids.cpu().tolist(), want)
+        assert ids.cpu().tolist() == want and history[0].cpu().tolist() == want and int(counter[0]) == 1
+        assert regions[0][50 * 4:51 * 4].view(torch.int32).item() == 1              # the owner's exchange counter
+        if world == 2:
+            assert regions[1][34 * 4:35 * 4].view(torch.int32).item() == 1          # the signal sent to the peer
+            sent = regions[1][4096 + 2 * world * slot_bytes: 4096 + 2 * world * slot_bytes + rows * 8].view(torch.int64).cpu().numpy().view(np.uint64)
+            assert [int(v >> np.uint64(32)) for v in sent] == [index for _, index in local_best]
