@@ -122,7 +122,7 @@ def _declare(l: C.CDLL) -> None:
         "dl_decoder_generate": (C.c_int, [vp, vp, vp, vp, i64, vp, pp]),
         "dl_generation_profile_step": (C.c_int, [vp, C.POINTER(C.c_double)]),
         "dl_b200_tp_unique_id": (C.c_int, [vp]), "dl_b200_tp_init": (C.c_int, [Device, i32, i32, vp]),
-        "dl_b200_tp_finalize": (C.c_int, [Device]),
+        "dl_b200_tp_finalize": (C.c_int, [Device]), "dl_b200_tp_set_push": (C.c_int, [Device, i32]),
         "dl_b200_tp_symmetric_handle": (C.c_int, [Device, sz, vp]), "dl_b200_tp_symmetric_open": (C.c_int, [Device, vp, i32]), "dl_transformer_decoder_set_tensor_parallel": (C.c_int, [vp, i32, i32]),
         "dl_b200_timer_start": (C.c_int, [Device]), "dl_b200_timer_stop": (C.c_int, [Device, C.POINTER(C.c_double)]),
         "dl_b200_stream": (vp, [Device]),
@@ -156,7 +156,7 @@ def _declare(l: C.CDLL) -> None:
         "b200_linear_argmax_parts": (i32, [i64, i64, i64]),
         "b200_tp_argmax_finish": (C.c_int, [pp, i32, i32, sz, i32, vp, vp, i32, i64, vp, vp, vp, i64, vp, pp, i32, vp]),
         "b200_tp_reduce_parts": (i32, [i64]), "b200_tp_region_bytes": (sz, [sz, i32]), "b200_tp_slot": (vp, [vp, sz, i32, i32, i32]),
-        "b200_tp_reduce_shadow": (C.c_int, [pp, i32, i32, i32, sz, i64, i64, vp, i32, vp, vp, vp, vp, vp]),
+        "b200_tp_reduce_shadow": (C.c_int, [pp, i32, i32, i32, sz, i32, i64, i64, vp, i32, vp, vp, vp, vp, vp]),
         "b200_argmax_finish": (C.c_int, [vp, vp, i32, i64, vp, vp, vp, i64, vp, pp, i32, vp]),
         "b200_scaled_add": (C.c_int, [vp, vp, C.c_float, i64, vp]),
         "b200_take_device_status": (C.c_int, [i32, vp, C.POINTER(i32)]),
@@ -541,7 +541,7 @@ def timer_stop(device: int = 0) -> float:
     return ms.value
 
 
-def tensor_parallel_init(rank: int, world: int, device: int, peer_slot_bytes: int = 8 << 20) -> None:
+def tensor_parallel_init(rank: int, world: int, device: int, peer_slot_bytes: int = 8 << 20, push: bool | None = None) -> None:
     """Joins the tensor-parallel group of `world` ranks; the NCCL id travels over torch.distributed (any backend).
     `peer_slot_bytes` > 0 also maps the ranks' symmetric memory (CUDA IPC handles gathered the same way) so that steps of
     up to that many bytes of residual rows sum over NVLink peer memory instead of calling NCCL."""
@@ -565,6 +565,8 @@ def tensor_parallel_init(rank: int, world: int, device: int, peer_slot_bytes: in
         table = [torch.empty_like(mine) for _ in range(world)]
         dist.all_gather(table, mine)
         check(lib().dl_b200_tp_symmetric_open(cuda(device), bytes(torch.cat(table).cpu().tolist()), world))
+        if push is not None:
+            check(lib().dl_b200_tp_set_push(cuda(device), int(push)))
         dist.barrier()   # every rank has mapped every region before the first step
 
 

@@ -417,6 +417,9 @@ dl_status dl_b200_tp_symmetric_handle(dl_device device, size_t slot_bytes, void*
 dl_status dl_b200_tp_symmetric_open(dl_device device, const void* handles, int32_t world) {
     return invoke([&] { dl::runtime::tp_symmetric_open(device.index, handles, world); });
 }
+dl_status dl_b200_tp_set_push(dl_device device, int32_t push) {
+    return invoke([&] { dl::runtime::tp_set_push(device.index, push != 0); });
+}
 dl_status dl_b200_tp_finalize(dl_device device) { return invoke([&] { dl::runtime::tp_finalize(device.index); }); }
 dl_status dl_transformer_decoder_set_tensor_parallel(dl_module* decoder, int32_t rank, int32_t world) {
     return invoke([&] { as<dl::nn::TransformerDecoder>(decoder, "TransformerDecoder").set_tensor_parallel(rank, world); });

@@ -22,6 +22,8 @@ int tp_rank(int device);
 void tp_all_reduce(int device, float* data, std::size_t count);
 void tp_symmetric_handle(int device, std::size_t slot_bytes, void* handle64);
 void tp_symmetric_open(int device, const void* handles, int world);
+void tp_set_push(int device, bool push);   // partial sums pushed by the projections (true) or pulled by the sums (false, default)
+bool tp_push(int device);
 bool tp_symmetric_ready(int device, std::size_t bytes);   // mapped on all ranks and a slot holds `bytes`
 float* tp_partial_slot(int device, int slot, int owner = -1);   // this rank's partial rows of sum 0 or 1 in rank `owner`'s region (own by default)
 void tp_argmax_finish(int device, std::int32_t first_index, const float* best_value, const std::int32_t* best_index, std::int32_t parts,

@@ -409,6 +409,7 @@ void DecodePlan::run_layers(const float* x, Index batch, Index length, std::span
         // With symmetric memory mapped (and the rows fitting a slot) the projections write their partial rows into this
         // rank's slot and one kernel sums the ranks' slots over NVLink and rebuilds the shadow; otherwise NCCL.
         const bool peer_sum = parallel && runtime::tp_symmetric_ready(device, static_cast<std::size_t>(rows * D) * sizeof(float));
+        const bool push_sums = peer_sum && runtime::tp_push(device);
         const int parts_summed = peer_sum ? b200_tp_reduce_parts(D) : 1;   // partial sums of squares the rebuilt shadow comes with
         const int parts_o = parallel ? parts_summed : b200_linear_shadow_parts(rows, D, D);
         const int parts_down = parallel ? parts_summed : b200_linear_shadow_parts(rows, F, D);
@@ -472,7 +473,7 @@ void DecodePlan::run_layers(const float* x, Index batch, Index length, std::span
             out_proj.x_hi = att_hi_.raw_data(); out_proj.x_lo = lo_plane(att_lo_); out_proj.rows = rows; out_proj.in = Dl;
             out_proj.weight = packed.wo; out_proj.out = D; out_proj.y = peer_sum ? runtime::tp_partial_slot(device, 0) : h;
             float* o_copies[7];
-            if (peer_sum) {   // the partial rows go to this rank's slot in every peer's memory from the projection's own epilogue
+            if (peer_sum && push_sums) {   // the partial rows go to this rank's slot in every peer's memory from the projection's own epilogue
                 for (int r = 0, c = 0; r < world; ++r)
                     if (r != rank) o_copies[c++] = runtime::tp_partial_slot(device, 0, r);
                 out_proj.y_copies = o_copies; out_proj.copies = world - 1;
@@ -494,7 +495,7 @@ void DecodePlan::run_layers(const float* x, Index batch, Index length, std::span
             down.x_hi = act_hi_.raw_data(); down.x_lo = lo_plane(act_lo_); down.rows = rows; down.in = Fl;
             down.weight = packed.wd; down.out = D; down.y = peer_sum ? runtime::tp_partial_slot(device, 1) : h;
             float* down_copies[7];
-            if (peer_sum) {
+            if (peer_sum && push_sums) {
                 for (int r = 0, c = 0; r < world; ++r)
                     if (r != rank) down_copies[c++] = runtime::tp_partial_slot(device, 1, r);
                 down.y_copies = down_copies; down.copies = world - 1;

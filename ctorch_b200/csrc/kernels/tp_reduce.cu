@@ -18,6 +18,8 @@
 //   3. A CTA takes 1024 columns of one row, one 16-byte vector per thread: it reads them from the W sender slots of its OWN
 //      region (local memory; ld.global.cv, because the peers wrote those lines and a stale L1 copy of the slot's previous
 //      use must not be served), adds them in rank order 0..W-1 (every rank computes the same bits),
+//      (`pull` mode: the projections wrote only their own region, and sender r's rows are read from rank r's region over
+//      NVLink instead - one round trip per call; measured faster than pushing at two ranks, see the plan)
 //      writes the f32 values, the shadow planes of value * norm_weight, and its partial of the row's sum of squares.
 //   4. The last CTA to leave stores the call number (exit ticket), so the next call sees e + 1.
 // Slot reuse: a rank overwrites its slots of sum s two calls later.  By then it has passed the wait of the call in
@@ -66,7 +68,7 @@ __global__ void __launch_bounds__(kReduceThreads) tp_reduce_shadow_kernel(const 
                                                                          int64_t slot_bytes, int64_t rows, int64_t width,
                                                                          const void* norm_weight, int norm_dtype, float* out,
                                                                          __nv_bfloat16* out_hi, __nv_bfloat16* out_lo, float* sumsq_out,
-                                                                         int32_t* status) {
+                                                                         int32_t* status, int pull) {
     __shared__ float partial[32];
     __shared__ uint32_t proceed;
     grid_dependency_wait();   // the projection that wrote this rank's slot precedes this kernel in the stream
@@ -108,7 +110,7 @@ __global__ void __launch_bounds__(kReduceThreads) tp_reduce_shadow_kernel(const 
 #pragma unroll
         for (int r = 0; r < 8; ++r) {
             if (r < world) {
-                const float4* source = reinterpret_cast<const float4*>(peers.region[rank] + kControlBytes
+                const float4* source = reinterpret_cast<const float4*>(peers.region[pull ? r : rank] + kControlBytes
                                                                        + (static_cast<int64_t>(slot) * world + r) * slot_bytes)
                                        + row * vectors + v;
                 part[r] = __ldcv(source);
@@ -264,7 +266,7 @@ void* b200_tp_slot(void* region, size_t slot_bytes, int32_t world, int32_t slot,
     return static_cast<char*>(region) + kControlBytes + (static_cast<size_t>(slot) * world + sender) * slot_bytes;
 }
 
-int b200_tp_reduce_shadow(void* const* regions, int32_t rank, int32_t world, int32_t slot, size_t slot_bytes, int64_t rows, int64_t width,
+int b200_tp_reduce_shadow(void* const* regions, int32_t rank, int32_t world, int32_t slot, size_t slot_bytes, int32_t pull, int64_t rows, int64_t width,
                           const void* norm_weight, int32_t norm_dtype, float* out, void* out_hi, void* out_lo, float* sumsq_out,
                           void* stream) {
     if (!regions || world < 1 || world > 8 || rank < 0 || rank >= world || slot < 0 || slot > 1 || rows <= 0 || width <= 0 || (width & 3)
@@ -285,7 +287,7 @@ int b200_tp_reduce_shadow(void* const* regions, int32_t rank, int32_t world, int
     return cuda_status(launch_dependent(tp_reduce_shadow_kernel, grid, dim3(kReduceThreads), 0, as_stream(stream), table,
                                         static_cast<int>(rank), static_cast<int>(world), static_cast<int>(slot), static_cast<int64_t>(slot_bytes),
                                         rows, width, norm_weight, static_cast<int>(norm_dtype), out, static_cast<__nv_bfloat16*>(out_hi),
-                                        static_cast<__nv_bfloat16*>(out_lo), sumsq_out, status),
+                                        static_cast<__nv_bfloat16*>(out_lo), sumsq_out, status, static_cast<int>(pull != 0)),
                        "tp_reduce_shadow_kernel launch");
 }
 

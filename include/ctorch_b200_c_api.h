@@ -229,6 +229,11 @@ DL_API dl_status dl_b200_tp_finalize(dl_device device);
  * the application) before any of them calls dl_b200_tp_finalize. */
 DL_API dl_status dl_b200_tp_symmetric_handle(dl_device device, size_t slot_bytes, void* handle64);
 DL_API dl_status dl_b200_tp_symmetric_open(dl_device device, const void* handles, int32_t world);
+/* How the partial sums of the output and down projections travel once the peer memory is mapped.  push = 0 (default): a
+ * projection writes its rows into its own region and the sum that follows loads the peers' rows over NVLink.  push != 0:
+ * the projection's epilogue stores its rows into every peer's region and the sum reads local memory only.  Every rank of a
+ * group must choose the same mode, before its first step.  The environment variable CTORCH_B200_TP_PUSH sets the default. */
+DL_API dl_status dl_b200_tp_set_push(dl_device device, int32_t push);
 DL_API dl_status dl_transformer_decoder_set_tensor_parallel(dl_module* decoder, int32_t rank, int32_t world);
 
 /* CUDA-event timing on the library's compute stream of a device (benchmarks must time on the launching

@@ -275,11 +275,12 @@ B200_API int b200_take_device_status(int32_t device, void* stream, int32_t* stat
  * expiry the device status word reads B200_DEVICE_TIMEOUT) for all ranks' signals, and writes out[rows, width] = sum over
  * senders in rank order of the slots of its OWN region (local loads only), the shadow planes of out * norm_weight and
  * per-row partial sums of squares ([b200_tp_reduce_parts(width)][rows], one partial per 1024 columns).  Callers alternate
- * slots 0 and 1 from call to call. */
+ * slots 0 and 1 from call to call.  pull != 0: the projections deposited their rows in their own region only (no
+ * y_copies) and the sum reads sender r's slot from rank r's region with peer loads instead. */
 B200_API int32_t b200_tp_reduce_parts(int64_t width);
 B200_API size_t b200_tp_region_bytes(size_t slot_bytes, int32_t world);
 B200_API void* b200_tp_slot(void* region, size_t slot_bytes, int32_t world, int32_t slot, int32_t sender);
-B200_API int b200_tp_reduce_shadow(void* const* regions, int32_t rank, int32_t world, int32_t slot, size_t slot_bytes, int64_t rows,
+B200_API int b200_tp_reduce_shadow(void* const* regions, int32_t rank, int32_t world, int32_t slot, size_t slot_bytes, int32_t pull, int64_t rows,
                                    int64_t width, const void* norm_weight, int32_t norm_dtype, float* out, void* out_hi, void* out_lo,
                                    float* sumsq_out, void* stream);
 

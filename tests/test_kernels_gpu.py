@@ -560,16 +560,18 @@ def test_peer_memory_sum_one_gpu():
     hi = torch.zeros((rows, width), dtype=torch.bfloat16, device="cuda")
     lo = torch.zeros_like(hi)
     sums = torch.zeros((l.b200_tp_reduce_parts(width), rows), device="cuda")
-    for world in (1, 2):
+    for world, pull in ((1, 0), (2, 0), (2, 1)):
         regions, table = _tp_regions(world, slot_bytes)
         for call, slot in ((1, 0), (2, 1), (3, 0)):
             parts = [rng.standard_normal((rows, width), dtype=np.float32) for _ in range(world)]
-            for r in range(world):   # every sender's rows lie in rank 0's own region: the sum reads local memory only
-                _slot_view(regions[0], slot_bytes, world, slot, r, rows, width).copy_(torch.from_numpy(parts[r]))
+            for r in range(world):
+                # pushed: every sender's rows lie in rank 0's own region (the sum reads local memory only); pulled: sender
+                # r's rows lie in rank r's region and the sum loads them from there
+                _slot_view(regions[r if pull else 0], slot_bytes, world, slot, r, rows, width).copy_(torch.from_numpy(parts[r]))
             if world == 2:   # rank 1 "arrived" for this call
                 regions[0][4:8].view(torch.int32)[0] = call
             torch.cuda.synchronize()
-            B.kcheck(l.b200_tp_reduce_shadow(table, 0, world, slot, slot_bytes, rows, width, nd.data_ptr(), B.BF16, out.data_ptr(),
+            B.kcheck(l.b200_tp_reduce_shadow(table, 0, world, slot, slot_bytes, pull, rows, width, nd.data_ptr(), B.BF16, out.data_ptr(),
                                              hi.data_ptr(), lo.data_ptr(), sums.data_ptr(), stream()))
             sync()
             status = C.c_int32()
@@ -598,13 +600,13 @@ def test_peer_memory_sum_gives_up_when_a_rank_never_arrives():
     sums = torch.zeros((1, rows), device="cuda")
     torch.cuda.synchronize()
     t0 = time.perf_counter()
-    B.kcheck(l.b200_tp_reduce_shadow(table, 0, 2, 0, slot_bytes, rows, width, None, 0, out.data_ptr(), hi.data_ptr(), lo.data_ptr(),
+    B.kcheck(l.b200_tp_reduce_shadow(table, 0, 2, 0, slot_bytes, 0, rows, width, None, 0, out.data_ptr(), hi.data_ptr(), lo.data_ptr(),
                                      sums.data_ptr(), stream()))
     sync()
     waited = time.perf_counter() - t0
     assert 1.5 < waited < 10.0
     t0 = time.perf_counter()
-    B.kcheck(l.b200_tp_reduce_shadow(table, 0, 2, 1, slot_bytes, rows, width, None, 0, out.data_ptr(), hi.data_ptr(), lo.data_ptr(),
+    B.kcheck(l.b200_tp_reduce_shadow(table, 0, 2, 1, slot_bytes, 1, rows, width, None, 0, out.data_ptr(), hi.data_ptr(), lo.data_ptr(),
                                      sums.data_ptr(), stream()))
     sync()
     assert time.perf_counter() - t0 < 1.0

@@ -29,7 +29,10 @@ def main():
     # 64 KiB slots: single-token steps (rows * 512 * 4 bytes <= 64 KiB) sum over NVLink peer memory, prefill chunks keep NCCL
     B.tensor_parallel_init(rank, world, local, peer_slot_bytes=64 << 10)
     report = {"rank": rank, "cases": []}
-    for batch, adapters in ((4, True), (32, False)):     # streaming kernel with adapters; tensor-core kernel without
+    # streaming kernel with adapters, partial sums pulled by the sum kernel; tensor-core kernel without adapters, partial sums
+    # pushed by the projections' epilogues
+    for batch, adapters, push in ((4, True, False), (32, False, True), (4, False, True)):
+        B.check(B.lib().dl_b200_tp_set_push(B.cuda(local), int(push)))
         spec = dict(vocab=1024, d_model=512, layers=3, heads=8, kv_heads=8 if world > 4 else 4, hidden=1024, dtype="bf16", batch=batch, prompt=40,
                     steps=6, context=64, tied=True, eps=1e-5, rope_base=10000.0)
         if adapters:
@@ -47,7 +50,7 @@ def main():
         tokens = sharded.generate(prompt, spec["steps"])          # graph replay with the all-reduce captured inside
         gathered = [None] * world
         dist.all_gather_object(gathered, tokens.tolist())
-        case = {"batch": batch, "prefill": rel(got_prefill, want_prefill), "step": rel(got_step, want_step),
+        case = {"batch": batch, "push": push, "prefill": rel(got_prefill, want_prefill), "step": rel(got_step, want_step),
                 "same_tokens_on_all_ranks": all(g == gathered[0] for g in gathered), "cache_length": sharded.cache_length()}
         if rank == 0:
             cpu = oracle.CpuDecoder(spec, weights, lora=lora)
