@@ -57,8 +57,9 @@ SplitPlan plan_splits(int64_t rows, int kv_heads, int max_length, int page_size)
     if (pps < 8) pps = 8;
     if (pps > 16) pps = 16;
     if (items * ((s.pages_total + pps - 1) / pps) > 32768) pps = s.pages_total;
-    // short contexts: one CTA per (row, KV head), no merge kernel
-    if (s.pages_total <= 16 || (s.pages_total <= 32 && items >= fill)) pps = s.pages_total;
+    // short contexts: one CTA per (row, KV head), no merge kernel - also up to 32 pages once the items alone give every SM a
+    // CTA (a decode step is a chain of dependent launches: the merge launch costs more than the shorter streams save)
+    if (s.pages_total <= 16 || (s.pages_total <= 32 && items >= 148)) pps = s.pages_total;
     if (pps > s.pages_total) pps = s.pages_total;
     s.pages_per_split = static_cast<int>(pps);
     s.num_splits = (s.pages_total + s.pages_per_split - 1) / s.pages_per_split;
