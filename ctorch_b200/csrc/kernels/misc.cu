@@ -261,17 +261,24 @@ __global__ void token_feedback_kernel(const int64_t* next, int64_t batch, int64_
     if (threadIdx.x == 0) *counter = step + 1;
 }
 
-// Merge of the per-tile candidates of the fused logits + argmax: warp w takes rows w, w + warps, ...; its lanes walk the
-// tiles, a butterfly leaves the row's choice, and lane 0 does the token bookkeeping of token_feedback_kernel.
+// Merge of the per-tile candidates of the fused logits + argmax.  Every CTA takes eight rows, one per warp: the lanes walk the
+// tiles, a butterfly leaves the row's choice, and lane 0 does the token bookkeeping of token_feedback_kernel for that row.
+// The CTA that finishes last (a ticket in device memory; the library issues these launches on one stream per device, so
+// one word serves) closes the step: cache lengths move on and the step counter is advanced - only then, because every
+// CTA reads the counter when it starts.
 struct LengthList { int32_t* lengths[64]; int32_t counts[64]; int32_t caches; };
-__global__ void __launch_bounds__(1024) argmax_finish_kernel(const float* best_value, const int32_t* best_index, int parts, int64_t rows,
-                                                             int64_t* next, int64_t* ids, int64_t* history, int64_t history_rows,
-                                                             int32_t* counter, const LengthList advance) {
+__device__ unsigned int argmax_finish_ticket;
+constexpr int kFinishWarps = 8;
+__global__ void __launch_bounds__(kFinishWarps * 32) argmax_finish_kernel(const float* best_value, const int32_t* best_index, int parts, int64_t rows,
+                                                                          int64_t* next, int64_t* ids, int64_t* history, int64_t history_rows,
+                                                                          int32_t* counter, const LengthList advance) {
+    __shared__ unsigned int last;
     grid_dependency_wait();
     grid_launch_dependents();
     const int32_t step = *counter;
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
-    for (int64_t row = warp; row < rows; row += warps) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int64_t row = static_cast<int64_t>(blockIdx.x) * kFinishWarps + warp;
+    if (row < rows) {
         Candidate best{-INFINITY, INT32_MAX};
         for (int t0 = 0; t0 < parts; t0 += 32 * 8) {   // eight independent loads per lane in flight
             Candidate batch[8];
@@ -296,11 +303,21 @@ __global__ void __launch_bounds__(1024) argmax_finish_kernel(const float* best_v
             if (history && step < history_rows) history[static_cast<int64_t>(step) * rows + row] = token;
         }
     }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        __threadfence();
+        last = atomicAdd(&argmax_finish_ticket, 1u) == gridDim.x - 1 ? 1u : 0u;
+    }
+    __syncthreads();
+    if (!last) return;
     // end of a step: the caches (one per layer) move on by the token every earlier kernel of the step appended and read
     for (int c = 0; c < advance.caches; ++c)
         for (int i = threadIdx.x; i < advance.counts[c]; i += blockDim.x) advance.lengths[c][i] += 1;
     __syncthreads();
-    if (threadIdx.x == 0) *counter = step + 1;
+    if (threadIdx.x == 0) {
+        argmax_finish_ticket = 0;
+        *counter = step + 1;
+    }
 }
 
 // One CTA per row.  Thread t owns the contiguous slice [t * chunk, (t + 1) * chunk) of the row, so per-thread f64 sums
@@ -413,8 +430,8 @@ int b200_argmax_finish(const float* best_value, const int32_t* best_index, int32
         advance.lengths[i] = caches[i]->lengths;
         advance.counts[i] = caches[i]->sequences;
     }
-    const unsigned threads = rows >= 32 ? 1024 : static_cast<unsigned>(rows) * 32;
-    return cuda_status(launch_dependent(b200::argmax_finish_kernel, dim3(1), dim3(threads), 0, as_stream(stream), best_value, best_index,
+    const unsigned ctas = static_cast<unsigned>((rows + b200::kFinishWarps - 1) / b200::kFinishWarps);
+    return cuda_status(launch_dependent(b200::argmax_finish_kernel, dim3(ctas), dim3(b200::kFinishWarps * 32), 0, as_stream(stream), best_value, best_index,
                                         static_cast<int>(parts), rows, next, ids, history, history_rows, counter, advance),
                        "argmax_finish_kernel launch");
 }
