@@ -362,7 +362,9 @@ def measure_decoder(args, name, spec, weights, rank, world, local, dist) -> dict
         ms = step_ms * shares[kind]
         achieved = bytes_ / (ms / 1000.0) / 1e9 if ms > 0 else None
         if kind == "linear":
-            kernel = ("linear_decode_kernel" if batch > 16 or spec["d_model"] > 2048 else "linear_stream_kernel") if spec["dtype"] == "bf16" else "linear_small_kernel"
+            # the family the library runs the largest projection (gate/up) of this batch on
+            kernel = (B.lib().b200_linear_shadow_kernel(batch, spec["d_model"], 2 * spec["hidden"]).decode()
+                      if spec["dtype"] == "bf16" else "linear_small_kernel")
             kernel += " (the %d projection launches of one step: weights streamed once)" % (profile["launches"] - spec["layers"] - 2)
         else:
             kernel = ("attention_mma_kernel" if spec["dtype"] == "bf16" else "attention_generic_kernel") + " (%d launches of one step: K and V streamed once)" % spec["layers"]

@@ -44,17 +44,35 @@ struct LinearParams {
     int copies;
 };
 
-// The result pair of (row, feature0) to every extra destination (see LinearParams::y_copy).
-__device__ __forceinline__ void store_copies(const LinearParams& p, int64_t at, float a, float b, bool second) {
-    for (int c = 0; c < p.copies; ++c) {
-        float* target = p.y_copy[c] + at;
-        if (second && (reinterpret_cast<uintptr_t>(target) & 7) == 0) {
-            *reinterpret_cast<float2*>(target) = make_float2(a, b);
-        } else {
-            target[0] = a;
-            if (second) target[1] = b;
-        }
+// The result pair of (row, feature0) to every extra destination (see LinearParams::y_copy).  The destinations are named
+// one by one: a loop over the array would index the kernel's parameters with a register, which costs a copy of the whole
+// parameter block in local memory.
+__device__ __forceinline__ void store_copy_pair(float* target, float a, float b, bool second) {
+    if (second && (reinterpret_cast<uintptr_t>(target) & 7) == 0) {
+        *reinterpret_cast<float2*>(target) = make_float2(a, b);
+    } else {
+        target[0] = a;
+        if (second) target[1] = b;
     }
+}
+__device__ __forceinline__ void store_copies(const LinearParams& p, int64_t at, float a, float b, bool second) {
+    if (p.copies > 0) store_copy_pair(p.y_copy[0] + at, a, b, second);
+    if (p.copies > 1) store_copy_pair(p.y_copy[1] + at, a, b, second);
+    if (p.copies > 2) store_copy_pair(p.y_copy[2] + at, a, b, second);
+    if (p.copies > 3) store_copy_pair(p.y_copy[3] + at, a, b, second);
+    if (p.copies > 4) store_copy_pair(p.y_copy[4] + at, a, b, second);
+    if (p.copies > 5) store_copy_pair(p.y_copy[5] + at, a, b, second);
+    if (p.copies > 6) store_copy_pair(p.y_copy[6] + at, a, b, second);
+}
+// The same for four adjacent features on a 16-byte boundary.
+__device__ __forceinline__ void store_copies(const LinearParams& p, int64_t at, const float4& v) {
+    if (p.copies > 0) *reinterpret_cast<float4*>(p.y_copy[0] + at) = v;
+    if (p.copies > 1) *reinterpret_cast<float4*>(p.y_copy[1] + at) = v;
+    if (p.copies > 2) *reinterpret_cast<float4*>(p.y_copy[2] + at) = v;
+    if (p.copies > 3) *reinterpret_cast<float4*>(p.y_copy[3] + at) = v;
+    if (p.copies > 4) *reinterpret_cast<float4*>(p.y_copy[4] + at) = v;
+    if (p.copies > 5) *reinterpret_cast<float4*>(p.y_copy[5] + at) = v;
+    if (p.copies > 6) *reinterpret_cast<float4*>(p.y_copy[6] + at) = v;
 }
 
 // (value, index) ordering of the reference's argmax (src/kernels/cpu/reduction.cpp:128-151): a NaN beats every number,

@@ -38,7 +38,7 @@ constexpr int kThreads = 384;             // 12 warps: producer, tensor-core iss
 constexpr int kMaxStages = 8;
 constexpr int kControlBytes = 3584;       // barriers, TMEM slot, flags, row scales, row places (position and cache page)
 constexpr int kTileStride = kFeatures + 4;
-constexpr int kMaxRows = 128;             // above, the prefill kernel (tokens as the M side) is faster inside a decode step
+constexpr int kMaxRows = 256;             // two token tiles of 128; above, the prefill kernel (tokens as the M side) takes over
 constexpr int kHalfSmem = 113 * 1024;     // two CTAs of this size share an SM
 
 struct DecodeParams {
@@ -54,10 +54,10 @@ struct DecodeParams {
     int epilogue;       // B200_EPI_*: one kernel serves every epilogue, so that the launches of a step share their code
 };
 
-template <int TILES, bool LO>
+template <int TILES, bool LO, bool QUADS>
 __global__ void __launch_bounds__(kThreads, 1) linear_decode_kernel(const __grid_constant__ CUtensorMap map_hi,
                                                                     const __grid_constant__ CUtensorMap map_lo,
-                                                                    const __grid_constant__ CUtensorMap map_w, const DecodeParams dp) {
+                                                                    const __grid_constant__ CUtensorMap map_w, const __grid_constant__ DecodeParams dp) {
     const LinearParams& p = dp.base;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
@@ -67,7 +67,7 @@ __global__ void __launch_bounds__(kThreads, 1) linear_decode_kernel(const __grid
     uint64_t* accumulator_ready = empty + kMaxStages;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(control + 160);
     volatile int* tile_ready = reinterpret_cast<volatile int*>(control + 192);   // one flag per epilogue warp
-    float* row_scale = reinterpret_cast<float*>(control + 256);                  // kMaxRows floats
+    float* row_scale = reinterpret_cast<float*>(control + 256);                  // one per row of the token tile
     int2* row_place = reinterpret_cast<int2*>(control + 1536);                   // q|k|v: position and cache page of every row
 
     // The warp index goes through a shuffle so that the compiler knows it to be warp-uniform: the role branches below are
@@ -218,11 +218,14 @@ __global__ void __launch_bounds__(kThreads, 1) linear_decode_kernel(const __grid
                 row_place[row] = qkv_row_place(p, row0 + row);
             }
         }
-        ready = mbar_wait_relaxed(accumulator_ready, 0);
-        if (!ready && lane == 0) atomicExch(dp.status, B200_DEVICE_TIMEOUT);
-        tc_fence_after_sync();
-        if (lane == 0) tile_ready[quarter] = ready ? 1 : 0;
     }
+    // Every warp takes part in draining the accumulators: warp w may read the TMEM lanes 32 * (w % 4) .. + 31, so three
+    // warps share each lane quarter and divide the token columns among themselves.
+    ready = mbar_wait_relaxed(accumulator_ready, 0);
+    if (!ready && lane == 0) atomicExch(dp.status, B200_DEVICE_TIMEOUT);
+    tc_fence_after_sync();
+    if (lane == 0) tile_ready[warp] = ready ? 1 : 0;
+    const int third = warp >> 2;
     const int rows_each = (dp.token_tile + split - 1) / split;   // the same for every token tile, so that the slab sizes agree
     const int first = min(rows_here, part * rows_each), last = min(rows_here, first + rows_each);
     const uint32_t slab_bytes = static_cast<uint32_t>(rows_each * kTileStride * 4);
@@ -233,15 +236,14 @@ __global__ void __launch_bounds__(kThreads, 1) linear_decode_kernel(const __grid
     const uint32_t slabs = smem_u32(smem);
 
     auto push_tile = [&](int t, uint32_t set_base) {
-        if (!(finisher && ready)) return;
+        if (!ready) return;
         const uint32_t source = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(t * dp.n_alloc);
         // my slab inside the owner's set, at this thread's feature column
         const uint32_t mine = set_base + static_cast<uint32_t>(part) * slab_bytes + static_cast<uint32_t>(quarter * 32 + lane) * 4;
-        int owner = 0, band_row = 0;
         if (split == 1) {   // no peers: plain stores into this CTA's tile
             float* column = reinterpret_cast<float*>(smem + (mine - slabs));
 #pragma unroll 1
-            for (int c = 0; c < dp.n_pad; c += 32) {
+            for (int c = third * 32; c < dp.n_pad; c += 96) {
                 uint32_t r[32];
                 tmem_load_32(source + static_cast<uint32_t>(c), r);
 #pragma unroll
@@ -250,9 +252,10 @@ __global__ void __launch_bounds__(kThreads, 1) linear_decode_kernel(const __grid
             }
             return;
         }
-        uint32_t target = map_peer_shared(mine, 0u);
 #pragma unroll 1
-        for (int c = 0; c < dp.n_pad; c += 32) {
+        for (int c = third * 32; c < dp.n_pad; c += 96) {
+            int owner = c / rows_each, band_row = c - owner * rows_each;
+            uint32_t target = map_peer_shared(mine, static_cast<uint32_t>(owner < split ? owner : 0));
             uint32_t r[32];
             tmem_load_32(source + static_cast<uint32_t>(c), r);
 #pragma unroll
@@ -273,15 +276,16 @@ __global__ void __launch_bounds__(kThreads, 1) linear_decode_kernel(const __grid
 #pragma unroll
         for (int z = 0; z < 8; ++z)   // band-relative storage addressed by tile row: shift the base by the band's first row
             partial[z] = set_base + static_cast<uint32_t>(z < split ? z : 0) * slab_bytes - static_cast<uint32_t>(first * kTileStride * 4);
-        const bool whole = tile_ready[0] && tile_ready[1] && tile_ready[2] && tile_ready[3];
+        bool whole = true;
+        for (int w = 0; w < kThreads / 32; ++w) whole = whole && tile_ready[w] != 0;
         const float* local = reinterpret_cast<const float*>(smem + (set_base - slabs)) - first * kTileStride;
         const int n0 = (tile0 + t) * kFeatures, workers = kThreads / 32;
         switch (dp.epilogue) {
-        case B200_EPI_STORE: finish_rows<B200_EPI_STORE, kFeatures>(p, local, partial, split, row_scale, row0, n0, tile0 + t, first, last, warp, workers, lane, whole); break;
-        case B200_EPI_RESIDUAL: finish_rows<B200_EPI_RESIDUAL, kFeatures>(p, local, partial, split, row_scale, row0, n0, tile0 + t, first, last, warp, workers, lane, whole); break;
-        case B200_EPI_SWIGLU: finish_rows<B200_EPI_SWIGLU, kFeatures>(p, local, partial, split, row_scale, row0, n0, tile0 + t, first, last, warp, workers, lane, whole); break;
-        case B200_EPI_QKV: finish_rows<B200_EPI_QKV, kFeatures>(p, local, partial, split, row_scale, row0, n0, tile0 + t, first, last, warp, workers, lane, whole, row_place); break;
-        default: finish_rows<B200_EPI_ARGMAX, kFeatures>(p, local, partial, split, row_scale, row0, n0, tile0 + t, first, last, warp, workers, lane, whole); break;
+        case B200_EPI_STORE: finish_rows<B200_EPI_STORE, kFeatures, QUADS ? 1 : 2>(p, local, partial, split, row_scale, row0, n0, tile0 + t, first, last, warp, workers, lane, whole); break;
+        case B200_EPI_RESIDUAL: finish_rows<B200_EPI_RESIDUAL, kFeatures, QUADS ? 1 : 2>(p, local, partial, split, row_scale, row0, n0, tile0 + t, first, last, warp, workers, lane, whole); break;
+        case B200_EPI_SWIGLU: finish_rows<B200_EPI_SWIGLU, kFeatures, QUADS ? 1 : 2>(p, local, partial, split, row_scale, row0, n0, tile0 + t, first, last, warp, workers, lane, whole); break;
+        case B200_EPI_QKV: finish_rows<B200_EPI_QKV, kFeatures, QUADS ? 1 : 2>(p, local, partial, split, row_scale, row0, n0, tile0 + t, first, last, warp, workers, lane, whole, row_place); break;
+        default: finish_rows<B200_EPI_ARGMAX, kFeatures, QUADS ? 1 : 2>(p, local, partial, split, row_scale, row0, n0, tile0 + t, first, last, warp, workers, lane, whole); break;
         }
     };
     auto barrier_all = [&]() {
@@ -293,7 +297,6 @@ __global__ void __launch_bounds__(kThreads, 1) linear_decode_kernel(const __grid
     if (split > 1) {
         // The slabs lie in the operand ring: a peer may only write into this CTA once the ring is drained, which is when
         // the accumulators are complete.  Every warp waits for that, then the cluster meets once before the pushes.
-        if (!finisher && !mbar_wait_relaxed(accumulator_ready, 0) && lane == 0) atomicExch(dp.status, B200_DEVICE_TIMEOUT);
         __syncwarp();
         cluster_sync_all();
     }
@@ -349,7 +352,7 @@ int cluster_capacity(int split, bool two_per_sm, int sms) {
     std::lock_guard<std::mutex> lock(mutex);
     int& slot = cached[two_per_sm ? 1 : 0][split];
     if (slot) return slot;
-    auto kernel = linear_decode_kernel<1, true>;
+    auto kernel = linear_decode_kernel<1, true, true>;
     const int smem = two_per_sm ? kHalfSmem : 232448;
     int clusters = 0;
     cudaLaunchConfig_t config{};
@@ -443,10 +446,10 @@ bool linear_decode_takes(int rows) { return rows >= 1 && rows <= kMaxRows; }
 
 namespace {
 
-template <int TILES, bool LO>
+template <int TILES, bool LO, bool QUADS>
 int launch_decode_as(const CUtensorMap& hi, const CUtensorMap& lo, const CUtensorMap& w, const DecodeParams& dp, const DecodeShape& shape,
                      cudaStream_t stream) {
-    auto kernel = linear_decode_kernel<TILES, LO>;
+    auto kernel = linear_decode_kernel<TILES, LO, QUADS>;
     B200_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 232448));
     const dim3 grid(static_cast<unsigned>(shape.token_tiles), static_cast<unsigned>(shape.ctas), static_cast<unsigned>(shape.split));
     if (shape.split == 1)
@@ -457,13 +460,30 @@ int launch_decode_as(const CUtensorMap& hi, const CUtensorMap& lo, const CUtenso
                        "linear_decode_kernel cluster launch");
 }
 
+template <int TILES, bool LO>
+int launch_decode_form(const CUtensorMap& hi, const CUtensorMap& lo, const CUtensorMap& w, const DecodeParams& dp, const DecodeShape& shape,
+                       bool quads, cudaStream_t stream) {
+    return quads ? launch_decode_as<TILES, LO, true>(hi, lo, w, dp, shape, stream) : launch_decode_as<TILES, LO, false>(hi, lo, w, dp, shape, stream);
+}
+
+// Whether the epilogue may address its matrices four features at a time (width and alignment, see rows_take_quads).
+bool epilogue_takes_quads(const LinearParams& p, int epilogue) {
+    switch (epilogue) {
+    case B200_EPI_STORE: return rows_take_quads<B200_EPI_STORE>(p);
+    case B200_EPI_RESIDUAL: return rows_take_quads<B200_EPI_RESIDUAL>(p);
+    case B200_EPI_SWIGLU: return rows_take_quads<B200_EPI_SWIGLU>(p);
+    case B200_EPI_QKV: return rows_take_quads<B200_EPI_QKV>(p);
+    default: return rows_take_quads<B200_EPI_ARGMAX>(p);
+    }
+}
+
 int launch_decode(const CUtensorMap& hi, const CUtensorMap& lo, const CUtensorMap& w, const DecodeParams& dp, const DecodeShape& shape,
                   cudaStream_t stream) {
-    const bool two = dp.base.x_lo != nullptr;
+    const bool two = dp.base.x_lo != nullptr, quads = epilogue_takes_quads(dp.base, dp.epilogue);
     switch (shape.tiles) {
-    case 1: return two ? launch_decode_as<1, true>(hi, lo, w, dp, shape, stream) : launch_decode_as<1, false>(hi, lo, w, dp, shape, stream);
-    case 2: return two ? launch_decode_as<2, true>(hi, lo, w, dp, shape, stream) : launch_decode_as<2, false>(hi, lo, w, dp, shape, stream);
-    case 4: return two ? launch_decode_as<4, true>(hi, lo, w, dp, shape, stream) : launch_decode_as<4, false>(hi, lo, w, dp, shape, stream);
+    case 1: return two ? launch_decode_form<1, true>(hi, lo, w, dp, shape, quads, stream) : launch_decode_form<1, false>(hi, lo, w, dp, shape, quads, stream);
+    case 2: return two ? launch_decode_form<2, true>(hi, lo, w, dp, shape, quads, stream) : launch_decode_form<2, false>(hi, lo, w, dp, shape, quads, stream);
+    case 4: return two ? launch_decode_form<4, true>(hi, lo, w, dp, shape, quads, stream) : launch_decode_form<4, false>(hi, lo, w, dp, shape, quads, stream);
     }
     return B200_UNSUPPORTED;
 }

@@ -71,15 +71,320 @@ __device__ __forceinline__ void finish_pair(const LinearParams& p, int row, int 
     }
 }
 
+// Whether the vector form applies to this call: every matrix the epilogue touches is addressed in 16-byte (f32) or
+// 8-byte (bf16 shadow) units per lane.  The greedy-choice epilogue stores nothing and always qualifies.
+template <int EPI>
+__host__ __device__ __forceinline__ bool rows_take_quads(const LinearParams& p) {
+    if constexpr (EPI == B200_EPI_ARGMAX) return true;
+    if (p.out & 3) return false;
+    uintptr_t bits = 0;
+    if constexpr (EPI == B200_EPI_STORE || EPI == B200_EPI_RESIDUAL) {
+        bits |= reinterpret_cast<uintptr_t>(p.y);
+        if (p.copies > 0) bits |= reinterpret_cast<uintptr_t>(p.y_copy[0]);
+        if (p.copies > 1) bits |= reinterpret_cast<uintptr_t>(p.y_copy[1]);
+        if (p.copies > 2) bits |= reinterpret_cast<uintptr_t>(p.y_copy[2]);
+        if (p.copies > 3) bits |= reinterpret_cast<uintptr_t>(p.y_copy[3]);
+        if (p.copies > 4) bits |= reinterpret_cast<uintptr_t>(p.y_copy[4]);
+        if (p.copies > 5) bits |= reinterpret_cast<uintptr_t>(p.y_copy[5]);
+        if (p.copies > 6) bits |= reinterpret_cast<uintptr_t>(p.y_copy[6]);
+    }
+    if constexpr (EPI == B200_EPI_RESIDUAL) {
+        bits |= reinterpret_cast<uintptr_t>(p.residual) | (reinterpret_cast<uintptr_t>(p.out_hi) << 1) | (reinterpret_cast<uintptr_t>(p.out_lo) << 1)
+              | (p.out_norm_dtype == B200_BF16 ? reinterpret_cast<uintptr_t>(p.out_norm_weight) << 1 : reinterpret_cast<uintptr_t>(p.out_norm_weight));
+    }
+    if constexpr (EPI == B200_EPI_SWIGLU)
+        bits |= (reinterpret_cast<uintptr_t>(p.y) << 1) | (reinterpret_cast<uintptr_t>(p.out_hi) << 2) | (reinterpret_cast<uintptr_t>(p.out_lo) << 2);
+    if constexpr (EPI == B200_EPI_QKV) {
+        if ((p.heads * p.head_dim) & 3 || (p.kv_heads * p.head_dim) & 3) return false;   // a quad never straddles q | k | v
+    }
+    return (bits & 15) == 0;
+}
+
+__device__ __forceinline__ float4 load_cluster_float4(uint32_t cluster_address) {
+    float4 value;
+    asm("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(value.x), "=f"(value.y), "=f"(value.z), "=f"(value.w) : "r"(cluster_address));
+    return value;
+}
+
+// Residual values of kBatch rows (rows past `last` repeat the last one), four features per lane and pass.
+template <int EPI, int kBatch, int kPasses>
+__device__ __forceinline__ void fetch_residual_quads(const LinearParams& p, int m0, int n0, int last, int lane, int base,
+                                                     float4 (&into)[kBatch][kPasses]) {
+#pragma unroll
+    for (int r = 0; r < kBatch; ++r) {
+        const int row = m0 + min(base + r, last - 1);
+#pragma unroll
+        for (int pass = 0; pass < kPasses; ++pass) {
+            into[r][pass] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            if constexpr (EPI == B200_EPI_RESIDUAL) {
+                const int feature0 = n0 + pass * 128 + lane * 4;
+                if (feature0 < p.out) into[r][pass] = *reinterpret_cast<const float4*>(p.residual + static_cast<int64_t>(row) * p.out + feature0);
+            }
+        }
+    }
+}
+
+// Vector form of finish_rows_pairs below: a lane holds four adjacent features, so a 128-feature row is one instruction
+// per access.  A batch of kBatch rows is worked in three straight-line phases - fetch (accumulators, residual values),
+// arithmetic, stores - with no branch between the rows, so that the rows' dependent chains (shared-memory load, scale,
+// exponential, reciprocal, roundings) overlap: with twelve warps on an SM nothing else hides those latencies.  Rows past
+// the end repeat the last live row (the same values go to the same places twice) instead of being branched around.
+template <int EPI, int kTileN>
+__device__ __forceinline__ void finish_rows_quads(const LinearParams& p, const float* tile, const uint32_t (&peer_tile)[8], int split,
+                                                  const float* row_scale, int m0, int n0, int feature_tile, int first, int last, int worker,
+                                                  int workers, int lane, bool ready, const int2* row_place) {
+    constexpr int kTileStride = kTileN + 4;
+    constexpr int kBatch = 4, kPasses = kTileN / 128;
+    if (last > p.rows - m0) last = p.rows - m0;
+    if (first >= last) return;
+    float4 norm[kPasses];
+    bool live[kPasses];   // this lane's four features exist and the accumulators are valid
+#pragma unroll
+    for (int pass = 0; pass < kPasses; ++pass) {
+        const int feature0 = n0 + pass * 128 + lane * 4;
+        live[pass] = ready && feature0 < p.out;
+        norm[pass] = make_float4(1.0f, 1.0f, 1.0f, 1.0f);
+        if constexpr (EPI == B200_EPI_RESIDUAL) {
+            if (p.out_hi && p.out_norm_weight && feature0 < p.out) {
+                if (p.out_norm_dtype == B200_BF16) {
+                    const uint2 w = __ldg(reinterpret_cast<const uint2*>(static_cast<const __nv_bfloat16*>(p.out_norm_weight) + feature0));
+                    norm[pass] = make_float4(__uint_as_float(w.x << 16), __uint_as_float(w.x & 0xffff0000u), __uint_as_float(w.y << 16),
+                                             __uint_as_float(w.y & 0xffff0000u));
+                } else {
+                    norm[pass] = __ldg(reinterpret_cast<const float4*>(static_cast<const float*>(p.out_norm_weight) + feature0));
+                }
+            }
+        }
+    }
+    const float4 zero = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    if constexpr (EPI == B200_EPI_QKV) {
+        // q | k | v: adapter delta, rotation and the cache append per feature pair (linear_epilogue); the body is large,
+        // so the rows are walked one at a time
+#pragma unroll 1
+        for (int tile_row = first + worker; tile_row < last; tile_row += workers) {
+            const float scale = row_scale[tile_row];
+            const int2* place = row_place ? row_place + tile_row : nullptr;
+#pragma unroll
+            for (int pass = 0; pass < kPasses; ++pass) {
+                if (!live[pass]) continue;
+                const int c = pass * 128 + lane * 4;
+                float4 v;
+                if (split == 1) {
+                    v = *reinterpret_cast<const float4*>(tile + tile_row * kTileStride + c);
+                } else {
+                    const uint32_t offset = static_cast<uint32_t>(tile_row * kTileStride + c) * 4;
+                    v = load_cluster_float4(peer_tile[0] + offset);
+#pragma unroll
+                    for (int z = 1; z < 8; ++z) {
+                        if (z < split) {
+                            const float4 w = load_cluster_float4(peer_tile[z] + offset);
+                            v.x += w.x; v.y += w.y; v.z += w.z; v.w += w.w;
+                        }
+                    }
+                }
+#pragma unroll 1
+                for (int half = 0; half < 2; ++half) {
+                    float a = (half ? v.z : v.x) * scale, b = (half ? v.w : v.y) * scale;
+                    linear_epilogue<EPI>(p, m0 + tile_row, n0 + c + 2 * half, a, b, place);
+                }
+            }
+        }
+        return;
+    }
+    float4 carried[kBatch][kPasses];
+    int base = first + worker * kBatch;
+    if (base < last) fetch_residual_quads<EPI, kBatch, kPasses>(p, m0, n0, last, lane, base, carried);
+    for (; base < last; base += workers * kBatch) {
+        float4 value[kBatch][kPasses], ahead[kBatch][kPasses];
+        int rows[kBatch];
+        float scale[kBatch];
+        // ---- fetch ----
+#pragma unroll
+        for (int r = 0; r < kBatch; ++r) {
+            const int tile_row = min(base + r, last - 1);
+            rows[r] = tile_row;
+            scale[r] = row_scale[tile_row];
+#pragma unroll
+            for (int pass = 0; pass < kPasses; ++pass) {
+                const int c = pass * 128 + lane * 4;
+                if (split == 1) {
+                    value[r][pass] = *reinterpret_cast<const float4*>(tile + tile_row * kTileStride + c);
+                } else {
+                    const uint32_t offset = static_cast<uint32_t>(tile_row * kTileStride + c) * 4;
+                    float4 v[8];
+#pragma unroll
+                    for (int z = 0; z < 8; ++z) v[z] = z < split ? load_cluster_float4(peer_tile[z] + offset) : zero;
+                    float4 sum = v[0];
+#pragma unroll
+                    for (int z = 1; z < 8; ++z) { sum.x += v[z].x; sum.y += v[z].y; sum.z += v[z].z; sum.w += v[z].w; }
+                    value[r][pass] = sum;
+                }
+            }
+        }
+        if constexpr (EPI == B200_EPI_RESIDUAL) {
+            if (base + workers * kBatch < last) fetch_residual_quads<EPI, kBatch, kPasses>(p, m0, n0, last, lane, base + workers * kBatch, ahead);
+        }
+        // ---- arithmetic (no branches) and stores ----
+        if constexpr (EPI == B200_EPI_RESIDUAL) {
+            float4 sum[kBatch][kPasses];
+            uint2 hi[kBatch][kPasses], lo[kBatch][kPasses];
+            float squares[kBatch];
+#pragma unroll
+            for (int r = 0; r < kBatch; ++r) {
+                squares[r] = 0.0f;
+#pragma unroll
+                for (int pass = 0; pass < kPasses; ++pass) {
+                    const float4 v = value[r][pass], c = carried[r][pass];
+                    float4 t = make_float4(__fadd_rn(c.x, v.x * scale[r]), __fadd_rn(c.y, v.y * scale[r]), __fadd_rn(c.z, v.z * scale[r]),
+                                           __fadd_rn(c.w, v.w * scale[r]));
+                    if (!live[pass]) t = zero;
+                    sum[r][pass] = t;
+                    squares[r] += t.x * t.x + t.y * t.y;
+                    squares[r] += t.z * t.z + t.w * t.w;
+                    const float a = __fmul_rn(t.x, norm[pass].x), b = __fmul_rn(t.y, norm[pass].y), c2 = __fmul_rn(t.z, norm[pass].z),
+                                d = __fmul_rn(t.w, norm[pass].w);
+                    const __nv_bfloat162 hi0 = __floats2bfloat162_rn(a, b), hi1 = __floats2bfloat162_rn(c2, d);
+                    const __nv_bfloat162 lo0 = __floats2bfloat162_rn(a - __low2float(hi0), b - __high2float(hi0));
+                    const __nv_bfloat162 lo1 = __floats2bfloat162_rn(c2 - __low2float(hi1), d - __high2float(hi1));
+                    hi[r][pass] = make_uint2(*reinterpret_cast<const uint32_t*>(&hi0), *reinterpret_cast<const uint32_t*>(&hi1));
+                    lo[r][pass] = make_uint2(*reinterpret_cast<const uint32_t*>(&lo0), *reinterpret_cast<const uint32_t*>(&lo1));
+                }
+            }
+            if (p.sumsq_out) {
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) {
+#pragma unroll
+                    for (int r = 0; r < kBatch; ++r) squares[r] += __shfl_xor_sync(0xffffffffu, squares[r], o);
+                }
+                if (lane < kBatch) {
+                    float mine = squares[0];
+#pragma unroll
+                    for (int r = 1; r < kBatch; ++r) mine = lane == r ? squares[r] : mine;
+                    int row_of_lane = rows[0];
+#pragma unroll
+                    for (int r = 1; r < kBatch; ++r) row_of_lane = lane == r ? rows[r] : row_of_lane;
+                    p.sumsq_out[static_cast<int64_t>(feature_tile) * p.rows + m0 + row_of_lane] = mine;
+                }
+            }
+#pragma unroll
+            for (int r = 0; r < kBatch; ++r) {
+#pragma unroll
+                for (int pass = 0; pass < kPasses; ++pass) {
+                    if (!live[pass]) continue;
+                    const int64_t at = static_cast<int64_t>(m0 + rows[r]) * p.out + n0 + pass * 128 + lane * 4;
+                    *reinterpret_cast<float4*>(p.y + at) = sum[r][pass];
+                    if (p.out_hi) {
+                        *reinterpret_cast<uint2*>(p.out_hi + at) = hi[r][pass];
+                        *reinterpret_cast<uint2*>(p.out_lo + at) = lo[r][pass];
+                    }
+                }
+            }
+            if (p.copies > 0) {
+#pragma unroll
+                for (int r = 0; r < kBatch; ++r) {
+#pragma unroll
+                    for (int pass = 0; pass < kPasses; ++pass) {
+                        if (!live[pass]) continue;
+                        const int64_t at = static_cast<int64_t>(m0 + rows[r]) * p.out + n0 + pass * 128 + lane * 4;
+                        store_copies(p, at, sum[r][pass]);
+                    }
+                }
+            }
+#pragma unroll
+            for (int r = 0; r < kBatch; ++r)
+#pragma unroll
+                for (int pass = 0; pass < kPasses; ++pass) carried[r][pass] = ahead[r][pass];
+        } else if constexpr (EPI == B200_EPI_SWIGLU) {
+            float2 result[kBatch][kPasses];
+            uint32_t hi[kBatch][kPasses], lo[kBatch][kPasses];
+#pragma unroll
+            for (int r = 0; r < kBatch; ++r) {
+#pragma unroll
+                for (int pass = 0; pass < kPasses; ++pass) {
+                    // (gate_j, up_j, gate_j+1, up_j+1) of the interleaved weight rows; the shadow input makes this a bf16
+                    // model, whose SiLU takes the hardware exponential (see silu_fast)
+                    const float4 v = value[r][pass];
+                    const float a = __fmul_rn(silu_fast(v.x * scale[r]), v.y * scale[r]);
+                    const float b = __fmul_rn(silu_fast(v.z * scale[r]), v.w * scale[r]);
+                    result[r][pass] = make_float2(a, b);
+                    const __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+                    const __nv_bfloat162 l = __floats2bfloat162_rn(a - __low2float(h), b - __high2float(h));
+                    hi[r][pass] = *reinterpret_cast<const uint32_t*>(&h);
+                    lo[r][pass] = *reinterpret_cast<const uint32_t*>(&l);
+                }
+            }
+#pragma unroll
+            for (int r = 0; r < kBatch; ++r) {
+#pragma unroll
+                for (int pass = 0; pass < kPasses; ++pass) {
+                    if (!live[pass]) continue;
+                    const int64_t at = static_cast<int64_t>(m0 + rows[r]) * (p.out >> 1) + ((n0 + pass * 128 + lane * 4) >> 1);
+                    if (p.y) *reinterpret_cast<float2*>(p.y + at) = result[r][pass];
+                    if (p.out_hi) {
+                        *reinterpret_cast<uint32_t*>(p.out_hi + at) = hi[r][pass];
+                        *reinterpret_cast<uint32_t*>(p.out_lo + at) = lo[r][pass];
+                    }
+                }
+            }
+        } else if constexpr (EPI == B200_EPI_STORE) {
+#pragma unroll
+            for (int r = 0; r < kBatch; ++r) {
+#pragma unroll
+                for (int pass = 0; pass < kPasses; ++pass) {
+                    if (!live[pass]) continue;
+                    const float4 v = value[r][pass];
+                    const float4 t = make_float4(v.x * scale[r], v.y * scale[r], v.z * scale[r], v.w * scale[r]);
+                    const int64_t at = static_cast<int64_t>(m0 + rows[r]) * p.out + n0 + pass * 128 + lane * 4;
+                    *reinterpret_cast<float4*>(p.y + at) = t;
+                    store_copies(p, at, t);
+                }
+            }
+        } else if constexpr (EPI == B200_EPI_ARGMAX) {
+            Candidate best[kBatch];
+#pragma unroll
+            for (int r = 0; r < kBatch; ++r) {
+                best[r] = Candidate{-INFINITY, INT32_MAX};
+#pragma unroll
+                for (int pass = 0; pass < kPasses; ++pass) {
+                    const int feature0 = n0 + pass * 128 + lane * 4;
+                    const float4 v = value[r][pass];
+                    const Candidate low = pair_candidate(feature0, v.x * scale[r], v.y * scale[r], p.out);
+                    const Candidate high = pair_candidate(feature0 + 2, v.z * scale[r], v.w * scale[r], p.out);
+                    if (live[pass] && preferred(low, best[r])) best[r] = low;
+                    if (live[pass] && feature0 + 2 < p.out && preferred(high, best[r])) best[r] = high;
+                }
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+#pragma unroll
+                for (int r = 0; r < kBatch; ++r) {
+                    const Candidate other{__shfl_xor_sync(0xffffffffu, best[r].value, o), __shfl_xor_sync(0xffffffffu, best[r].index, o)};
+                    if (preferred(other, best[r])) best[r] = other;
+                }
+            }
+            if (lane < kBatch) {
+                Candidate mine = best[0];
+                int row_of_lane = rows[0];
+#pragma unroll
+                for (int r = 1; r < kBatch; ++r) {
+                    if (lane == r) { mine = best[r]; row_of_lane = rows[r]; }
+                }
+                p.best_value[static_cast<int64_t>(feature_tile) * p.rows + m0 + row_of_lane] = mine.value;
+                p.best_index[static_cast<int64_t>(feature_tile) * p.rows + m0 + row_of_lane] = mine.index;
+            }
+        }
+    }
+}
+
 // Finishes the rows [first, last) of a tile held row-major in shared memory (`tile`, or the sum over the cluster's
 // `split` partial tiles `peer_tile[z]`).  Warp `worker` of `workers` takes kBatch consecutive rows per iteration: first
 // every value the rows need is requested (accumulators from shared memory or from the peers, residual pairs from global
 // memory), then the rows are finished, so the memory round trips of the rows overlap instead of queueing behind each
 // other.  Lanes run across the feature pairs: every global access is coalesced; per-row reductions are butterflies.
 template <int EPI, int kTileN>
-__device__ __forceinline__ void finish_rows(const LinearParams& p, const float* tile, const uint32_t (&peer_tile)[8], int split,
+__device__ __forceinline__ void finish_rows_pairs(const LinearParams& p, const float* tile, const uint32_t (&peer_tile)[8], int split,
                                             const float* row_scale, int m0, int n0, int feature_tile, int first, int last, int worker,
-                                            int workers, int lane, bool ready, const int2* row_place = nullptr) {
+                                            int workers, int lane, bool ready, const int2* row_place) {
     constexpr int kTileStride = kTileN + 4;
         constexpr int kBatch = 4, kPasses = kTileN / 64;
         for (int base = first + worker * kBatch; base < last; base += workers * kBatch) {
@@ -156,5 +461,17 @@ __device__ __forceinline__ void finish_rows(const LinearParams& p, const float* 
             }
         }
     }
+
+// kForm: 0 = decided here from the call's sizes and addresses, 1 = the caller has checked that the vector form applies
+// (rows_take_quads on the host side of its launch), 2 = pairs.
+template <int EPI, int kTileN, int kForm = 0>
+__device__ __forceinline__ void finish_rows(const LinearParams& p, const float* tile, const uint32_t (&peer_tile)[8], int split,
+                                            const float* row_scale, int m0, int n0, int feature_tile, int first, int last, int worker,
+                                            int workers, int lane, bool ready, const int2* row_place = nullptr) {
+    if (kForm == 1 || (kForm == 0 && rows_take_quads<EPI>(p)))
+        finish_rows_quads<EPI, kTileN>(p, tile, peer_tile, split, row_scale, m0, n0, feature_tile, first, last, worker, workers, lane, ready, row_place);
+    else
+        finish_rows_pairs<EPI, kTileN>(p, tile, peer_tile, split, row_scale, m0, n0, feature_tile, first, last, worker, workers, lane, ready, row_place);
+}
 
 }  // namespace b200

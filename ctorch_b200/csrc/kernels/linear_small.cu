@@ -310,6 +310,16 @@ extern "C" int32_t b200_linear_shadow_parts(int64_t rows, int64_t in, int64_t ou
     return b200::linear_stream_parts(static_cast<int>(rows), static_cast<int>(in), static_cast<int>(out));
 }
 
+extern "C" const char* b200_linear_shadow_kernel(int64_t rows, int64_t in, int64_t out) {
+    // mirrors the dispatch of launch_linear_stream / launch_linear_gemm for a shadow call with bf16 weights
+    if (rows <= 0 || in <= 0 || out <= 0 || rows > INT32_MAX) return "";
+    if (rows >= b200::kGemmRows || in > 2048) {
+        if (rows >= b200::kGemmRows && out <= 64 && rows <= 512) return "linear_thin_kernel";
+        return b200::linear_decode_takes(static_cast<int>(rows)) ? "linear_decode_kernel" : "linear_gemm_kernel";
+    }
+    return "linear_stream_kernel";
+}
+
 extern "C" int32_t b200_linear_argmax_parts(int64_t rows, int64_t in, int64_t out) {
     if (rows <= 0 || in <= 0 || out <= 0 || rows > INT32_MAX || in > INT32_MAX || out > INT32_MAX) return 0;
     return b200::linear_argmax_parts(static_cast<int>(rows), static_cast<int>(in), static_cast<int>(out));

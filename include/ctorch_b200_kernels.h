@@ -162,6 +162,10 @@ B200_API int32_t b200_linear_shadow_parts(int64_t rows, int64_t in, int64_t out)
 /* Number of candidate slices a B200_EPI_ARGMAX call with these sizes writes (one per CTA of the streaming kernel, one per
  * feature tile of the dense kernel), 0 if unsupported. */
 B200_API int32_t b200_linear_argmax_parts(int64_t rows, int64_t in, int64_t out);
+/* Name of the kernel family a b200_linear_shadow call with these sizes runs on ("linear_stream_kernel": up to 16 rows;
+ * "linear_decode_kernel": decode batches on tcgen05 with the weights as the streamed operand; "linear_gemm_kernel": more
+ * rows; "linear_thin_kernel": at most 64 output features).  For logs and benchmarks. */
+B200_API const char* b200_linear_shadow_kernel(int64_t rows, int64_t in, int64_t out);
 /* Second half of the fused logits + greedy choice: merges the `parts` per-tile candidates of every row (same rule), writes
  * the chosen feature index to next[rows], and does what b200_token_feedback does with it (ids, history, counter; any of
  * ids / history may be NULL).  With caches (at most 64, one per layer) it also does b200_kv_cache_advance(caches, count, 1): the
