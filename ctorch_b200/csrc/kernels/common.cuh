@@ -74,6 +74,9 @@ __device__ __forceinline__ float silu_reference(float v) {
 // of a SwiGLU epilogue is a dependent chain per lane, so this is what bounds that epilogue's time.
 __device__ __forceinline__ float silu_fast(float v) { return __fdividef(v, 1.0f + __expf(-v)); }
 
+// Asks for the 128-byte line at `address` to be brought into L2; nothing waits for it.
+__device__ __forceinline__ void prefetch_l2(const void* address) { asm volatile("prefetch.global.L2 [%0];" ::"l"(address)); }
+
 // ---- mbarrier / TMA (cp.async.bulk.tensor, no multicast) --------------------------------------------------
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
 

@@ -91,6 +91,45 @@ __device__ __forceinline__ Candidate pair_candidate(int feature0, float a, float
     return first;
 }
 
+// Adapter delta of the feature pair (local, local + 1) of region q (0) or v (2) for activation row `row`, before the
+// alpha / rank scale: up(down(x)), the products added in index order (src/nn/decoder.cpp:26-28).
+__device__ __forceinline__ void lora_pair_delta(const LinearParams& p, int row, int region, int local, float& da, float& db) {
+    // LoRALinear::forward: base + up(down(x)) * f32(alpha/rank)
+    const float* low = p.low + static_cast<int64_t>(row) * 2 * p.lora_rank + (region == 2 ? p.lora_rank : 0);
+    const void* up = region == 0 ? p.q_up : p.v_up;
+    da = 0.0f; db = 0.0f;
+    if (p.weight_dtype == B200_BF16 && (p.lora_rank & 7) == 0) {
+        // 16-byte loads: eight up-projection weights of each feature and eight low-rank activations per step; the
+        // products are added in the same order as the scalar loop below (j ascending)
+        const uint4* ua = reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(up) + static_cast<int64_t>(local) * p.lora_rank);
+        const uint4* ub = ua + (p.lora_rank >> 3);
+        const float4* lv = reinterpret_cast<const float4*>(low);
+        for (int j = 0; j < (p.lora_rank >> 3); ++j) {
+            const uint4 wa = __ldg(ua + j), wb = __ldg(ub + j);
+            const float4 l0 = __ldg(lv + 2 * j), l1 = __ldg(lv + 2 * j + 1);
+            const float l[8] = {l0.x, l0.y, l0.z, l0.w, l1.x, l1.y, l1.z, l1.w};
+            const uint32_t pa[4] = {wa.x, wa.y, wa.z, wa.w}, pb[4] = {wb.x, wb.y, wb.z, wb.w};
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                da = __fadd_rn(da, __fmul_rn(l[2 * i], __uint_as_float(pa[i] << 16)));
+                db = __fadd_rn(db, __fmul_rn(l[2 * i], __uint_as_float(pb[i] << 16)));
+                da = __fadd_rn(da, __fmul_rn(l[2 * i + 1], __uint_as_float(pa[i] & 0xffff0000u)));
+                db = __fadd_rn(db, __fmul_rn(l[2 * i + 1], __uint_as_float(pb[i] & 0xffff0000u)));
+            }
+        }
+    } else
+    for (int j = 0; j < p.lora_rank; ++j) {
+        const int64_t at = static_cast<int64_t>(local) * p.lora_rank + j;
+        const float ua = p.weight_dtype == B200_BF16 ? load_as_f32(static_cast<const __nv_bfloat16*>(up), at)
+                                                   : load_as_f32(static_cast<const float*>(up), at);
+        const float ub = p.weight_dtype == B200_BF16 ? load_as_f32(static_cast<const __nv_bfloat16*>(up), at + p.lora_rank)
+                                                   : load_as_f32(static_cast<const float*>(up), at + p.lora_rank);
+        const float lj = __ldg(low + j);
+        da = __fadd_rn(da, __fmul_rn(lj, ua));
+        db = __fadd_rn(db, __fmul_rn(lj, ub));
+    }
+}
+
 // Finishes one pair of adjacent output features (feature0 even) of activation row `row`.
 //   store | residual add (src/nn/decoder.cpp:104-105) | SiLU(gate)*up on interleaved rows (src/nn/decoder.cpp:16) |
 //   q|k|v: adapter delta (src/nn/decoder.cpp:26-28), adjacent-pair RoPE (src/ops/contraction.cpp:44-49), q store,
@@ -98,7 +137,8 @@ __device__ __forceinline__ Candidate pair_candidate(int feature0, float a, float
 //   `place` (optional, q|k|v only): the row's position and physical cache page, looked up once per row by the caller
 //   (x = position, y = page) instead of once per feature pair here.
 template <int EPI>
-__device__ __forceinline__ void linear_epilogue(const LinearParams& p, int row, int feature0, float& a, float& b, const int2* place = nullptr) {
+__device__ __forceinline__ void linear_epilogue(const LinearParams& p, int row, int feature0, float& a, float& b, const int2* place = nullptr,
+                                                bool store = true) {
     const bool second = feature0 + 1 < p.out;
     if constexpr (EPI == B200_EPI_STORE) {
         p.y[static_cast<int64_t>(row) * p.out + feature0] = a;
@@ -125,45 +165,14 @@ __device__ __forceinline__ void linear_epilogue(const LinearParams& p, int row, 
         if (local >= D) { region = 1; local -= D; }
         if (region == 1 && local >= KV) { region = 2; local -= KV; }
         if (p.lora_rank > 0 && region != 1) {
-            // LoRALinear::forward: base + up(down(x)) * f32(alpha/rank)
-            const float* low = p.low + static_cast<int64_t>(row) * 2 * p.lora_rank + (region == 2 ? p.lora_rank : 0);
-            const void* up = region == 0 ? p.q_up : p.v_up;
-            float da = 0.0f, db = 0.0f;
-            if (p.weight_dtype == B200_BF16 && (p.lora_rank & 7) == 0) {
-                // 16-byte loads: eight up-projection weights of each feature and eight low-rank activations per step; the
-                // products are added in the same order as the scalar loop below (j ascending)
-                const uint4* ua = reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(up) + static_cast<int64_t>(local) * p.lora_rank);
-                const uint4* ub = ua + (p.lora_rank >> 3);
-                const float4* lv = reinterpret_cast<const float4*>(low);
-                for (int j = 0; j < (p.lora_rank >> 3); ++j) {
-                    const uint4 wa = __ldg(ua + j), wb = __ldg(ub + j);
-                    const float4 l0 = __ldg(lv + 2 * j), l1 = __ldg(lv + 2 * j + 1);
-                    const float l[8] = {l0.x, l0.y, l0.z, l0.w, l1.x, l1.y, l1.z, l1.w};
-                    const uint32_t pa[4] = {wa.x, wa.y, wa.z, wa.w}, pb[4] = {wb.x, wb.y, wb.z, wb.w};
-#pragma unroll
-                    for (int i = 0; i < 4; ++i) {
-                        da = __fadd_rn(da, __fmul_rn(l[2 * i], __uint_as_float(pa[i] << 16)));
-                        db = __fadd_rn(db, __fmul_rn(l[2 * i], __uint_as_float(pb[i] << 16)));
-                        da = __fadd_rn(da, __fmul_rn(l[2 * i + 1], __uint_as_float(pa[i] & 0xffff0000u)));
-                        db = __fadd_rn(db, __fmul_rn(l[2 * i + 1], __uint_as_float(pb[i] & 0xffff0000u)));
-                    }
-                }
-            } else
-            for (int j = 0; j < p.lora_rank; ++j) {
-                const int64_t at = static_cast<int64_t>(local) * p.lora_rank + j;
-                const float ua = p.weight_dtype == B200_BF16 ? load_as_f32(static_cast<const __nv_bfloat16*>(up), at)
-                                                           : load_as_f32(static_cast<const float*>(up), at);
-                const float ub = p.weight_dtype == B200_BF16 ? load_as_f32(static_cast<const __nv_bfloat16*>(up), at + p.lora_rank)
-                                                           : load_as_f32(static_cast<const float*>(up), at + p.lora_rank);
-                const float lj = __ldg(low + j);
-                da = __fadd_rn(da, __fmul_rn(lj, ua));
-                db = __fadd_rn(db, __fmul_rn(lj, ub));
-            }
+            float da, db;
+            lora_pair_delta(p, row, region, local, da, db);
             a = __fadd_rn(a, __fmul_rn(da, p.lora_scale));
             b = __fadd_rn(b, __fmul_rn(db, p.lora_scale));
         }
         const int head = local / p.head_dim, d = local % p.head_dim;
-        if (region != 2 && position < p.context) {
+        // (unsigned comparison: a warm-up pass may hand in a position that nobody has written yet)
+        if (region != 2 && static_cast<unsigned>(position) < static_cast<unsigned>(p.context)) {
             // adjacent-pair rotation, each product rounded before the add (src/ops/contraction.cpp:44-49)
             const float c = __ldg(p.cosine + static_cast<int64_t>(position) * (p.head_dim >> 1) + (d >> 1));
             const float s = __ldg(p.sine + static_cast<int64_t>(position) * (p.head_dim >> 1) + (d >> 1));
@@ -171,7 +180,9 @@ __device__ __forceinline__ void linear_epilogue(const LinearParams& p, int row, 
             a = __fsub_rn(__fmul_rn(even, c), __fmul_rn(odd, s));
             b = __fadd_rn(__fmul_rn(even, s), __fmul_rn(odd, c));
         }
-        if (region == 0) {
+        if (!store) {
+            // warm-up pass of the caller: everything above has run, nothing is written
+        } else if (region == 0) {
             float* q = p.q_out + static_cast<int64_t>(row) * D + local;
             q[0] = a;
             q[1] = b;

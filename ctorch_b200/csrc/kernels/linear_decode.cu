@@ -100,6 +100,32 @@ __global__ void __launch_bounds__(kThreads, 1) linear_decode_kernel(const __grid
     tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
 
+    // ---- what the epilogue needs, fixed by the launch (used early by the warm-up pass below) ----
+    const int rows_each = (dp.token_tile + split - 1) / split;   // the same for every token tile, so that the slab sizes agree
+    const int first = min(rows_here, part * rows_each), last = min(rows_here, first + rows_each);
+    const uint32_t slab_bytes = static_cast<uint32_t>(rows_each * kTileStride * 4);
+    const uint32_t set_bytes = slab_bytes * static_cast<uint32_t>(split);
+    int live_tiles = 0;
+    for (int t = 0; t < TILES; ++t) live_tiles += (tile0 + t) * kFeatures < p.out ? 1 : 0;   // the same in every CTA of the cluster
+    const bool together = static_cast<uint32_t>(live_tiles) * set_bytes <= static_cast<uint32_t>(dp.body_bytes);
+    const uint32_t slabs = smem_u32(smem);
+
+    auto finish_tile = [&](int t, uint32_t set_base, bool whole, int worker) {
+        uint32_t partial[8];
+#pragma unroll
+        for (int z = 0; z < 8; ++z)   // band-relative storage addressed by tile row: shift the base by the band's first row
+            partial[z] = set_base + static_cast<uint32_t>(z < split ? z : 0) * slab_bytes - static_cast<uint32_t>(first * kTileStride * 4);
+        const float* local = reinterpret_cast<const float*>(smem + (set_base - slabs)) - first * kTileStride;
+        const int n0 = (tile0 + t) * kFeatures, workers = kThreads / 32;
+        switch (dp.epilogue) {
+        case B200_EPI_STORE: finish_rows<B200_EPI_STORE, kFeatures, QUADS ? 1 : 2, true>(p, local, partial, split, row_scale, row0, n0, tile0 + t, first, last, worker, workers, lane, whole); break;
+        case B200_EPI_RESIDUAL: finish_rows<B200_EPI_RESIDUAL, kFeatures, QUADS ? 1 : 2, true>(p, local, partial, split, row_scale, row0, n0, tile0 + t, first, last, worker, workers, lane, whole); break;
+        case B200_EPI_SWIGLU: finish_rows<B200_EPI_SWIGLU, kFeatures, QUADS ? 1 : 2, true>(p, local, partial, split, row_scale, row0, n0, tile0 + t, first, last, worker, workers, lane, whole); break;
+        case B200_EPI_QKV: finish_rows<B200_EPI_QKV, kFeatures, QUADS ? 1 : 2, true>(p, local, partial, split, row_scale, row0, n0, tile0 + t, first, last, worker, workers, lane, whole, row_place); break;
+        default: finish_rows<B200_EPI_ARGMAX, kFeatures, QUADS ? 1 : 2, true>(p, local, partial, split, row_scale, row0, n0, tile0 + t, first, last, worker, workers, lane, whole); break;
+        }
+    };
+
     if (warp == 0) {
         // TMA producer: the whole warp walks the loop, one elected lane issues.
         if (elect_one()) {
@@ -151,6 +177,24 @@ __global__ void __launch_bounds__(kThreads, 1) linear_decode_kernel(const __grid
     } else {
         grid_dependency_wait();   // sums of squares, residual, cache lengths come from the preceding kernels
         grid_launch_dependents();
+        // What the epilogue will read from global memory is asked into L2 now, while the products run: inside a decode
+        // step the attention kernels stream the whole cache through L2 between two projections, so the residual rows
+        // and the next norm's weights would otherwise come from DRAM one dependent round trip after the other.
+        if (dp.epilogue == B200_EPI_RESIDUAL && warp >= 6) {
+            const int band = (dp.token_tile + split - 1) / split;
+            const int band_first = min(rows_here, part * band), band_rows = min(rows_here, band_first + band) - band_first;
+            const int lines_per_row = TILES * (kFeatures * 4 / 128);
+            for (int i = static_cast<int>(threadIdx.x) - 192; i < band_rows * lines_per_row; i += kThreads - 192) {
+                const int r = i / lines_per_row, line = i - r * lines_per_row;
+                const int feature = tile0 * kFeatures + line * 32;
+                if (feature < p.out) prefetch_l2(p.residual + static_cast<int64_t>(row0 + band_first + r) * p.out + feature);
+            }
+            if (p.out_norm_weight && threadIdx.x - 192 < TILES * 4) {
+                const int feature = tile0 * kFeatures + (static_cast<int>(threadIdx.x) - 192) * 32;
+                if (feature < p.out)
+                    prefetch_l2(static_cast<const uint8_t*>(p.out_norm_weight) + static_cast<int64_t>(feature) * (p.out_norm_dtype == B200_BF16 ? 2 : 4));
+            }
+        }
     }
 
     if (warp == 1) {
@@ -215,26 +259,21 @@ __global__ void __launch_bounds__(kThreads, 1) linear_decode_kernel(const __grid
             }
             row_scale[row] = scale;
             if (dp.epilogue == B200_EPI_QKV) {
-                row_place[row] = qkv_row_place(p, row0 + row);
+                const int2 place = qkv_row_place(p, row0 + row);
+                row_place[row] = place;
+                if (place.x < p.context) {   // the row's rotation factors, wanted by the epilogue (head_dim / 2 floats each)
+                    const int64_t at = static_cast<int64_t>(place.x) * (p.head_dim >> 1);
+                    for (int offset = 0; offset < (p.head_dim >> 1); offset += 32) {
+                        prefetch_l2(p.cosine + at + offset);
+                        prefetch_l2(p.sine + at + offset);
+                    }
+                }
             }
         }
     }
     // Every warp takes part in draining the accumulators: warp w may read the TMEM lanes 32 * (w % 4) .. + 31, so three
     // warps share each lane quarter and divide the token columns among themselves.
-    ready = mbar_wait_relaxed(accumulator_ready, 0);
-    if (!ready && lane == 0) atomicExch(dp.status, B200_DEVICE_TIMEOUT);
-    tc_fence_after_sync();
-    if (lane == 0) tile_ready[warp] = ready ? 1 : 0;
     const int third = warp >> 2;
-    const int rows_each = (dp.token_tile + split - 1) / split;   // the same for every token tile, so that the slab sizes agree
-    const int first = min(rows_here, part * rows_each), last = min(rows_here, first + rows_each);
-    const uint32_t slab_bytes = static_cast<uint32_t>(rows_each * kTileStride * 4);
-    const uint32_t set_bytes = slab_bytes * static_cast<uint32_t>(split);
-    int live_tiles = 0;
-    for (int t = 0; t < TILES; ++t) live_tiles += (tile0 + t) * kFeatures < p.out ? 1 : 0;   // the same in every CTA of the cluster
-    const bool together = static_cast<uint32_t>(live_tiles) * set_bytes <= static_cast<uint32_t>(dp.body_bytes);
-    const uint32_t slabs = smem_u32(smem);
-
     auto push_tile = [&](int t, uint32_t set_base) {
         if (!ready) return;
         const uint32_t source = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(t * dp.n_alloc);
@@ -271,45 +310,50 @@ __global__ void __launch_bounds__(kThreads, 1) linear_decode_kernel(const __grid
             }
         }
     };
-    auto finish_tile = [&](int t, uint32_t set_base) {
-        uint32_t partial[8];
-#pragma unroll
-        for (int z = 0; z < 8; ++z)   // band-relative storage addressed by tile row: shift the base by the band's first row
-            partial[z] = set_base + static_cast<uint32_t>(z < split ? z : 0) * slab_bytes - static_cast<uint32_t>(first * kTileStride * 4);
-        bool whole = true;
-        for (int w = 0; w < kThreads / 32; ++w) whole = whole && tile_ready[w] != 0;
-        const float* local = reinterpret_cast<const float*>(smem + (set_base - slabs)) - first * kTileStride;
-        const int n0 = (tile0 + t) * kFeatures, workers = kThreads / 32;
-        switch (dp.epilogue) {
-        case B200_EPI_STORE: finish_rows<B200_EPI_STORE, kFeatures, QUADS ? 1 : 2>(p, local, partial, split, row_scale, row0, n0, tile0 + t, first, last, warp, workers, lane, whole); break;
-        case B200_EPI_RESIDUAL: finish_rows<B200_EPI_RESIDUAL, kFeatures, QUADS ? 1 : 2>(p, local, partial, split, row_scale, row0, n0, tile0 + t, first, last, warp, workers, lane, whole); break;
-        case B200_EPI_SWIGLU: finish_rows<B200_EPI_SWIGLU, kFeatures, QUADS ? 1 : 2>(p, local, partial, split, row_scale, row0, n0, tile0 + t, first, last, warp, workers, lane, whole); break;
-        case B200_EPI_QKV: finish_rows<B200_EPI_QKV, kFeatures, QUADS ? 1 : 2>(p, local, partial, split, row_scale, row0, n0, tile0 + t, first, last, warp, workers, lane, whole, row_place); break;
-        default: finish_rows<B200_EPI_ARGMAX, kFeatures, QUADS ? 1 : 2>(p, local, partial, split, row_scale, row0, n0, tile0 + t, first, last, warp, workers, lane, whole); break;
-        }
-    };
     auto barrier_all = [&]() {
         __syncwarp();
         if (split > 1) cluster_sync_all();
         else __syncthreads();
     };
 
-    if (split > 1) {
-        // The slabs lie in the operand ring: a peer may only write into this CTA once the ring is drained, which is when
-        // the accumulators are complete.  Every warp waits for that, then the cluster meets once before the pushes.
-        __syncwarp();
-        cluster_sync_all();
-    }
-    if (together) {
-        for (int t = 0; t < live_tiles; ++t) push_tile(t, slabs + static_cast<uint32_t>(t) * set_bytes);
-        barrier_all();   // every partial sum of this CTA's band has arrived; nobody writes here any more
-        for (int t = 0; t < live_tiles; ++t) finish_tile(t, slabs + static_cast<uint32_t>(t) * set_bytes);
-    } else {
-        for (int t = 0; t < live_tiles; ++t) {
-            push_tile(t, slabs);
-            barrier_all();
-            finish_tile(t, slabs);
-            barrier_all();   // the slabs may be overwritten by the next tile's partial sums
+    bool whole = true;   // read after a round's first barrier: every warp has posted its flag by then
+    auto read_flags = [&]() {
+        whole = true;
+        for (int w = 0; w < kThreads / 32; ++w) whole = whole && tile_ready[w] != 0;
+    };
+    // Two rounds over the same code.  Round 0, warps 6-11 only, while the products still run: the row epilogue once with
+    // every store switched off (accumulators "not valid"), on whatever the shared-memory tile holds.  Inside a decode step
+    // the kernels before this one have pushed this code out of the instruction caches and, with the attention kernels
+    // streaming the whole cache, out of L2; fetched only when the products were done it stretched the epilogue to two or
+    // three times its warm duration.  Round 1 is the epilogue proper.
+#pragma unroll 1
+    for (int round = (warp >= 6 && live_tiles > 0 && first < last) ? 0 : 1; round < 2; ++round) {
+        const bool real = round == 1;
+        if (real) {
+            ready = mbar_wait_relaxed(accumulator_ready, 0);
+            if (!ready && lane == 0) atomicExch(dp.status, B200_DEVICE_TIMEOUT);
+            tc_fence_after_sync();
+            if (lane == 0) tile_ready[warp] = ready ? 1 : 0;
+            if (split > 1) {
+                // The slabs lie in the operand ring: a peer may only write into this CTA once the ring is drained, which is
+                // when the accumulators are complete.  Every warp has waited for that; the cluster meets before the pushes.
+                __syncwarp();
+                cluster_sync_all();
+            }
+        }
+        const int tiles_now = real ? live_tiles : 1;
+#pragma unroll 1
+        for (int t = 0; t < tiles_now; ++t) {
+            if (real && (t == 0 || !together)) {
+                // all tile sets fit the drained ring: one barrier per launch; otherwise the tiles take turns
+                const int from = together ? 0 : t, to = together ? live_tiles : t + 1;
+#pragma unroll 1
+                for (int u = from; u < to; ++u) push_tile(u, together ? slabs + static_cast<uint32_t>(u) * set_bytes : slabs);
+                barrier_all();   // every partial sum of this CTA's band has arrived
+                read_flags();
+            }
+            finish_tile(t, together ? slabs + static_cast<uint32_t>(t) * set_bytes : slabs, real && whole, real ? warp : warp - 6);
+            if (real && !together) barrier_all();   // the slabs may be overwritten by the next tile's partial sums
         }
     }
     tc_fence_before_sync();

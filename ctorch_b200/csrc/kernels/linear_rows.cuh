@@ -95,11 +95,20 @@ __host__ __device__ __forceinline__ bool rows_take_quads(const LinearParams& p) 
     if constexpr (EPI == B200_EPI_SWIGLU)
         bits |= (reinterpret_cast<uintptr_t>(p.y) << 1) | (reinterpret_cast<uintptr_t>(p.out_hi) << 2) | (reinterpret_cast<uintptr_t>(p.out_lo) << 2);
     if constexpr (EPI == B200_EPI_QKV) {
-        if ((p.heads * p.head_dim) & 3 || (p.kv_heads * p.head_dim) & 3) return false;   // a quad never straddles q | k | v
+        if (p.head_dim & 3) return false;   // a quad never straddles q | k | v or two heads
+        bits |= reinterpret_cast<uintptr_t>(p.q_out) | reinterpret_cast<uintptr_t>(p.cosine) << 1 | reinterpret_cast<uintptr_t>(p.sine) << 1
+              | reinterpret_cast<uintptr_t>(p.kv.pool[0]) | reinterpret_cast<uintptr_t>(p.kv.pool[1]);
     }
     return (bits & 15) == 0;
 }
 
+// The same from this CTA's own shared memory (an address of the CTA's window): the plain path, which does not go through
+// the cluster's network.
+__device__ __forceinline__ float4 load_shared_float4(uint32_t address) {
+    float4 value;
+    asm("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(value.x), "=f"(value.y), "=f"(value.z), "=f"(value.w) : "r"(address));
+    return value;
+}
 __device__ __forceinline__ float4 load_cluster_float4(uint32_t cluster_address) {
     float4 value;
     asm("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(value.x), "=f"(value.y), "=f"(value.z), "=f"(value.w) : "r"(cluster_address));
@@ -129,7 +138,7 @@ __device__ __forceinline__ void fetch_residual_quads(const LinearParams& p, int 
 // arithmetic, stores - with no branch between the rows, so that the rows' dependent chains (shared-memory load, scale,
 // exponential, reciprocal, roundings) overlap: with twelve warps on an SM nothing else hides those latencies.  Rows past
 // the end repeat the last live row (the same values go to the same places twice) instead of being branched around.
-template <int EPI, int kTileN>
+template <int EPI, int kTileN, bool kLocal>
 __device__ __forceinline__ void finish_rows_quads(const LinearParams& p, const float* tile, const uint32_t (&peer_tile)[8], int split,
                                                   const float* row_scale, int m0, int n0, int feature_tile, int first, int last, int worker,
                                                   int workers, int lane, bool ready, const int2* row_place) {
@@ -157,39 +166,21 @@ __device__ __forceinline__ void finish_rows_quads(const LinearParams& p, const f
         }
     }
     const float4 zero = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-    if constexpr (EPI == B200_EPI_QKV) {
-        // q | k | v: adapter delta, rotation and the cache append per feature pair (linear_epilogue); the body is large,
-        // so the rows are walked one at a time
-#pragma unroll 1
-        for (int tile_row = first + worker; tile_row < last; tile_row += workers) {
-            const float scale = row_scale[tile_row];
-            const int2* place = row_place ? row_place + tile_row : nullptr;
+    // q | k | v: what a lane's four features are does not depend on the row - region, head and offset inside the head
+    // (a quad never straddles q | k | v or a head: rows_take_quads)
+    int region[kPasses], local[kPasses], head[kPasses], inside[kPasses];
 #pragma unroll
-            for (int pass = 0; pass < kPasses; ++pass) {
-                if (!live[pass]) continue;
-                const int c = pass * 128 + lane * 4;
-                float4 v;
-                if (split == 1) {
-                    v = *reinterpret_cast<const float4*>(tile + tile_row * kTileStride + c);
-                } else {
-                    const uint32_t offset = static_cast<uint32_t>(tile_row * kTileStride + c) * 4;
-                    v = load_cluster_float4(peer_tile[0] + offset);
-#pragma unroll
-                    for (int z = 1; z < 8; ++z) {
-                        if (z < split) {
-                            const float4 w = load_cluster_float4(peer_tile[z] + offset);
-                            v.x += w.x; v.y += w.y; v.z += w.z; v.w += w.w;
-                        }
-                    }
-                }
-#pragma unroll 1
-                for (int half = 0; half < 2; ++half) {
-                    float a = (half ? v.z : v.x) * scale, b = (half ? v.w : v.y) * scale;
-                    linear_epilogue<EPI>(p, m0 + tile_row, n0 + c + 2 * half, a, b, place);
-                }
-            }
+    for (int pass = 0; pass < kPasses; ++pass) {
+        region[pass] = 0; local[pass] = 0; head[pass] = 0; inside[pass] = 0;
+        if constexpr (EPI == B200_EPI_QKV) {
+            const int D = p.heads * p.head_dim, KV = p.kv_heads * p.head_dim;
+            int l = n0 + pass * 128 + lane * 4;
+            if (l >= D) { region[pass] = 1; l -= D; }
+            if (region[pass] == 1 && l >= KV) { region[pass] = 2; l -= KV; }
+            local[pass] = l;
+            head[pass] = l / p.head_dim;
+            inside[pass] = l - head[pass] * p.head_dim;
         }
-        return;
     }
     float4 carried[kBatch][kPasses];
     int base = first + worker * kBatch;
@@ -213,7 +204,7 @@ __device__ __forceinline__ void finish_rows_quads(const LinearParams& p, const f
                     const uint32_t offset = static_cast<uint32_t>(tile_row * kTileStride + c) * 4;
                     float4 v[8];
 #pragma unroll
-                    for (int z = 0; z < 8; ++z) v[z] = z < split ? load_cluster_float4(peer_tile[z] + offset) : zero;
+                    for (int z = 0; z < 8; ++z) v[z] = z < split ? (kLocal ? load_shared_float4(peer_tile[z] + offset) : load_cluster_float4(peer_tile[z] + offset)) : zero;
                     float4 sum = v[0];
 #pragma unroll
                     for (int z = 1; z < 8; ++z) { sum.x += v[z].x; sum.y += v[z].y; sum.z += v[z].z; sum.w += v[z].w; }
@@ -250,7 +241,7 @@ __device__ __forceinline__ void finish_rows_quads(const LinearParams& p, const f
                     lo[r][pass] = make_uint2(*reinterpret_cast<const uint32_t*>(&lo0), *reinterpret_cast<const uint32_t*>(&lo1));
                 }
             }
-            if (p.sumsq_out) {
+            if (p.sumsq_out && ready) {
 #pragma unroll
                 for (int o = 16; o > 0; o >>= 1) {
 #pragma unroll
@@ -362,7 +353,7 @@ __device__ __forceinline__ void finish_rows_quads(const LinearParams& p, const f
                     if (preferred(other, best[r])) best[r] = other;
                 }
             }
-            if (lane < kBatch) {
+            if (lane < kBatch && ready) {
                 Candidate mine = best[0];
                 int row_of_lane = rows[0];
 #pragma unroll
@@ -371,6 +362,83 @@ __device__ __forceinline__ void finish_rows_quads(const LinearParams& p, const f
                 }
                 p.best_value[static_cast<int64_t>(feature_tile) * p.rows + m0 + row_of_lane] = mine.value;
                 p.best_index[static_cast<int64_t>(feature_tile) * p.rows + m0 + row_of_lane] = mine.index;
+            }
+        } else {
+            // q | k | v (src/nn/decoder.cpp:26-28,77-88; src/ops/contraction.cpp:44-49; src/nn/kv_cache.cpp:24-28)
+            int2 place[kBatch];
+            float2 cosine[kBatch][kPasses], sine[kBatch][kPasses];
+#pragma unroll
+            for (int r = 0; r < kBatch; ++r) {
+                place[r] = row_place ? row_place[rows[r]] : qkv_row_place(p, m0 + rows[r]);
+#pragma unroll
+                for (int pass = 0; pass < kPasses; ++pass) {
+                    cosine[r][pass] = make_float2(1.0f, 1.0f);
+                    sine[r][pass] = make_float2(0.0f, 0.0f);
+                    // (unsigned comparison: the warm-up pass of a caller may see a position that nobody has written yet)
+                    const bool turns = region[pass] != 2 && static_cast<unsigned>(place[r].x) < static_cast<unsigned>(p.context)
+                                       && n0 + pass * 128 + lane * 4 < p.out;
+                    if (turns) {
+                        const int64_t at = static_cast<int64_t>(place[r].x) * (p.head_dim >> 1) + (inside[pass] >> 1);
+                        cosine[r][pass] = __ldg(reinterpret_cast<const float2*>(p.cosine + at));
+                        sine[r][pass] = __ldg(reinterpret_cast<const float2*>(p.sine + at));
+                    }
+                }
+            }
+            float4 result[kBatch][kPasses];
+#pragma unroll
+            for (int r = 0; r < kBatch; ++r) {
+#pragma unroll
+                for (int pass = 0; pass < kPasses; ++pass) {
+                    const float4 v = value[r][pass];
+                    result[r][pass] = make_float4(v.x * scale[r], v.y * scale[r], v.z * scale[r], v.w * scale[r]);
+                }
+            }
+            if (p.lora_rank > 0) {
+#pragma unroll
+                for (int r = 0; r < kBatch; ++r) {
+#pragma unroll
+                    for (int pass = 0; pass < kPasses; ++pass) {
+                        if (region[pass] == 1 || n0 + pass * 128 + lane * 4 >= p.out) continue;
+                        float da, db, dc, dd;
+                        lora_pair_delta(p, m0 + rows[r], region[pass], local[pass], da, db);
+                        lora_pair_delta(p, m0 + rows[r], region[pass], local[pass] + 2, dc, dd);
+                        float4& t = result[r][pass];
+                        t = make_float4(__fadd_rn(t.x, __fmul_rn(da, p.lora_scale)), __fadd_rn(t.y, __fmul_rn(db, p.lora_scale)),
+                                        __fadd_rn(t.z, __fmul_rn(dc, p.lora_scale)), __fadd_rn(t.w, __fmul_rn(dd, p.lora_scale)));
+                    }
+                }
+            }
+#pragma unroll
+            for (int r = 0; r < kBatch; ++r) {
+#pragma unroll
+                for (int pass = 0; pass < kPasses; ++pass) {
+                    // adjacent-pair rotation, each product rounded before the add; v (and positions past the table) keep
+                    // cosine 1 and sine 0, which leaves the values as they are
+                    const float4 t = result[r][pass];
+                    const float2 c = cosine[r][pass], sn = sine[r][pass];
+                    float4 turned = t;
+                    if (region[pass] != 2) {
+                        turned = make_float4(__fsub_rn(__fmul_rn(t.x, c.x), __fmul_rn(t.y, sn.x)), __fadd_rn(__fmul_rn(t.x, sn.x), __fmul_rn(t.y, c.x)),
+                                             __fsub_rn(__fmul_rn(t.z, c.y), __fmul_rn(t.w, sn.y)), __fadd_rn(__fmul_rn(t.z, sn.y), __fmul_rn(t.w, c.y)));
+                        if (!(static_cast<unsigned>(place[r].x) < static_cast<unsigned>(p.context))) turned = t;
+                    }
+                    if (!live[pass]) continue;
+                    if (region[pass] == 0) {
+                        *reinterpret_cast<float4*>(p.q_out + static_cast<int64_t>(m0 + rows[r]) * (p.heads * p.head_dim) + local[pass]) = turned;
+                    } else {
+                        const int slot = place[r].x % p.kv.page_size;
+                        const int64_t at = ((static_cast<int64_t>(place[r].y) * p.kv.kv_heads + head[pass]) * p.kv.page_size + slot) * p.kv.head_dim
+                                           + inside[pass];
+                        void* pool = p.kv.pool[region[pass] - 1];
+                        if (p.kv.dtype == B200_BF16) {
+                            const __nv_bfloat162 lo2 = __floats2bfloat162_rn(turned.x, turned.y), hi2 = __floats2bfloat162_rn(turned.z, turned.w);
+                            *reinterpret_cast<uint2*>(static_cast<__nv_bfloat16*>(pool) + at) =
+                                make_uint2(*reinterpret_cast<const uint32_t*>(&lo2), *reinterpret_cast<const uint32_t*>(&hi2));
+                        } else {
+                            *reinterpret_cast<float4*>(static_cast<float*>(pool) + at) = turned;
+                        }
+                    }
+                }
             }
         }
     }
@@ -463,13 +531,14 @@ __device__ __forceinline__ void finish_rows_pairs(const LinearParams& p, const f
     }
 
 // kForm: 0 = decided here from the call's sizes and addresses, 1 = the caller has checked that the vector form applies
-// (rows_take_quads on the host side of its launch), 2 = pairs.
-template <int EPI, int kTileN, int kForm = 0>
+// (rows_take_quads on the host side of its launch), 2 = pairs.  kLocal: the `split` partial tiles all lie in this CTA's own
+// shared memory (their senders pushed them here), so they are read with plain shared-memory loads.
+template <int EPI, int kTileN, int kForm = 0, bool kLocal = false>
 __device__ __forceinline__ void finish_rows(const LinearParams& p, const float* tile, const uint32_t (&peer_tile)[8], int split,
                                             const float* row_scale, int m0, int n0, int feature_tile, int first, int last, int worker,
                                             int workers, int lane, bool ready, const int2* row_place = nullptr) {
     if (kForm == 1 || (kForm == 0 && rows_take_quads<EPI>(p)))
-        finish_rows_quads<EPI, kTileN>(p, tile, peer_tile, split, row_scale, m0, n0, feature_tile, first, last, worker, workers, lane, ready, row_place);
+        finish_rows_quads<EPI, kTileN, kLocal>(p, tile, peer_tile, split, row_scale, m0, n0, feature_tile, first, last, worker, workers, lane, ready, row_place);
     else
         finish_rows_pairs<EPI, kTileN>(p, tile, peer_tile, split, row_scale, m0, n0, feature_tile, first, last, worker, workers, lane, ready, row_place);
 }
