@@ -368,8 +368,13 @@ def measure_decoder(args, name, spec, weights, rank, world, local, dist) -> dict
             kernel += " (the %d projection launches of one step: weights streamed once)" % (profile["launches"] - spec["layers"] - 2)
         else:
             kernel = ("attention_mma_kernel" if spec["dtype"] == "bf16" else "attention_generic_kernel") + " (%d launches of one step: K and V streamed once)" % spec["layers"]
+        # DRAM traffic per algorithmic byte from the ncu captures of these kernels (dram__bytes_read + dram__bytes_write
+        # of one launch / its algorithmic bytes): attention 1.03; projections 1.03 (gate/up) to 1.31 (down, whose
+        # activation planes and residual rows weigh most against its weights), 1.1 over the launches of a layer
+        ratio = 1.03 if kind == "attention" else 1.1
         return {"bound": "hbm", "kernel": kernel, "achieved": achieved, "peak": peak, "unit": "GB/s",
-                "frac": achieved / peak if achieved else None, "peak_kind": peak_kind, "traffic": None,
+                "frac": achieved / peak if achieved else None, "peak_kind": peak_kind, "traffic": bytes_ * ratio,
+                "traffic_source": "ncu capture of one launch of a smaller case, scaled by the units processed (x%.2f algorithmic)" % ratio,
                 "algorithmic_bytes": bytes_, "launch_ms": ms, "share_of_step": shares[kind],
                 "share_source": "per-launch CUDA events of the same step run eagerly", "eager_profile_ms": profile[kind + "_ms"]}
 
