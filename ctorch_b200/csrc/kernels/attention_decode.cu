@@ -34,6 +34,7 @@ struct AttnParams {
     int positions_per_item;   // tensor-core kernel: consecutive positions of one sequence that share a CTA (1 in decode)
     KvView kv;
     int pages_per_split, num_splits;
+    int items;         // persistent tensor-core kernel: items the grid walks (grid x otherwise)
     float* part_o;     // [rows*heads, num_splits, head_dim]
     float* part_ml;    // [rows*heads, num_splits, 2]
     float* out;        // [rows, heads*head_dim]
@@ -99,19 +100,23 @@ constexpr int kConsumerWarps = 8;   // two groups of four: group g takes pages g
 constexpr int kGroupWarps = 4;      // tensor-core pipeline at a time; a warp owns 16 tokens of its group's page
 constexpr int kFastThreads = (kConsumerWarps + 1) * 32;
 constexpr int kHalfTileBytes = 64 * 128;  // one TMA box: 64 tokens x 64 bf16
+constexpr int kFastControlBytes = 256;    // behind the ring: full / empty barriers (at most 128 bytes), the give-up flag at 192
 
 template <int HD, int STAGES> struct FastShape {
     static constexpr int halves = HD / 64;
     static constexpr int tile_bytes = halves * kHalfTileBytes;  // K or V page
     static constexpr int stage_bytes = 2 * tile_bytes;
     static constexpr int stages = STAGES;  // 6 x 32 KB (head_dim 128) or 8 / 6 x 16 KB (head_dim 64) of K and V in flight per CTA
-    static constexpr int smem_bytes = stages * stage_bytes + 1024 + 2 * stages * 8;
+    static constexpr int smem_bytes = stages * stage_bytes + 1024 + kFastControlBytes;   // 1024: slack of the 1024-byte alignment
 };
 
 // Byte offset of 16-byte chunk `chunk` (8 features) of token `token` inside a swizzled K or V page.
 __device__ __forceinline__ uint32_t tile_offset(int token, int chunk) {
     return static_cast<uint32_t>((chunk >> 3) * kHalfTileBytes + token * 128 + (((chunk & 7) ^ (token & 7)) << 4));
 }
+
+// Barrier over the consumer warps only (the producer warp keeps streaming).
+__device__ __forceinline__ void consumer_barrier() { asm volatile("bar.sync 1, %0;" ::"n"(kConsumerWarps * 32) : "memory"); }
 
 // Pages per split for a sequence of `pages` cached pages: the splits the sequence needs at the planned size share its
 // pages evenly (17 pages planned as 16 + 1 become 9 + 8).
@@ -122,7 +127,11 @@ __device__ __forceinline__ int balanced_pages_per_split(int pages, int planned) 
 
 // MULTI: items of several positions (prefill chunks); the decode instantiation keeps one position per item and one key
 // count for all of its rows.
-template <int HD, int STAGES, bool MULTI>
+// PERSIST (decode, unsplit items, more items than resident CTAs): a CTA walks the items blockIdx.x, + gridDim.x, ... and its
+// producer warp runs ahead into the next item's pages while the consumers finish the current one, so the K/V stream of an
+// SM does not stop at item boundaries (an item of 17 pages is ~290 KB: a sixth of its time was pipeline ramp).  The
+// cross-warp merge then has its own shared memory behind the ring instead of re-using drained stages.
+template <int HD, int STAGES, bool MULTI, bool PERSIST>
 __global__ void __launch_bounds__(kFastThreads) attention_mma_kernel(const __grid_constant__ CUtensorMap kmap,
                                                                      const __grid_constant__ CUtensorMap vmap,
                                                                      const AttnParams p) {
@@ -131,74 +140,89 @@ __global__ void __launch_bounds__(kFastThreads) attention_mma_kernel(const __gri
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
     uint64_t* full = reinterpret_cast<uint64_t*>(smem + S::stages * S::stage_bytes);
     uint64_t* empty = full + S::stages;
+    volatile int* gave_up = reinterpret_cast<volatile int*>(smem + S::stages * S::stage_bytes + 192);   // a consumer's wait ran out
 
-    grid_dependency_wait();   // q, the cache and the lengths come from the preceding kernels
-    grid_launch_dependents();
-    // An item is (sequence, block of consecutive positions, KV head).  The 16 fragment rows of a warp hold the block's
-    // positions times the head group: row r = position r / group, query head r % group.  Decode: one position, rows =
-    // the group.  Prefill: 16 / group positions share every K/V byte the CTA streams.
-    const int item = blockIdx.x, split = blockIdx.y;
-    const int kvh = item % p.kv.kv_heads, block = item / p.kv.kv_heads;
-    const int positions = MULTI ? p.positions_per_item : 1;
-    const int blocks_per_sequence = (p.tokens_per_sequence + positions - 1) / positions;
-    const int sequence = block / blocks_per_sequence;
-    const int t_first = (block - sequence * blocks_per_sequence) * positions;
-    const int t_count = MULTI ? min(positions, p.tokens_per_sequence - t_first) : 1;
-    const int row = sequence * p.tokens_per_sequence + t_first;   // first activation row of the item
-    const int base_len = p.kv.lengths[sequence];
-    const int kv_len = base_len + (p.causal ? t_first + t_count : 0);   // keys the item's last position sees
-    int page_end = (kv_len + kFastPageSize - 1) / kFastPageSize;
-    const int per_split = balanced_pages_per_split(page_end, p.pages_per_split);
-    const int page_begin = split * per_split;
-    if (page_end > page_begin + per_split) page_end = page_begin + per_split;
-    if (page_begin >= page_end) return;  // uniform for the CTA
-    const int pages = page_end - page_begin;
-    const int group = p.heads / p.kv.kv_heads;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-
     if (threadIdx.x == 0) {
         for (int s = 0; s < S::stages; ++s) {
             mbar_init(&full[s], 1);
             mbar_init(&empty[s], kGroupWarps);
         }
+        *gave_up = 0;
         mbar_fence_init();
     }
     __syncthreads();
+    grid_dependency_wait();   // q, the cache and the lengths come from the preceding kernels
+    grid_launch_dependents();
 
-    float m_row[2] = {-INFINITY, -INFINITY}, l_row[2] = {0.0f, 0.0f};
-    float o[HD / 8][4];
-#pragma unroll
-    for (int j = 0; j < HD / 8; ++j) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.0f;
+    // An item is (sequence, block of consecutive positions, KV head).  The 16 fragment rows of a warp hold the block's
+    // positions times the head group: row r = position r / group, query head r % group.  Decode: one position, rows =
+    // the group.  Prefill: 16 / group positions share every K/V byte the CTA streams.
+    const int group = p.heads / p.kv.kv_heads;
+    const int positions = MULTI ? p.positions_per_item : 1;
+    const int blocks_per_sequence = (p.tokens_per_sequence + positions - 1) / positions;
+    const int split = PERSIST ? 0 : static_cast<int>(blockIdx.y);
+    const int items = PERSIST ? p.items : static_cast<int>(blockIdx.x) + 1;
+    // the cross-warp merge: [warps][16][HD] partial outputs and [warps][16][2] (max, sum); PERSIST keeps only the rows of a
+    // decode item ([warps][group][...]) in its own memory behind the barriers
+    float* merge_o = PERSIST ? reinterpret_cast<float*>(smem + S::stages * S::stage_bytes + kFastControlBytes) : reinterpret_cast<float*>(smem);
+    const int merge_rows = PERSIST ? group : 16;
+    float* merge_ml = merge_o + kConsumerWarps * merge_rows * HD;
+    int walked = 0;   // pages this CTA has been through before the current item: stage and phase follow from it
 
-    if (warp == kConsumerWarps) {
-        // ---- producer: all lanes walk the loop together, lane 0 waits and issues ----
-        if (lane == 0) { tma_prefetch_descriptor(&kmap); tma_prefetch_descriptor(&vmap); }
-        const int32_t* table = p.kv.page_table + static_cast<int64_t>(sequence) * p.kv.pages_per_seq + page_begin;
-        bool alive = true;
-        for (int i = 0; i < pages && alive; ++i) {
-            if (lane == 0) {
-                const int s = i % S::stages;
-                const uint32_t phase = (i / S::stages) & 1;
-                if (!mbar_wait(&empty[s], phase ^ 1)) {
-                    atomicExch(p.status, B200_DEVICE_TIMEOUT);
-                    alive = false;
-                } else {
-                    const int page = table[i];
-                    const int y = (page * p.kv.kv_heads + kvh) * kFastPageSize;
-                    uint8_t* kdst = smem + s * S::stage_bytes;
-                    uint8_t* vdst = kdst + S::tile_bytes;
-                    mbar_expect_tx(&full[s], S::stage_bytes);
+    for (int item = blockIdx.x; item < items; item += gridDim.x) {
+        const int kvh = item % p.kv.kv_heads, block = item / p.kv.kv_heads;
+        const int sequence = block / blocks_per_sequence;
+        const int t_first = (block - sequence * blocks_per_sequence) * positions;
+        const int t_count = MULTI ? min(positions, p.tokens_per_sequence - t_first) : 1;
+        const int row = sequence * p.tokens_per_sequence + t_first;   // first activation row of the item
+        const int base_len = p.kv.lengths[sequence];
+        const int kv_len = base_len + (p.causal ? t_first + t_count : 0);   // keys the item's last position sees
+        int page_end = (kv_len + kFastPageSize - 1) / kFastPageSize;
+        const int per_split = balanced_pages_per_split(page_end, p.pages_per_split);
+        const int page_begin = split * per_split;
+        if (page_end > page_begin + per_split) page_end = page_begin + per_split;
+        if (page_begin >= page_end) continue;  // uniform for the CTA (a sequence without keys writes nothing, as before)
+        const int pages = page_end - page_begin;
+
+        if (warp == kConsumerWarps) {
+            // ---- producer: all lanes walk the loop together, lane 0 waits and issues ----
+            if (lane == 0 && walked == 0) { tma_prefetch_descriptor(&kmap); tma_prefetch_descriptor(&vmap); }
+            const int32_t* table = p.kv.page_table + static_cast<int64_t>(sequence) * p.kv.pages_per_seq + page_begin;
+            bool alive = true;
+            for (int i = 0; i < pages && alive; ++i) {
+                if (lane == 0) {
+                    const int n = walked + i;
+                    const int s = n % S::stages;
+                    const uint32_t phase = (n / S::stages) & 1;
+                    if (!mbar_wait(&empty[s], phase ^ 1)) {
+                        atomicExch(p.status, B200_DEVICE_TIMEOUT);
+                        alive = false;
+                    } else {
+                        const int page = table[i];
+                        const int y = (page * p.kv.kv_heads + kvh) * kFastPageSize;
+                        uint8_t* kdst = smem + s * S::stage_bytes;
+                        uint8_t* vdst = kdst + S::tile_bytes;
+                        mbar_expect_tx(&full[s], S::stage_bytes);
 #pragma unroll
-                    for (int h = 0; h < S::halves; ++h) {
-                        tma_load_2d(kdst + h * kHalfTileBytes, &kmap, h * 64, y, &full[s]);
-                        tma_load_2d(vdst + h * kHalfTileBytes, &vmap, h * 64, y, &full[s]);
+                        for (int h = 0; h < S::halves; ++h) {
+                            tma_load_2d(kdst + h * kHalfTileBytes, &kmap, h * 64, y, &full[s]);
+                            tma_load_2d(vdst + h * kHalfTileBytes, &vmap, h * 64, y, &full[s]);
+                        }
                     }
                 }
+                alive = __shfl_sync(0xffffffffu, alive, 0);
             }
-            alive = __shfl_sync(0xffffffffu, alive, 0);
+            walked += pages;
+            if (!alive) break;   // the consumers run into their own bounded waits
+            continue;
         }
-    } else {
+
         // ---- consumers ----
+        float m_row[2] = {-INFINITY, -INFINITY}, l_row[2] = {0.0f, 0.0f};
+        float o[HD / 8][4];
+#pragma unroll
+        for (int j = 0; j < HD / 8; ++j) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.0f;
         const int g = lane >> 2, t = lane & 3;
         uint32_t qa[HD / 16][4];
         // this thread's two fragment rows: position and head inside the item, and the keys each may see
@@ -222,11 +246,13 @@ __global__ void __launch_bounds__(kFastThreads) attention_mma_kernel(const __gri
         const int group_index = warp / kGroupWarps;
         const int mi = lane >> 3, ri = lane & 7;
         bool alive = true;
-        for (int i = group_index; i < pages && alive; i += kConsumerWarps / kGroupWarps) {
-            const int s = i % S::stages;
-            const uint32_t phase = (i / S::stages) & 1;
+        // the two warp groups alternate over the CTA's pages as a whole, not per item: stage n belongs to group n % 2
+        for (int i = (group_index + walked) & 1; i < pages && alive; i += kConsumerWarps / kGroupWarps) {
+            const int n = walked + i;
+            const int s = n % S::stages;
+            const uint32_t phase = (n / S::stages) & 1;
             if (!mbar_wait(&full[s], phase)) {
-                if (lane == 0) atomicExch(p.status, B200_DEVICE_TIMEOUT);
+                if (lane == 0) { atomicExch(p.status, B200_DEVICE_TIMEOUT); *gave_up = 1; }
                 alive = false;
                 break;
             }
@@ -235,7 +261,7 @@ __global__ void __launch_bounds__(kFastThreads) attention_mma_kernel(const __gri
 
             float sc[2][4];
 #pragma unroll
-            for (int n = 0; n < 2; ++n) sc[n][0] = sc[n][1] = sc[n][2] = sc[n][3] = 0.0f;
+            for (int n2 = 0; n2 < 2; ++n2) sc[n2][0] = sc[n2][1] = sc[n2][2] = sc[n2][3] = 0.0f;
 #pragma unroll
             for (int kk = 0; kk < HD / 16; ++kk) {
                 uint32_t r[4];
@@ -247,12 +273,12 @@ __global__ void __launch_bounds__(kFastThreads) attention_mma_kernel(const __gri
             const int token_base = (page_begin + i) * kFastPageSize + tok0 + 2 * t;
             float mx[2] = {-INFINITY, -INFINITY};
 #pragma unroll
-            for (int n = 0; n < 2; ++n)
+            for (int n2 = 0; n2 < 2; ++n2)
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
-                    const int token = token_base + n * 8 + (e & 1);
-                    const float v = token < (MULTI ? ((e >> 1) ? limit1 : limit0) : kv_len) ? sc[n][e] * p.scale : -INFINITY;
-                    sc[n][e] = v;
+                    const int token = token_base + n2 * 8 + (e & 1);
+                    const float v = token < (MULTI ? ((e >> 1) ? limit1 : limit0) : kv_len) ? sc[n2][e] * p.scale : -INFINITY;
+                    sc[n2][e] = v;
                     mx[e >> 1] = fmaxf(mx[e >> 1], v);
                 }
             float corr[2], safe[2];
@@ -267,11 +293,11 @@ __global__ void __launch_bounds__(kFastThreads) attention_mma_kernel(const __gri
             }
             float sum[2] = {0.0f, 0.0f};
 #pragma unroll
-            for (int n = 0; n < 2; ++n)
+            for (int n2 = 0; n2 < 2; ++n2)
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
-                    sc[n][e] = expf(sc[n][e] - safe[e >> 1]);
-                    sum[e >> 1] += sc[n][e];
+                    sc[n2][e] = expf(sc[n2][e] - safe[e >> 1]);
+                    sum[e >> 1] += sc[n2][e];
                 }
             l_row[0] = l_row[0] * corr[0] + sum[0];
             l_row[1] = l_row[1] * corr[1] + sum[1];
@@ -295,58 +321,56 @@ __global__ void __launch_bounds__(kFastThreads) attention_mma_kernel(const __gri
             __syncwarp();
             if (lane == 0) mbar_arrive(&empty[s]);
         }
+        walked += pages;
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
             l_row[h] += __shfl_xor_sync(0xffffffffu, l_row[h], 1);
             l_row[h] += __shfl_xor_sync(0xffffffffu, l_row[h], 2);
         }
-    }
-    __syncthreads();  // every page has been consumed: the stage memory can be reused for the merge
-
-    float* merge_o = reinterpret_cast<float*>(smem);                       // [warps][group][HD]
-    float* merge_ml = merge_o + kConsumerWarps * 16 * HD;                   // [warps][16][2]
-    if (warp < kConsumerWarps) {
-        const int g = lane >> 2, t = lane & 3;
+        // Every consumer warp is through its pages: without PERSIST the whole ring is drained and serves the merge; with it
+        // the merge has its own memory, which the previous item's readers have left (second barrier below).
+        consumer_barrier();
+        if (*gave_up) break;   // the same for every consumer warp after the barrier: nobody is left waiting at the next one
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
             const int r = g + 8 * h;
             if (r < group * t_count) {
-                float* dst = merge_o + (warp * 16 + r) * HD + 2 * t;
+                float* dst = merge_o + (warp * merge_rows + r) * HD + 2 * t;
 #pragma unroll
                 for (int j = 0; j < HD / 8; ++j) {
                     dst[j * 8] = o[j][2 * h];
                     dst[j * 8 + 1] = o[j][2 * h + 1];
                 }
                 if (t == 0) {
-                    merge_ml[(warp * 16 + r) * 2] = m_row[h];
-                    merge_ml[(warp * 16 + r) * 2 + 1] = l_row[h];
+                    merge_ml[(warp * merge_rows + r) * 2] = m_row[h];
+                    merge_ml[(warp * merge_rows + r) * 2 + 1] = l_row[h];
                 }
             }
         }
-    }
-    __syncthreads();
-    for (int i = threadIdx.x; i < group * t_count * HD; i += kFastThreads) {
-        const int r = i / HD, d = i - r * HD;
-        float m = -INFINITY;
+        consumer_barrier();
+        for (int i = threadIdx.x; i < group * t_count * HD; i += kConsumerWarps * 32) {
+            const int r = i / HD, d = i - r * HD;
+            float m = -INFINITY;
 #pragma unroll
-        for (int w = 0; w < kConsumerWarps; ++w) m = fmaxf(m, merge_ml[(w * 16 + r) * 2]);
-        float acc = 0.0f, l = 0.0f;
+            for (int w = 0; w < kConsumerWarps; ++w) m = fmaxf(m, merge_ml[(w * merge_rows + r) * 2]);
+            float acc = 0.0f, l = 0.0f;
 #pragma unroll
-        for (int w = 0; w < kConsumerWarps; ++w) {
-            const float mw = merge_ml[(w * 16 + r) * 2];
-            const float weight = mw == -INFINITY ? 0.0f : expf(mw - m);
-            acc += weight * merge_o[(w * 16 + r) * HD + d];
-            l += weight * merge_ml[(w * 16 + r) * 2 + 1];
-        }
-        const int position = MULTI ? r / group : 0;
-        const int64_t head_item = static_cast<int64_t>(row + position) * p.heads + kvh * group + (r - position * group);
-        if (p.num_splits == 1) {
-            store_result(p, head_item * HD + d, acc / l);
-        } else {
-            p.part_o[(head_item * p.num_splits + split) * HD + d] = acc;
-            if (d == 0) {
-                p.part_ml[(head_item * p.num_splits + split) * 2] = m;
-                p.part_ml[(head_item * p.num_splits + split) * 2 + 1] = l;
+            for (int w = 0; w < kConsumerWarps; ++w) {
+                const float mw = merge_ml[(w * merge_rows + r) * 2];
+                const float weight = mw == -INFINITY ? 0.0f : expf(mw - m);
+                acc += weight * merge_o[(w * merge_rows + r) * HD + d];
+                l += weight * merge_ml[(w * merge_rows + r) * 2 + 1];
+            }
+            const int position = MULTI ? r / group : 0;
+            const int64_t head_item = static_cast<int64_t>(row + position) * p.heads + kvh * group + (r - position * group);
+            if (p.num_splits == 1) {
+                store_result(p, head_item * HD + d, acc / l);
+            } else {
+                p.part_o[(head_item * p.num_splits + split) * HD + d] = acc;
+                if (d == 0) {
+                    p.part_ml[(head_item * p.num_splits + split) * 2] = m;
+                    p.part_ml[(head_item * p.num_splits + split) * 2 + 1] = l;
+                }
             }
         }
     }
@@ -455,12 +479,37 @@ __global__ void attention_combine_kernel(const AttnParams p) {
     }
 }
 
-template <int HD, int STAGES> int launch_fast(const b200_kv_cache* cache, const AttnParams& p, cudaStream_t stream) {
+template <int HD, int STAGES> int launch_fast(const b200_kv_cache* cache, AttnParams p, cudaStream_t stream) {
     using S = FastShape<HD, STAGES>;
-    auto kernel = p.positions_per_item > 1 ? attention_mma_kernel<HD, STAGES, true> : attention_mma_kernel<HD, STAGES, false>;
-    B200_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, S::smem_bytes));
     const int blocks_per_sequence = (p.tokens_per_sequence + p.positions_per_item - 1) / p.positions_per_item;
-    const dim3 grid(static_cast<unsigned>(p.rows / p.tokens_per_sequence) * blocks_per_sequence * p.kv.kv_heads, p.num_splits);
+    const int items = (p.rows / p.tokens_per_sequence) * blocks_per_sequence * p.kv.kv_heads;
+    int device = 0;
+    B200_CUDA(cudaGetDevice(&device));
+    // Decode, one CTA per item, more items than the SMs hold at once: persistent CTAs that stream across item boundaries.
+    const int group = p.heads / p.kv.kv_heads;
+    const int merge_bytes = kConsumerWarps * group * (HD + 2) * static_cast<int>(sizeof(float));
+    const int persist_bytes = S::smem_bytes + merge_bytes;   // the merge area follows the control block
+    if (p.positions_per_item == 1 && p.num_splits == 1 && persist_bytes <= 232448 && items > sm_count(device)) {
+        auto kernel = attention_mma_kernel<HD, STAGES, false, true>;
+        B200_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, persist_bytes));
+        int per_sm = 0;   // CTAs of this kernel an SM holds at once, asked of the runtime (1 if it cannot say)
+        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, kFastThreads, static_cast<size_t>(persist_bytes)) != cudaSuccess || per_sm < 1) {
+            cudaGetLastError();
+            per_sm = 1;
+        }
+        const int resident = per_sm * sm_count(device);
+        if (items <= resident) {   // every item has a CTA of its own anyway
+            p.items = items;
+            return cuda_status(launch_dependent(kernel, dim3(static_cast<unsigned>(items)), dim3(kFastThreads), static_cast<size_t>(persist_bytes),
+                                                stream, *kv_tensor_map(cache, 0), *kv_tensor_map(cache, 1), p), "attention_mma_kernel launch");
+        }
+        p.items = items;
+        return cuda_status(launch_dependent(kernel, dim3(static_cast<unsigned>(resident)), dim3(kFastThreads), static_cast<size_t>(persist_bytes),
+                                            stream, *kv_tensor_map(cache, 0), *kv_tensor_map(cache, 1), p), "attention_mma_kernel launch");
+    }
+    auto kernel = p.positions_per_item > 1 ? attention_mma_kernel<HD, STAGES, true, false> : attention_mma_kernel<HD, STAGES, false, false>;
+    B200_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, S::smem_bytes));
+    const dim3 grid(static_cast<unsigned>(items), p.num_splits);
     return cuda_status(launch_dependent(kernel, grid, dim3(kFastThreads), S::smem_bytes, stream, *kv_tensor_map(cache, 0),
                                         *kv_tensor_map(cache, 1), p), "attention_mma_kernel launch");
 }

@@ -230,6 +230,10 @@ def attention(q, cache, L, heads, max_length, causal=1):
     (B.BF16, 128, 8, 8, [300]),                        # G = 1
     (B.BF16, 64, 16, 1, [129, 77]),                    # G = 16
     (B.BF16, 32, 8, 2, [40, 90]),                      # bf16 pool on the generic path
+    # more unsplit items than the GPU holds at once: persistent CTAs walk several items each, their producer warp running
+    # into the next item's pages while the current one is merged (96 x 8 = 768 items, two CTAs per SM; 200 x 2 = 400, one)
+    (B.BF16, 64, 32, 8, [1 + (37 * s) % 700 for s in range(96)]),
+    (B.BF16, 128, 8, 2, [1 + (53 * s) % 900 for s in range(200)]),
 ])
 def test_decode_attention_ragged(cache_dtype, hd, heads, kv_heads, lengths):
     """One new token per sequence, per-sequence context lengths, shuffled physical pages."""
