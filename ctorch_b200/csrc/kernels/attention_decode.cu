@@ -127,7 +127,7 @@ __device__ __forceinline__ int balanced_pages_per_split(int pages, int planned) 
 
 // MULTI: items of several positions (prefill chunks); the decode instantiation keeps one position per item and one key
 // count for all of its rows.
-// PERSIST (decode, unsplit items, more items than resident CTAs): a CTA walks the items blockIdx.x, + gridDim.x, ... and its
+// PERSIST (decode, more units of work than resident CTAs): a CTA walks the units blockIdx.x, + gridDim.x, ... and its
 // producer warp runs ahead into the next item's pages while the consumers finish the current one, so the K/V stream of an
 // SM does not stop at item boundaries (an item of 17 pages is ~290 KB: a sixth of its time was pipeline ramp).  The
 // cross-warp merge then has its own shared memory behind the ring instead of re-using drained stages.
@@ -161,8 +161,8 @@ __global__ void __launch_bounds__(kFastThreads) attention_mma_kernel(const __gri
     const int group = p.heads / p.kv.kv_heads;
     const int positions = MULTI ? p.positions_per_item : 1;
     const int blocks_per_sequence = (p.tokens_per_sequence + positions - 1) / positions;
-    const int split = PERSIST ? 0 : static_cast<int>(blockIdx.y);
-    const int items = PERSIST ? p.items : static_cast<int>(blockIdx.x) + 1;
+    // units of work: (item, split of its pages); without PERSIST the grid has one CTA per unit
+    const int units = PERSIST ? p.items * p.num_splits : static_cast<int>(blockIdx.x) + 1;
     // the cross-warp merge: [warps][16][HD] partial outputs and [warps][16][2] (max, sum); PERSIST keeps only the rows of a
     // decode item ([warps][group][...]) in its own memory behind the barriers
     float* merge_o = PERSIST ? reinterpret_cast<float*>(smem + S::stages * S::stage_bytes + kFastControlBytes) : reinterpret_cast<float*>(smem);
@@ -170,7 +170,9 @@ __global__ void __launch_bounds__(kFastThreads) attention_mma_kernel(const __gri
     float* merge_ml = merge_o + kConsumerWarps * merge_rows * HD;
     int walked = 0;   // pages this CTA has been through before the current item: stage and phase follow from it
 
-    for (int item = blockIdx.x; item < items; item += gridDim.x) {
+    for (int unit = blockIdx.x; unit < units; unit += gridDim.x) {
+        const int item = PERSIST ? unit / p.num_splits : unit;
+        const int split = PERSIST ? unit - item * p.num_splits : static_cast<int>(blockIdx.y);
         const int kvh = item % p.kv.kv_heads, block = item / p.kv.kv_heads;
         const int sequence = block / blocks_per_sequence;
         const int t_first = (block - sequence * blocks_per_sequence) * positions;
@@ -485,11 +487,14 @@ template <int HD, int STAGES> int launch_fast(const b200_kv_cache* cache, AttnPa
     const int items = (p.rows / p.tokens_per_sequence) * blocks_per_sequence * p.kv.kv_heads;
     int device = 0;
     B200_CUDA(cudaGetDevice(&device));
-    // Decode, one CTA per item, more items than the SMs hold at once: persistent CTAs that stream across item boundaries.
+    // Decode with more units of work than the SMs hold at once: persistent CTAs that stream across unit boundaries.
     const int group = p.heads / p.kv.kv_heads;
     const int merge_bytes = kConsumerWarps * group * (HD + 2) * static_cast<int>(sizeof(float));
     const int persist_bytes = S::smem_bytes + merge_bytes;   // the merge area follows the control block
-    if (p.positions_per_item == 1 && p.num_splits == 1 && persist_bytes <= 232448 && items > sm_count(device)) {
+    // With split items the units are dealt out in turn, which only balances when the sequences are equally long (what
+    // the cache's owner knows on the host); ragged split batches keep one CTA per unit and the hardware's scheduling.
+    if (p.positions_per_item == 1 && persist_bytes <= 232448 && static_cast<int64_t>(items) * p.num_splits > sm_count(device)
+        && (p.num_splits == 1 || cache->even_lengths)) {
         auto kernel = attention_mma_kernel<HD, STAGES, false, true>;
         B200_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, persist_bytes));
         int per_sm = 0;   // CTAs of this kernel an SM holds at once, asked of the runtime (1 if it cannot say)
@@ -498,10 +503,11 @@ template <int HD, int STAGES> int launch_fast(const b200_kv_cache* cache, AttnPa
             per_sm = 1;
         }
         const int resident = per_sm * sm_count(device);
-        if (items <= resident) {   // every item has a CTA of its own anyway
-            p.items = items;
-            return cuda_status(launch_dependent(kernel, dim3(static_cast<unsigned>(items)), dim3(kFastThreads), static_cast<size_t>(persist_bytes),
-                                                stream, *kv_tensor_map(cache, 0), *kv_tensor_map(cache, 1), p), "attention_mma_kernel launch");
+        p.items = items;
+        if (items * p.num_splits <= resident) {   // every unit has a CTA of its own anyway
+            return cuda_status(launch_dependent(kernel, dim3(static_cast<unsigned>(items * p.num_splits)), dim3(kFastThreads),
+                                                static_cast<size_t>(persist_bytes), stream, *kv_tensor_map(cache, 0), *kv_tensor_map(cache, 1), p),
+                               "attention_mma_kernel launch");
         }
         p.items = items;
         return cuda_status(launch_dependent(kernel, dim3(static_cast<unsigned>(resident)), dim3(kFastThreads), static_cast<size_t>(persist_bytes),

@@ -128,6 +128,7 @@ int b200_kv_cache_create(int32_t device, int32_t dtype, int32_t sequences, int32
     if (e != cudaSuccess) return fail(cuda_status(e, "cudaMemcpy(page table)"));
     e = cudaMemset(c->lengths, 0, sizeof(int32_t) * sequences);
     if (e != cudaSuccess) return fail(cuda_status(e, "cudaMemset(lengths)"));
+    c->even_lengths = true;
     const int status = make_maps(c);
     if (status != B200_OK) return fail(status);
     *out = c;
@@ -147,11 +148,14 @@ int b200_kv_cache_set_lengths(b200_kv_cache* c, const int32_t* host_lengths, voi
         if (host_lengths[s] < 0 || host_lengths[s] > c->capacity) { set_error("KV cache length outside [0, capacity]"); return B200_BAD_ARGUMENT; }
     B200_CUDA(cudaMemcpyAsync(c->lengths, host_lengths, sizeof(int32_t) * c->sequences, cudaMemcpyHostToDevice, as_stream(stream)));
     B200_CUDA(cudaStreamSynchronize(as_stream(stream)));  // host_lengths may be pageable and reused by the caller
+    c->even_lengths = true;
+    for (int s = 1; s < c->sequences; ++s) c->even_lengths = c->even_lengths && host_lengths[s] == host_lengths[0];
     return B200_OK;
 }
 int b200_kv_cache_fill_lengths(b200_kv_cache* c, int32_t length, void* stream) {
     if (!c || length < 0 || length > c->capacity) { set_error("KV cache length outside [0, capacity]"); return B200_BAD_ARGUMENT; }
     fill_lengths_kernel<<<(c->sequences + 127) / 128, 128, 0, as_stream(stream)>>>(c->lengths, c->sequences, length);
+    c->even_lengths = true;
     return cuda_status(cudaGetLastError(), "fill_lengths_kernel launch");
 }
 int b200_kv_cache_set_page_table(b200_kv_cache* c, const int32_t* host_table, void* stream) {

@@ -60,5 +60,6 @@ struct b200_kv_cache {
     int32_t* page_table;
     int32_t* lengths;
     bool has_maps;
+    bool even_lengths;   // host-side knowledge: every sequence has the same length (set_lengths with unequal entries clears it)
     alignas(64) CUtensorMap map[2];
 };
