@@ -127,11 +127,7 @@ __device__ __forceinline__ int balanced_pages_per_split(int pages, int planned) 
 
 // MULTI: items of several positions (prefill chunks); the decode instantiation keeps one position per item and one key
 // count for all of its rows.
-// PERSIST (decode, more units of work than resident CTAs): a CTA walks the units blockIdx.x, + gridDim.x, ... and its
-// producer warp runs ahead into the next item's pages while the consumers finish the current one, so the K/V stream of an
-// SM does not stop at item boundaries (an item of 17 pages is ~290 KB: a sixth of its time was pipeline ramp).  The
-// cross-warp merge then has its own shared memory behind the ring instead of re-using drained stages.
-template <int HD, int STAGES, bool MULTI, bool PERSIST>
+template <int HD, int STAGES, bool MULTI>
 __global__ void __launch_bounds__(kFastThreads) attention_mma_kernel(const __grid_constant__ CUtensorMap kmap,
                                                                      const __grid_constant__ CUtensorMap vmap,
                                                                      const AttnParams p) {
@@ -140,9 +136,247 @@ __global__ void __launch_bounds__(kFastThreads) attention_mma_kernel(const __gri
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
     uint64_t* full = reinterpret_cast<uint64_t*>(smem + S::stages * S::stage_bytes);
     uint64_t* empty = full + S::stages;
+
+    grid_dependency_wait();   // q, the cache and the lengths come from the preceding kernels
+    grid_launch_dependents();
+    // An item is (sequence, block of consecutive positions, KV head).  The 16 fragment rows of a warp hold the block's
+    // positions times the head group: row r = position r / group, query head r % group.  Decode: one position, rows =
+    // the group.  Prefill: 16 / group positions share every K/V byte the CTA streams.
+    const int item = blockIdx.x, split = blockIdx.y;
+    const int kvh = item % p.kv.kv_heads, block = item / p.kv.kv_heads;
+    const int positions = MULTI ? p.positions_per_item : 1;
+    const int blocks_per_sequence = (p.tokens_per_sequence + positions - 1) / positions;
+    const int sequence = block / blocks_per_sequence;
+    const int t_first = (block - sequence * blocks_per_sequence) * positions;
+    const int t_count = MULTI ? min(positions, p.tokens_per_sequence - t_first) : 1;
+    const int row = sequence * p.tokens_per_sequence + t_first;   // first activation row of the item
+    const int base_len = p.kv.lengths[sequence];
+    const int kv_len = base_len + (p.causal ? t_first + t_count : 0);   // keys the item's last position sees
+    int page_end = (kv_len + kFastPageSize - 1) / kFastPageSize;
+    const int per_split = balanced_pages_per_split(page_end, p.pages_per_split);
+    const int page_begin = split * per_split;
+    if (page_end > page_begin + per_split) page_end = page_begin + per_split;
+    if (page_begin >= page_end) return;  // uniform for the CTA
+    const int pages = page_end - page_begin;
+    const int group = p.heads / p.kv.kv_heads;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < S::stages; ++s) {
+            mbar_init(&full[s], 1);
+            mbar_init(&empty[s], kGroupWarps);
+        }
+        mbar_fence_init();
+    }
+    __syncthreads();
+
+    float m_row[2] = {-INFINITY, -INFINITY}, l_row[2] = {0.0f, 0.0f};
+    float o[HD / 8][4];
+#pragma unroll
+    for (int j = 0; j < HD / 8; ++j) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.0f;
+
+    if (warp == kConsumerWarps) {
+        // ---- producer: all lanes walk the loop together, lane 0 waits and issues ----
+        if (lane == 0) { tma_prefetch_descriptor(&kmap); tma_prefetch_descriptor(&vmap); }
+        const int32_t* table = p.kv.page_table + static_cast<int64_t>(sequence) * p.kv.pages_per_seq + page_begin;
+        bool alive = true;
+        for (int i = 0; i < pages && alive; ++i) {
+            if (lane == 0) {
+                const int s = i % S::stages;
+                const uint32_t phase = (i / S::stages) & 1;
+                if (!mbar_wait(&empty[s], phase ^ 1)) {
+                    atomicExch(p.status, B200_DEVICE_TIMEOUT);
+                    alive = false;
+                } else {
+                    const int page = table[i];
+                    const int y = (page * p.kv.kv_heads + kvh) * kFastPageSize;
+                    uint8_t* kdst = smem + s * S::stage_bytes;
+                    uint8_t* vdst = kdst + S::tile_bytes;
+                    mbar_expect_tx(&full[s], S::stage_bytes);
+#pragma unroll
+                    for (int h = 0; h < S::halves; ++h) {
+                        tma_load_2d(kdst + h * kHalfTileBytes, &kmap, h * 64, y, &full[s]);
+                        tma_load_2d(vdst + h * kHalfTileBytes, &vmap, h * 64, y, &full[s]);
+                    }
+                }
+            }
+            alive = __shfl_sync(0xffffffffu, alive, 0);
+        }
+    } else {
+        // ---- consumers ----
+        const int g = lane >> 2, t = lane & 3;
+        uint32_t qa[HD / 16][4];
+        // this thread's two fragment rows: position and head inside the item, and the keys each may see
+        const int pos0 = MULTI ? g / group : 0, pos1 = MULTI ? (g + 8) / group : 0;
+        const bool v0 = g < group * t_count, v1 = g + 8 < group * t_count;
+        const int limit0 = MULTI ? (v0 ? base_len + (p.causal ? t_first + pos0 + 1 : 0) : 0) : kv_len;
+        const int limit1 = MULTI ? (v1 ? base_len + (p.causal ? t_first + pos1 + 1 : 0) : 0) : kv_len;
+        {
+            const float* q0 = p.q + (static_cast<int64_t>(row + pos0) * p.heads + kvh * group + (g - pos0 * group)) * HD;
+            const float* q1 = p.q + (static_cast<int64_t>(row + pos1) * p.heads + kvh * group + (g + 8 - pos1 * group)) * HD;
+#pragma unroll
+            for (int kk = 0; kk < HD / 16; ++kk) {
+                const int c = kk * 16 + 2 * t;
+                qa[kk][0] = v0 ? pack_bf16(q0[c], q0[c + 1]) : 0u;
+                qa[kk][1] = v1 ? pack_bf16(q1[c], q1[c + 1]) : 0u;
+                qa[kk][2] = v0 ? pack_bf16(q0[c + 8], q0[c + 9]) : 0u;
+                qa[kk][3] = v1 ? pack_bf16(q1[c + 8], q1[c + 9]) : 0u;
+            }
+        }
+        const int tok0 = (warp & (kGroupWarps - 1)) * 16;
+        const int group_index = warp / kGroupWarps;
+        const int mi = lane >> 3, ri = lane & 7;
+        bool alive = true;
+        for (int i = group_index; i < pages && alive; i += kConsumerWarps / kGroupWarps) {
+            const int s = i % S::stages;
+            const uint32_t phase = (i / S::stages) & 1;
+            if (!mbar_wait(&full[s], phase)) {
+                if (lane == 0) atomicExch(p.status, B200_DEVICE_TIMEOUT);
+                alive = false;
+                break;
+            }
+            const uint32_t kbase = smem_u32(smem + s * S::stage_bytes);
+            const uint32_t vbase = kbase + S::tile_bytes;
+
+            float sc[2][4];
+#pragma unroll
+            for (int n = 0; n < 2; ++n) sc[n][0] = sc[n][1] = sc[n][2] = sc[n][3] = 0.0f;
+#pragma unroll
+            for (int kk = 0; kk < HD / 16; ++kk) {
+                uint32_t r[4];
+                ldmatrix_x4(r, kbase + tile_offset(tok0 + (mi >> 1) * 8 + ri, 2 * kk + (mi & 1)));
+                mma_bf16(sc[0], qa[kk], r[0], r[1]);
+                mma_bf16(sc[1], qa[kk], r[2], r[3]);
+            }
+            // scale, mask keys at or beyond the row's key count, online softmax per row (g and g+8)
+            const int token_base = (page_begin + i) * kFastPageSize + tok0 + 2 * t;
+            float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+            for (int n = 0; n < 2; ++n)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int token = token_base + n * 8 + (e & 1);
+                    const float v = token < (MULTI ? ((e >> 1) ? limit1 : limit0) : kv_len) ? sc[n][e] * p.scale : -INFINITY;
+                    sc[n][e] = v;
+                    mx[e >> 1] = fmaxf(mx[e >> 1], v);
+                }
+            float corr[2], safe[2];
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 1));
+                mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 2));
+                const float m_new = fmaxf(m_row[h], mx[h]);
+                safe[h] = m_new == -INFINITY ? 0.0f : m_new;
+                corr[h] = expf(m_row[h] - safe[h]);
+                m_row[h] = m_new;
+            }
+            float sum[2] = {0.0f, 0.0f};
+#pragma unroll
+            for (int n = 0; n < 2; ++n)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    sc[n][e] = expf(sc[n][e] - safe[e >> 1]);
+                    sum[e >> 1] += sc[n][e];
+                }
+            l_row[0] = l_row[0] * corr[0] + sum[0];
+            l_row[1] = l_row[1] * corr[1] + sum[1];
+#pragma unroll
+            for (int j = 0; j < HD / 8; ++j) {
+                o[j][0] *= corr[0]; o[j][1] *= corr[0];
+                o[j][2] *= corr[1]; o[j][3] *= corr[1];
+            }
+            uint32_t pa[4];
+            pa[0] = pack_bf16(sc[0][0], sc[0][1]);
+            pa[1] = pack_bf16(sc[0][2], sc[0][3]);
+            pa[2] = pack_bf16(sc[1][0], sc[1][1]);
+            pa[3] = pack_bf16(sc[1][2], sc[1][3]);
+#pragma unroll
+            for (int j = 0; j < HD / 8; j += 2) {
+                uint32_t r[4];
+                ldmatrix_x4_trans(r, vbase + tile_offset(tok0 + (mi & 1) * 8 + ri, j + (mi >> 1)));
+                mma_bf16(o[j], pa, r[0], r[1]);
+                mma_bf16(o[j + 1], pa, r[2], r[3]);
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&empty[s]);
+        }
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            l_row[h] += __shfl_xor_sync(0xffffffffu, l_row[h], 1);
+            l_row[h] += __shfl_xor_sync(0xffffffffu, l_row[h], 2);
+        }
+    }
+    __syncthreads();  // every page has been consumed: the stage memory can be reused for the merge
+
+    float* merge_o = reinterpret_cast<float*>(smem);                       // [warps][group][HD]
+    float* merge_ml = merge_o + kConsumerWarps * 16 * HD;                   // [warps][16][2]
+    if (warp < kConsumerWarps) {
+        const int g = lane >> 2, t = lane & 3;
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const int r = g + 8 * h;
+            if (r < group * t_count) {
+                float* dst = merge_o + (warp * 16 + r) * HD + 2 * t;
+#pragma unroll
+                for (int j = 0; j < HD / 8; ++j) {
+                    dst[j * 8] = o[j][2 * h];
+                    dst[j * 8 + 1] = o[j][2 * h + 1];
+                }
+                if (t == 0) {
+                    merge_ml[(warp * 16 + r) * 2] = m_row[h];
+                    merge_ml[(warp * 16 + r) * 2 + 1] = l_row[h];
+                }
+            }
+        }
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < group * t_count * HD; i += kFastThreads) {
+        const int r = i / HD, d = i - r * HD;
+        float m = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < kConsumerWarps; ++w) m = fmaxf(m, merge_ml[(w * 16 + r) * 2]);
+        float acc = 0.0f, l = 0.0f;
+#pragma unroll
+        for (int w = 0; w < kConsumerWarps; ++w) {
+            const float mw = merge_ml[(w * 16 + r) * 2];
+            const float weight = mw == -INFINITY ? 0.0f : expf(mw - m);
+            acc += weight * merge_o[(w * 16 + r) * HD + d];
+            l += weight * merge_ml[(w * 16 + r) * 2 + 1];
+        }
+        const int position = MULTI ? r / group : 0;
+        const int64_t head_item = static_cast<int64_t>(row + position) * p.heads + kvh * group + (r - position * group);
+        if (p.num_splits == 1) {
+            store_result(p, head_item * HD + d, acc / l);
+        } else {
+            p.part_o[(head_item * p.num_splits + split) * HD + d] = acc;
+            if (d == 0) {
+                p.part_ml[(head_item * p.num_splits + split) * 2] = m;
+                p.part_ml[(head_item * p.num_splits + split) * 2 + 1] = l;
+            }
+        }
+    }
+}
+
+// The same kernel for decode with more units of work (item, split of its pages) than resident CTAs: a CTA walks the units
+// blockIdx.x, + gridDim.x, ... and its
+// producer warp runs ahead into the next item's pages while the consumers finish the current one, so the K/V stream of an
+// SM does not stop at item boundaries (an item of 17 pages is ~290 KB: a sixth of its time was pipeline ramp).  The
+// cross-warp merge then has its own shared memory behind the ring instead of re-using drained stages.
+template <int HD, int STAGES>
+__global__ void __launch_bounds__(kFastThreads) attention_persistent_kernel(const __grid_constant__ CUtensorMap kmap,
+                                                                     const __grid_constant__ CUtensorMap vmap,
+                                                                     const AttnParams p) {
+    using S = FastShape<HD, STAGES>;
+    constexpr bool MULTI = false, PERSIST = true;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+    uint64_t* full = reinterpret_cast<uint64_t*>(smem + S::stages * S::stage_bytes);
+    uint64_t* empty = full + S::stages;
     volatile int* gave_up = reinterpret_cast<volatile int*>(smem + S::stages * S::stage_bytes + 192);   // a consumer's wait ran out
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    grid_dependency_wait();   // q, the cache and the lengths come from the preceding kernels
+    grid_launch_dependents();
     if (threadIdx.x == 0) {
         for (int s = 0; s < S::stages; ++s) {
             mbar_init(&full[s], 1);
@@ -152,8 +386,6 @@ __global__ void __launch_bounds__(kFastThreads) attention_mma_kernel(const __gri
         mbar_fence_init();
     }
     __syncthreads();
-    grid_dependency_wait();   // q, the cache and the lengths come from the preceding kernels
-    grid_launch_dependents();
 
     // An item is (sequence, block of consecutive positions, KV head).  The 16 fragment rows of a warp hold the block's
     // positions times the head group: row r = position r / group, query head r % group.  Decode: one position, rows =
@@ -495,7 +727,7 @@ template <int HD, int STAGES> int launch_fast(const b200_kv_cache* cache, AttnPa
     // the cache's owner knows on the host); ragged split batches keep one CTA per unit and the hardware's scheduling.
     if (p.positions_per_item == 1 && persist_bytes <= 232448 && static_cast<int64_t>(items) * p.num_splits > sm_count(device)
         && (p.num_splits == 1 || cache->even_lengths)) {
-        auto kernel = attention_mma_kernel<HD, STAGES, false, true>;
+        auto kernel = attention_persistent_kernel<HD, STAGES>;
         B200_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, persist_bytes));
         int per_sm = 0;   // CTAs of this kernel an SM holds at once, asked of the runtime (1 if it cannot say)
         if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, kFastThreads, static_cast<size_t>(persist_bytes)) != cudaSuccess || per_sm < 1) {
@@ -513,7 +745,7 @@ template <int HD, int STAGES> int launch_fast(const b200_kv_cache* cache, AttnPa
         return cuda_status(launch_dependent(kernel, dim3(static_cast<unsigned>(resident)), dim3(kFastThreads), static_cast<size_t>(persist_bytes),
                                             stream, *kv_tensor_map(cache, 0), *kv_tensor_map(cache, 1), p), "attention_mma_kernel launch");
     }
-    auto kernel = p.positions_per_item > 1 ? attention_mma_kernel<HD, STAGES, true, false> : attention_mma_kernel<HD, STAGES, false, false>;
+    auto kernel = p.positions_per_item > 1 ? attention_mma_kernel<HD, STAGES, true> : attention_mma_kernel<HD, STAGES, false>;
     B200_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, S::smem_bytes));
     const dim3 grid(static_cast<unsigned>(items), p.num_splits);
     return cuda_status(launch_dependent(kernel, grid, dim3(kFastThreads), S::smem_bytes, stream, *kv_tensor_map(cache, 0),
