@@ -155,6 +155,7 @@ def _declare(l: C.CDLL) -> None:
         "dl_generation_step_sampled": (C.c_int, [vp, C.c_double, vp, vp]),
         "b200_linear_argmax_parts": (i32, [i64, i64, i64]),
         "b200_linear_shadow_kernel": (C.c_char_p, [i64, i64, i64]),
+        "b200_linear_decode_launch_shape": (i32, [i64, i64, i64, i32, C.POINTER(i32)]),
         "b200_tp_argmax_finish": (C.c_int, [pp, i32, i32, sz, i32, vp, vp, i32, i64, vp, vp, vp, i64, vp, pp, i32, vp]),
         "b200_tp_reduce_parts": (i32, [i64]), "b200_tp_region_bytes": (sz, [sz, i32]), "b200_tp_slot": (vp, [vp, sz, i32, i32, i32]),
         "b200_tp_reduce_shadow": (C.c_int, [pp, i32, i32, i32, sz, i32, i64, i64, vp, i32, vp, vp, vp, vp, vp]),

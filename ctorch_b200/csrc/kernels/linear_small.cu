@@ -320,6 +320,19 @@ extern "C" const char* b200_linear_shadow_kernel(int64_t rows, int64_t in, int64
     return "linear_stream_kernel";
 }
 
+extern "C" int32_t b200_linear_decode_launch_shape(int64_t rows, int64_t in, int64_t out, int32_t two_planes, int32_t* shape) {
+    if (!shape || rows <= 0 || in <= 0 || out <= 0 || rows > INT32_MAX || in > INT32_MAX || out > INT32_MAX) return 0;
+    if (!b200::linear_decode_takes(static_cast<int>(rows))) return 0;
+    int device = 0;
+    const int sms = cudaGetDevice(&device) == cudaSuccess ? b200::sm_count(device) : 148;
+    cudaGetLastError();
+    const b200::DecodeShape s = b200::linear_decode_shape(static_cast<int>(rows), static_cast<int>(in), static_cast<int>(out), two_planes != 0, sms);
+    if (s.tiles == 0) return 0;
+    const int32_t values[10] = {s.tiles, s.split, s.ctas, s.stages, s.stage_bytes, s.n_pad, s.tmem_columns, s.smem_bytes, s.token_tile, s.token_tiles};
+    for (int i = 0; i < 10; ++i) shape[i] = values[i];
+    return 1;
+}
+
 extern "C" int32_t b200_linear_argmax_parts(int64_t rows, int64_t in, int64_t out) {
     if (rows <= 0 || in <= 0 || out <= 0 || rows > INT32_MAX || in > INT32_MAX || out > INT32_MAX) return 0;
     return b200::linear_argmax_parts(static_cast<int>(rows), static_cast<int>(in), static_cast<int>(out));

@@ -166,6 +166,11 @@ B200_API int32_t b200_linear_argmax_parts(int64_t rows, int64_t in, int64_t out)
  * "linear_decode_kernel": decode batches on tcgen05 with the weights as the streamed operand; "linear_gemm_kernel": more
  * rows; "linear_thin_kernel": at most 64 output features).  For logs and benchmarks. */
 B200_API const char* b200_linear_shadow_kernel(int64_t rows, int64_t in, int64_t out);
+/* Launch shape the decode-batch kernel would take for these sizes (host-side; needs no GPU - without one the figures of a
+ * 148-SM B200 are used): shape[0..9] = weight tiles per CTA, K split (cluster size), tile groups (grid y), ring stages,
+ * bytes per stage, N of the products (rows of a token tile padded to 16), tensor-memory columns, dynamic shared memory,
+ * rows per token tile, token tiles (grid x).  Returns 1, or 0 when that kernel does not take the row count.  Diagnostic. */
+B200_API int32_t b200_linear_decode_launch_shape(int64_t rows, int64_t in, int64_t out, int32_t two_planes, int32_t* shape);
 /* Second half of the fused logits + greedy choice: merges the `parts` per-tile candidates of every row (same rule), writes
  * the chosen feature index to next[rows], and does what b200_token_feedback does with it (ids, history, counter; any of
  * ids / history may be NULL).  With caches (at most 64, one per layer) it also does b200_kv_cache_advance(caches, count, 1): the

@@ -122,3 +122,40 @@ def test_partial_sum_buffers_follow_the_kernels_tilings():
         need = max(l.b200_linear_shadow_parts(rows, inner, d) for rows in (1, 16, 17, 256) for inner in (d, f))
         assert l.dl_b200_shadow_partial_rows(d, f) >= need >= 1
     assert l.dl_b200_shadow_partial_rows(0, 8) == 0
+
+
+def test_shadow_linear_dispatch_by_row_count():
+    """Which kernel family serves a shadow linear: the streaming kernel up to 16 rows (inner size up to 2048), the
+    decode-batch kernel up to 256 rows, the prefill kernel above, the thin kernel for adapter down-projections."""
+    name = lambda rows, inner, out: B.lib().b200_linear_shadow_kernel(rows, inner, out).decode()
+    assert name(1, 768, 2304) == name(16, 2048, 32000) == "linear_stream_kernel"
+    assert name(8, 4096, 6144) == "linear_decode_kernel"          # few rows, but wider than the streaming kernel's ring
+    assert name(17, 768, 2304) == name(128, 2048, 16384) == name(256, 8192, 2048) == "linear_decode_kernel"
+    assert name(257, 2048, 16384) == name(8192, 2048, 3072) == "linear_gemm_kernel"
+    assert name(32, 4096, 32) == "linear_thin_kernel"
+
+
+def test_decode_launch_shapes_fit_the_sm():
+    """The cost-model search of the decode-batch kernel, on the host: for the projection sizes of every BASELINE
+    configuration and some odd ones, at every row count it serves, the shape it picks fits an SM (227 KB of shared memory,
+    512 tensor-memory columns, a ring of at least two stages unless the CTA has a single K block) and covers the problem."""
+    shape = (C.c_int32 * 10)()
+    sizes = [(768, 2304), (768, 768), (768, 4096), (2048, 768), (768, 32000), (2048, 3072), (2048, 2048), (2048, 16384), (8192, 2048),
+             (2048, 32000), (4096, 6144), (4096, 4096), (4096, 28672), (14336, 4096), (4096, 128256), (2048, 1024), (1024, 7168),
+             (7168, 4096), (64, 128), (136, 200), (4096, 50257)]
+    for inner, out in sizes:
+        for rows in (1, 15, 16, 17, 31, 32, 33, 64, 100, 128, 129, 200, 256):
+            for planes in (0, 1):
+                assert B.lib().b200_linear_decode_launch_shape(rows, inner, out, planes, shape) == 1, (rows, inner, out)
+                tiles, split, groups, stages, stage_bytes, n_pad, tmem, smem, token_tile, token_tiles = list(shape)
+                k_blocks = -(-inner // 64)
+                per_cta = -(-k_blocks // split)
+                assert tiles in (1, 2, 4) and 1 <= split <= 8 and split <= max(1, k_blocks // 2), (rows, inner, out, list(shape))
+                assert groups * tiles * 128 >= out and (groups - 1) * tiles * 128 < out
+                assert token_tile <= 128 and token_tile * token_tiles >= rows and (token_tiles - 1) * token_tile < rows
+                assert n_pad % 16 == 0 and token_tile <= n_pad <= 128
+                assert tmem <= 512 and tmem >= tiles * n_pad and tmem & (tmem - 1) == 0
+                assert smem <= 232448 and stages * stage_bytes + 1024 <= smem
+                assert stage_bytes == tiles * 16384 + (2 if planes else 1) * n_pad * 128
+                assert 1 <= stages <= 8 and stages >= min(2, per_cta)
+    assert B.lib().b200_linear_decode_launch_shape(257, 2048, 2048, 1, shape) == 0
