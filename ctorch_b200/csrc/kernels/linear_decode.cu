@@ -1,12 +1,12 @@
-// Dense projection for decode batches (up to 128 activation rows; the code also walks token tiles of 128 for more): y = epilogue(scale_rows(x @ W^T)) with the WEIGHTS as
-// the streamed operand.  A decode step reads every weight once and the activations are small, so the kernel is built to
-// keep the weight stream going and to spend no tensor time on padding:
+// Dense projection for decode batches (up to 256 activation rows in token tiles of 128): y = epilogue(scale_rows(x @ W^T))
+// with the WEIGHTS as the streamed operand.  A decode step reads every weight once and the activations are small, so the
+// kernel is built to keep the weight stream going and to spend no tensor time on padding:
 //
 //   * operands are swapped against the prefill kernel (linear_gemm.cu): a 128-feature weight tile is the A operand
-//     (M = 128) and the tokens are the N side of tcgen05.mma (N = rows rounded up to 16).  A product costs about
-//     max(48, N / 2) cycles when it re-uses the A operand of its predecessor (the hi and lo planes of the activations
-//     are multiplied back to back against the same weight slice), so 32 rows cost a quarter of what a 128-row token tile
-//     costs; up to 128 rows one CTA covers all tokens and every weight byte crosses L2 -> SM exactly once;
+//     (M = 128) and the tokens are the N side of tcgen05.mma (N = rows of the token tile rounded up to 16).  A product
+//     costs about max(51, N / 2) cycles when it re-uses the A operand of its predecessor (the hi and lo planes of the
+//     activations are multiplied back to back against the same weight slice), so 32 rows cost less than half of what a
+//     128-row token tile costs; up to 128 rows one CTA covers all tokens and every weight byte crosses L2 -> SM once;
 //   * a CTA multiplies `tiles` (1, 2 or 4) adjacent weight tiles against each activation K block, one f32 accumulator
 //     [128 features x N tokens] per tile in tensor memory, which divides the activation bytes pulled per weight byte;
 //   * few feature tiles: K is split over a thread-block cluster (grid z, up to 8 CTAs); the partial accumulators are pushed
@@ -17,9 +17,10 @@
 //     warp 1 owns tensor memory and issues the products; both warps walk their loops as whole warps in uniform control
 //     flow, with ONE elected lane issuing a K block's instructions from fully unrolled code (tile count and plane count
 //     are template parameters): issued from a loop with run-time bounds the same products took three times as long;
-//   * warps 2-5 read the accumulators back (tcgen05.ld: one feature per thread, 32 tokens per instruction) and write them
-//     transposed into row-major [token][feature] slabs, from where all twelve warps finish token rows with the shared
-//     epilogues (linear_rows.cuh); six more warps exist only for that: a row's epilogue is a dependent chain per lane;
+//   * all twelve warps read the accumulators back (tcgen05.ld: one feature per thread, 32 tokens per instruction; three
+//     warps share a lane quarter) and write them transposed into row-major [token][feature] slabs, from where they finish
+//     token rows with the shared epilogues (linear_rows.cuh).  While the products run, warps 6-11 ask the epilogue's
+//     operands into L2 and run the epilogue's code once with its stores switched off (see the rounds below);
 //   * one kernel function serves every epilogue (run-time switch): consecutive launches of a decode step then share their
 //     instructions instead of starting cold;
 //   * the launch shape (tiles per CTA, K split, ring depth) comes from a small cost model that knows how many clusters of
@@ -237,16 +238,16 @@ __global__ void __launch_bounds__(kThreads, 1) linear_decode_kernel(const __grid
     }
 
     // ---- epilogue ----
-    // Warps 2-5 may touch TMEM lanes 32 * (warp % 4) .. + 31 = features of the weight tile; a thread holds one feature and
+    // Warp w may touch TMEM lanes 32 * (w % 4) .. + 31 = features of the weight tile; a thread holds one feature and
     // reads 32 tokens per instruction.  The token rows are divided over the cluster's CTAs (all of them here without a K
     // split).  Every CTA PUSHES its partial accumulators, transposed, into the shared memory of the CTA that owns the
     // token: slab [sender][row of the owner's band][feature] (for a fixed token the lanes of a warp write consecutive
     // features; remote stores do not wait for anything).  After one barrier over the cluster every CTA finds the partial
     // sums of its band in its own shared memory, adds them in sender order (results do not depend on timing) and
-    // finishes its rows with all six warps, lanes across the features (linear_rows.cuh).  When the slabs of all weight
+    // finishes its rows with all twelve warps, lanes across the features (linear_rows.cuh).  When the slabs of all weight
     // tiles fit the drained operand ring there is one barrier per launch and no CTA is written to after it; otherwise
     // the tiles take turns and a second barrier frees the slabs for the next one.
-    const bool finisher = warp >= 2 && warp < 6;   // the four warps that read tensor memory (lanes 32 * (warp % 4) ..)
+    const bool finisher = warp >= 2 && warp < 6;   // the four warps that prepare the rows' scales (and cache places)
     const int quarter = warp & 3;
     bool ready = false;
     if (finisher) {
