@@ -512,7 +512,7 @@ __device__ __forceinline__ void finish_rows_pairs(const LinearParams& p, const f
                     if (p.sumsq_out) {
 #pragma unroll
                         for (int o = 16; o > 0; o >>= 1) squares += __shfl_xor_sync(0xffffffffu, squares, o);
-                        if (lane == 0) p.sumsq_out[static_cast<int64_t>(feature_tile) * p.rows + row] = squares;
+                        if (lane == 0 && ready) p.sumsq_out[static_cast<int64_t>(feature_tile) * p.rows + row] = squares;
                     }
                 }
                 if constexpr (EPI == B200_EPI_ARGMAX) {
@@ -521,7 +521,7 @@ __device__ __forceinline__ void finish_rows_pairs(const LinearParams& p, const f
                         const Candidate other{__shfl_xor_sync(0xffffffffu, best.value, o), __shfl_xor_sync(0xffffffffu, best.index, o)};
                         if (preferred(other, best)) best = other;
                     }
-                    if (lane == 0) {
+                    if (lane == 0 && ready) {   // (a caller's warm-up pass hands in accumulators that are not valid: nothing is written)
                         p.best_value[static_cast<int64_t>(feature_tile) * p.rows + row] = best.value;
                         p.best_index[static_cast<int64_t>(feature_tile) * p.rows + row] = best.index;
                     }

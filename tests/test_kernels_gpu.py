@@ -400,7 +400,8 @@ def test_shadow_protocol_swiglu_and_attention_output():
                                                      (128, 72, 136, 0), (32, 4096, 1024, 1), (256, 2048, 3072, 2),
                                                      (1000, 512, 2560, 0), (20, 256, 76000, 0), (1100, 2304, 2304, 1), (40, 4096, 32, 0), (300, 768, 24, 0),
                                                      (64, 2048, 16384, 2), (256, 2048, 16384, 2), (200, 8192, 2048, 1), (96, 2048, 2048, 1),
-                                                     (32, 2048, 32000, 0), (48, 1032, 1000, 0), (257, 768, 1280, 1)])
+                                                     (32, 2048, 32000, 0), (48, 1032, 1000, 0), (257, 768, 1280, 1),
+                                                     (40, 768, 1282, 1), (24, 512, 330, 0), (150, 2048, 1282, 1)])
 def test_dense_tensor_core_linear(rows, inner, out, epilogue):
     """More than 16 rows (or a wide input) take the tcgen05 kernels: shadow input, split norm, every epilogue family.
     Up to 256 rows run on the decode-batch kernel (weights as the streamed M operand, tokens as the N side): one, two or four
@@ -409,6 +410,7 @@ def test_dense_tensor_core_linear(rows, inner, out, epilogue):
     CTAs, a row count that is no multiple of 16), ragged last tiles and K blocks ((48, 1032, 1000), (17, 4096, 200)).  More
     rows run on the prefill kernel: (1000, 512, 2560) on its persistent variant (8 token tiles, short K, more tiles than
     SMs), (1100, 2304, 2304) one tile per CTA with two CTAs per SM, (300, 768, 4096) and (257, 768, 1280) with a K split;
+    widths that are no multiple of 4 ((40, 768, 1282), (24, 512, 330), (150, 2048, 1282)) take the epilogue's pair form;
     (40, 4096, 32) and (300, 768, 24) (at most 64 output features, store epilogue: adapter down-projections) on the thin
     CUDA-core kernel."""
     l = B.lib()
