@@ -454,81 +454,81 @@ __device__ __forceinline__ void finish_rows_pairs(const LinearParams& p, const f
                                             const float* row_scale, int m0, int n0, int feature_tile, int first, int last, int worker,
                                             int workers, int lane, bool ready, const int2* row_place) {
     constexpr int kTileStride = kTileN + 4;
-        constexpr int kBatch = 4, kPasses = kTileN / 64;
-        for (int base = first + worker * kBatch; base < last; base += workers * kBatch) {
-            float2 value[kBatch][kPasses], carried[kBatch][kPasses];
+    constexpr int kBatch = 4, kPasses = kTileN / 64;
+    for (int base = first + worker * kBatch; base < last; base += workers * kBatch) {
+        float2 value[kBatch][kPasses], carried[kBatch][kPasses];
 #pragma unroll
-            for (int r = 0; r < kBatch; ++r) {
-                const int tile_row = base + r, row = m0 + tile_row;
-                const bool live_row = tile_row < last && row < p.rows;
+        for (int r = 0; r < kBatch; ++r) {
+            const int tile_row = base + r, row = m0 + tile_row;
+            const bool live_row = tile_row < last && row < p.rows;
 #pragma unroll
-                for (int pass = 0; pass < kPasses; ++pass) {
-                    const int c = pass * 64 + lane * 2;
-                    const int feature0 = n0 + c;
-                    value[r][pass] = make_float2(0.0f, 0.0f);
-                    carried[r][pass] = make_float2(0.0f, 0.0f);
-                    if (!live_row) continue;
-                    if (split == 1) {
-                        value[r][pass] = *reinterpret_cast<const float2*>(tile + tile_row * kTileStride + c);
-                    } else {
-                        const uint32_t offset = static_cast<uint32_t>(tile_row * kTileStride + c) * 4;
-                        float2 v[8];
+            for (int pass = 0; pass < kPasses; ++pass) {
+                const int c = pass * 64 + lane * 2;
+                const int feature0 = n0 + c;
+                value[r][pass] = make_float2(0.0f, 0.0f);
+                carried[r][pass] = make_float2(0.0f, 0.0f);
+                if (!live_row) continue;
+                if (split == 1) {
+                    value[r][pass] = *reinterpret_cast<const float2*>(tile + tile_row * kTileStride + c);
+                } else {
+                    const uint32_t offset = static_cast<uint32_t>(tile_row * kTileStride + c) * 4;
+                    float2 v[8];
 #pragma unroll
-                        for (int z = 0; z < 8; ++z) v[z] = z < split ? load_cluster_float2(peer_tile[z] + offset) : make_float2(0.0f, 0.0f);
-                        float2 sum = v[0];
+                    for (int z = 0; z < 8; ++z) v[z] = z < split ? load_cluster_float2(peer_tile[z] + offset) : make_float2(0.0f, 0.0f);
+                    float2 sum = v[0];
 #pragma unroll
-                        for (int z = 1; z < 8; ++z) { sum.x += v[z].x; sum.y += v[z].y; }
-                        value[r][pass] = sum;
-                    }
-                    if constexpr (EPI == B200_EPI_RESIDUAL) {
-                        if (feature0 < p.out) {
-                            const float* source = p.residual + static_cast<int64_t>(row) * p.out + feature0;
-                            if ((p.out & 1) == 0) carried[r][pass] = *reinterpret_cast<const float2*>(source);
-                            else carried[r][pass] = make_float2(source[0], feature0 + 1 < p.out ? source[1] : 0.0f);
-                        }
-                    }
-                }
-            }
-#pragma unroll
-            for (int r = 0; r < kBatch; ++r) {
-                const int tile_row = base + r, row = m0 + tile_row;
-                if (tile_row >= last || row >= p.rows) break;
-                const float scale = row_scale[tile_row];
-                float squares = 0.0f;
-                Candidate best{-INFINITY, INT32_MAX};
-#pragma unroll
-                for (int pass = 0; pass < kPasses; ++pass) {
-                    const int feature0 = n0 + pass * 64 + lane * 2;
-                    if (!ready || feature0 >= p.out) continue;
-                    const float a = value[r][pass].x * scale, b = value[r][pass].y * scale;
-                    if constexpr (EPI == B200_EPI_ARGMAX) {
-                        const Candidate pair = pair_candidate(feature0, a, b, p.out);
-                        if (preferred(pair, best)) best = pair;
-                    } else {
-                        finish_pair<EPI>(p, row, feature0, a, b, carried[r][pass], squares, row_place ? row_place + tile_row : nullptr);
-                    }
+                    for (int z = 1; z < 8; ++z) { sum.x += v[z].x; sum.y += v[z].y; }
+                    value[r][pass] = sum;
                 }
                 if constexpr (EPI == B200_EPI_RESIDUAL) {
-                    if (p.sumsq_out) {
-#pragma unroll
-                        for (int o = 16; o > 0; o >>= 1) squares += __shfl_xor_sync(0xffffffffu, squares, o);
-                        if (lane == 0 && ready) p.sumsq_out[static_cast<int64_t>(feature_tile) * p.rows + row] = squares;
-                    }
-                }
-                if constexpr (EPI == B200_EPI_ARGMAX) {
-#pragma unroll
-                    for (int o = 16; o > 0; o >>= 1) {
-                        const Candidate other{__shfl_xor_sync(0xffffffffu, best.value, o), __shfl_xor_sync(0xffffffffu, best.index, o)};
-                        if (preferred(other, best)) best = other;
-                    }
-                    if (lane == 0 && ready) {   // (a caller's warm-up pass hands in accumulators that are not valid: nothing is written)
-                        p.best_value[static_cast<int64_t>(feature_tile) * p.rows + row] = best.value;
-                        p.best_index[static_cast<int64_t>(feature_tile) * p.rows + row] = best.index;
+                    if (feature0 < p.out) {
+                        const float* source = p.residual + static_cast<int64_t>(row) * p.out + feature0;
+                        if ((p.out & 1) == 0) carried[r][pass] = *reinterpret_cast<const float2*>(source);
+                        else carried[r][pass] = make_float2(source[0], feature0 + 1 < p.out ? source[1] : 0.0f);
                     }
                 }
             }
         }
+#pragma unroll
+        for (int r = 0; r < kBatch; ++r) {
+            const int tile_row = base + r, row = m0 + tile_row;
+            if (tile_row >= last || row >= p.rows) break;
+            const float scale = row_scale[tile_row];
+            float squares = 0.0f;
+            Candidate best{-INFINITY, INT32_MAX};
+#pragma unroll
+            for (int pass = 0; pass < kPasses; ++pass) {
+                const int feature0 = n0 + pass * 64 + lane * 2;
+                if (!ready || feature0 >= p.out) continue;
+                const float a = value[r][pass].x * scale, b = value[r][pass].y * scale;
+                if constexpr (EPI == B200_EPI_ARGMAX) {
+                    const Candidate pair = pair_candidate(feature0, a, b, p.out);
+                    if (preferred(pair, best)) best = pair;
+                } else {
+                    finish_pair<EPI>(p, row, feature0, a, b, carried[r][pass], squares, row_place ? row_place + tile_row : nullptr);
+                }
+            }
+            if constexpr (EPI == B200_EPI_RESIDUAL) {
+                if (p.sumsq_out) {
+#pragma unroll
+                    for (int o = 16; o > 0; o >>= 1) squares += __shfl_xor_sync(0xffffffffu, squares, o);
+                    if (lane == 0 && ready) p.sumsq_out[static_cast<int64_t>(feature_tile) * p.rows + row] = squares;
+                }
+            }
+            if constexpr (EPI == B200_EPI_ARGMAX) {
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) {
+                    const Candidate other{__shfl_xor_sync(0xffffffffu, best.value, o), __shfl_xor_sync(0xffffffffu, best.index, o)};
+                    if (preferred(other, best)) best = other;
+                }
+                if (lane == 0 && ready) {   // (a caller's warm-up pass hands in accumulators that are not valid: nothing is written)
+                    p.best_value[static_cast<int64_t>(feature_tile) * p.rows + row] = best.value;
+                    p.best_index[static_cast<int64_t>(feature_tile) * p.rows + row] = best.index;
+                }
+            }
+        }
     }
+}
 
 // kForm: 0 = decided here from the call's sizes and addresses, 1 = the caller has checked that the vector form applies
 // (rows_take_quads on the host side of its launch), 2 = pairs.  kLocal: the `split` partial tiles all lie in this CTA's own
